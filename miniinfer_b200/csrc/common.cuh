@@ -1,0 +1,86 @@
+// Shared declarations of the sm_100a kernel libraries: the C calling convention, element types,
+// error reporting and a few device helpers.
+//
+// Every exported function returns 0 on success.  On a refused size or a failed launch it returns a
+// non-zero code and leaves a message that mi_last_error() of the same library hands out.  Nothing
+// is allocated here; callers pass every buffer and the stream.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define MI_API extern "C" __attribute__((visibility("default")))
+
+enum MiDtype { MI_F32 = 0, MI_BF16 = 1 };
+
+inline thread_local char mi_error_text[1024] = "";
+
+inline int mi_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(mi_error_text, sizeof(mi_error_text), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+#define MI_REQUIRE(cond, ...)              \
+  do {                                     \
+    if (!(cond)) return mi_fail(__VA_ARGS__); \
+  } while (0)
+
+#define MI_LAUNCH_OK(name)                                                              \
+  do {                                                                                  \
+    cudaError_t mi_e = cudaGetLastError();                                              \
+    if (mi_e != cudaSuccess) return mi_fail("%s: launch failed: %s", name, cudaGetErrorString(mi_e)); \
+  } while (0)
+
+// Each library defines mi_last_error once with this.
+#define MI_DEFINE_LAST_ERROR() \
+  MI_API const char* mi_last_error() { return mi_error_text; }
+
+namespace mi {
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of the additions
+// depends only on blockDim, so equal rows give equal sums whatever else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = lane < nw ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+}  // namespace mi

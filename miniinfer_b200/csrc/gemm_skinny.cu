@@ -1,0 +1,175 @@
+// bf16 matrix product for few rows (M <= 64): out[M, N] = x[M, K] * w[N, K]^T, fp32 accumulate,
+// bf16 or fp32 result.  This is the decode step's and the LM head's product, where the time goes
+// into reading the weight matrix once from HBM.
+//
+// Shape of the work: the weight rows are the long axis.  A warp owns 8*NT weight rows and one
+// eighth of K; it streams its weights with 16-byte loads that bypass L1 (each byte is used once),
+// reads the matching activations (small, L1/L2 resident) and multiplies on the tensor cores with
+// mma.m16n8k16 (activations as the 16-row operand, 8 weight rows as the 8-column operand).  The
+// eight warps of a block cover K between them and add their partial tiles in shared memory in a
+// fixed order.  No split across blocks, no atomics: the value of an output element is a function
+// of K alone, so a request's logits do not depend on what else is in the batch.
+//
+// The k index inside a 32-wide block is permuted the same way for both operands so that a thread's
+// 16-byte load is exactly its fragment of two consecutive MMAs (thread t of a quad loads
+// k = 8t..8t+7; MMA s uses elements 4s..4s+3 of it).
+//
+// The reference calls cuBLAS through nn.Linear for these products
+// (miniinfer/models/fused_qwen3.py:95,107,135,137; miniinfer/layers/embedding.py:29-32).
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint4 ld_cached(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_out(TOut* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// MT: 16-row tiles of x (M <= 16*MT).  NT: 8-row tiles of w per warp.
+template <int MT, int NT, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
+  extern __shared__ float red[];  // [WARPS][MT*16][NT*8 + 1]
+  constexpr int RS = NT * 8 + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * (NT * 8);
+
+  const int nkb = (K + 31) / 32;
+  const int per = (nkb + WARPS - 1) / WARPS;
+  const int kb_begin = warp * per;
+  const int kb_end = min(nkb, kb_begin + per);
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+  const __nv_bfloat16* wrow[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) wrow[j] = w + (size_t)min(n0 + j * 8 + g, N - 1) * K;
+
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 wv[NT], wnext[NT];
+  if (kb_begin < kb_end) {
+    const int k = kb_begin * 32 + 8 * t;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) wv[j] = k < K ? ld_stream(wrow[j] + k) : zero;
+  }
+  for (int kb = kb_begin; kb < kb_end; ++kb) {
+    const int k = kb * 32 + 8 * t;
+    if (kb + 1 < kb_end) {
+      const int k2 = k + 32;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) wnext[j] = k2 < K ? ld_stream(wrow[j] + k2) : zero;
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const int ma = i * 16 + g, mb = ma + 8;
+      const uint4 xa = (ma < M && k < K) ? ld_cached(x + (size_t)ma * K + k) : zero;
+      const uint4 xb = (mb < M && k < K) ? ld_cached(x + (size_t)mb * K + k) : zero;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        mma_bf16(acc[i][j], xa.x, xb.x, xa.y, xb.y, wv[j].x, wv[j].y);
+        mma_bf16(acc[i][j], xa.z, xb.z, xa.w, xb.w, wv[j].z, wv[j].w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) wv[j] = wnext[j];
+  }
+
+  // partial tiles -> shared memory; fragment element c of (i, j): row i*16 + g + 8*(c/2), col j*8 + 2t + (c&1)
+  float* mine = red + (size_t)warp * (MT * 16) * RS;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        mine[(i * 16 + g + 8 * (c >> 1)) * RS + j * 8 + 2 * t + (c & 1)] = acc[i][j][c];
+  __syncthreads();
+  const int rows = min(M, MT * 16);
+  for (int idx = threadIdx.x; idx < rows * (NT * 8); idx += WARPS * 32) {
+    const int m = idx / (NT * 8), c = idx % (NT * 8);
+    const int n = n0 + c;
+    if (n >= N) continue;
+    float s = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < WARPS; ++ww) s += red[((size_t)ww * (MT * 16) + m) * RS + c];
+    store_out<TOut>(out + (size_t)m * ldo + n, s);
+  }
+}
+
+template <int MT, int NT, typename TOut>
+int launch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
+           cudaStream_t stream) {
+  const size_t smem = (size_t)WARPS * (MT * 16) * (NT * 8 + 1) * sizeof(float);
+  auto kernel = gemm_skinny_kernel<MT, NT, TOut>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return mi_fail("gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  }
+  const int blocks = (N + NT * 8 - 1) / (NT * 8);
+  kernel<<<blocks, WARPS * 32, smem, stream>>>(out, x, w, M, N, K, ldo);
+  MI_LAUNCH_OK("gemm_skinny");
+  return 0;
+}
+
+template <typename TOut>
+int dispatch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
+             cudaStream_t stream) {
+  // Wider warp tiles re-use the activation fragments; narrower ones make more blocks.  Take the
+  // widest tile that still leaves at least two blocks for each of the 148 SMs.
+  const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
+  int nt = mt;
+  while (nt > 1 && (N + nt * 8 - 1) / (nt * 8) < 296) nt >>= 1;
+#define MI_SK(MT_, NT_) \
+  if (mt == MT_ && nt == NT_) return launch<MT_, NT_, TOut>(out, x, w, M, N, K, ldo, stream)
+  MI_SK(1, 1); MI_SK(2, 1); MI_SK(2, 2); MI_SK(4, 1); MI_SK(4, 2); MI_SK(4, 4);
+#undef MI_SK
+  return mi_fail("gemm_skinny: no kernel for M=%d", M);
+}
+
+}  // namespace
+
+MI_API int mi_gemm_skinny_bf16(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K,
+                               int ldo, cudaStream_t stream) {
+  MI_REQUIRE(M >= 0 && M <= 64, "gemm_skinny: M=%d is not in 0..64 (use the large-M product)", M);
+  MI_REQUIRE(N > 0 && K > 0 && ldo >= N, "gemm_skinny: bad sizes N=%d K=%d ldo=%d", N, K, ldo);
+  MI_REQUIRE(K % 8 == 0, "gemm_skinny: K=%d must be a multiple of 8 (16-byte loads of bf16 rows)", K);
+  MI_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_skinny: operands must be 16-byte aligned");
+  if (M == 0) return 0;
+  if (out_dtype == MI_BF16)
+    return dispatch<__nv_bfloat16>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldo, stream);
+  if (out_dtype == MI_F32)
+    return dispatch<float>((float*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldo, stream);
+  return mi_fail("gemm_skinny: unknown output dtype %d", out_dtype);
+}

@@ -1,0 +1,102 @@
+// One pass over the fused QKV activations of a step:
+//   q, k heads: RMSNorm over the head (optional), then the rotary encoding (optional), in float32,
+//               rounded once and written back in place;
+//   k, v heads: stored into the paged cache at the token's slot (optional).
+//
+// Stands where the reference runs two compiled norms, a dozen torch ops for the rotation
+// (miniinfer/models/fused_qwen3.py:101-105, miniinfer/layers/position_encoding.py:47-116) and an
+// index assignment into the cache (miniinfer/kvcache/memory_pool.py:48-56).
+//
+// Rotation: half-split over the first rotary_dim elements of the head, angles taken from a float32
+// table cos_sin[pos, 0:rotary_dim/2] = cos, [rotary_dim/2:rotary_dim] = sin.
+// Cache layout of one layer: [page, 2 (k, v), kv head, token in page, head_dim].
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_HEAD_DIM = 512;
+constexpr int WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                          const float* __restrict__ cos_sin, int rotary_dim,
+                          const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                          T* __restrict__ kv_layer, int nh, int nkv, int hd, int page_size, float eps) {
+  __shared__ float buf[WARPS][MAX_HEAD_DIM];
+  const int tkn = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nh + 2 * nkv;
+  T* row = qkv + (size_t)tkn * heads * hd;
+  const int pos = positions[tkn];
+  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
+  const int half = rotary_dim / 2;
+  const float* cs = cos_sin ? cos_sin + (size_t)pos * rotary_dim : nullptr;
+
+  for (int h = warp; h < heads; h += WARPS) {
+    T* x = row + (size_t)h * hd;
+    const bool is_q = h < nh;
+    const bool is_k = !is_q && h < nh + nkv;
+    const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+    T* dst = nullptr;
+    if (!is_q && slot >= 0) {
+      const int page = slot / page_size, off = slot % page_size;
+      dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * hd;
+    }
+    if (!is_q && !is_k) {  // v: copy to the cache
+      if (dst)
+        for (int d = lane; d < hd; d += 32) dst[d] = x[d];
+      continue;
+    }
+    const float* w = is_q ? q_w : k_w;
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+      const float v = mi::to_float(x[d]);
+      buf[warp][d] = v;
+      ss += v * v;
+    }
+    float rstd = 1.f;
+    if (w) {
+      ss = mi::warp_sum(ss);
+      rstd = rsqrtf(ss / (float)hd + eps);
+    }
+    __syncwarp();
+    for (int d = lane; d < hd; d += 32) {
+      float v = buf[warp][d] * rstd * (w ? w[d] : 1.f);
+      if (cs && d < rotary_dim) {
+        const int pd = d < half ? d + half : d - half;
+        const float pv = buf[warp][pd] * rstd * (w ? w[pd] : 1.f);
+        const int j = d < half ? d : d - half;
+        const float c = cs[j], s = cs[half + j];
+        v = d < half ? v * c - pv * s : v * c + pv * s;
+      }
+      const T r = mi::from_float<T>(v);
+      x[d] = r;
+      if (dst) dst[d] = r;
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace
+
+MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const float* k_w, const float* cos_sin,
+                                 int rotary_dim, const int* positions, const int* slot_mapping, void* kv_layer,
+                                 int T, int nh, int nkv, int hd, int page_size, float eps, cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && hd > 0, "qk_norm_rope: bad sizes T=%d nh=%d nkv=%d hd=%d", T, nh, nkv, hd);
+  MI_REQUIRE(hd <= MAX_HEAD_DIM, "qk_norm_rope: head_dim=%d is larger than %d", hd, MAX_HEAD_DIM);
+  MI_REQUIRE(!cos_sin || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= hd),
+             "qk_norm_rope: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, hd);
+  MI_REQUIRE(!kv_layer || page_size > 0, "qk_norm_rope: page_size must be positive");
+  if (T == 0) return 0;
+  if (dtype == MI_BF16)
+    qk_norm_rope_store_kernel<<<T, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+                                                           slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, hd, page_size, eps);
+  else if (dtype == MI_F32)
+    qk_norm_rope_store_kernel<<<T, WARPS * 32, 0, stream>>>((float*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+                                                           slot_mapping, (float*)kv_layer, nh, nkv, hd, page_size, eps);
+  else
+    return mi_fail("qk_norm_rope: unknown dtype %d", dtype);
+  MI_LAUNCH_OK("qk_norm_rope_store");
+  return 0;
+}

@@ -1,0 +1,207 @@
+// The sampler: one block per row of float32 logits.
+//
+//   temperature <= 0      arg-max, lowest index among equals
+//   otherwise             z = logit / temperature; keep the top_k largest (0: all), then the
+//                         smallest set of the most likely tokens whose probability reaches top_p
+//                         (1: all); draw from softmax(kept z) by the Gumbel-max rule:
+//                         token = argmax_i (z_i - log(-log u_i)),
+//                         u_i = uniform(seed, counter, i) from a counter-based generator.
+//
+// The reference samples with temperature, top-k and top-p through a library softmax and inverse
+// CDF (miniinfer/layers/sample.py:111-128) from the global generator, so its draws depend on what
+// else is in the batch.  Here a draw is a function of (logits row, seed, counter) alone.
+//
+// Thresholds are found exactly by a 4 x 8-bit radix walk over the order-preserving integer image
+// of z: counts per bin for top-k, probability mass per bin for top-p.  Mass is held as 64-bit
+// fixed point (exp(z - max) * 2^40, integer adds), so the walk does not depend on the order in
+// which threads add.  Entries equal to a threshold are all kept.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  x ^= x >> 30;
+  x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27;
+  x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return x;
+}
+
+__device__ __forceinline__ float uniform_for(uint64_t key, int index) {
+  const uint64_t bits = mix64(key ^ ((uint64_t)index * 0xD1342543DE82EF95ull));
+  return ((float)(bits >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+__device__ __forceinline__ uint32_t ordered(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+struct Best {
+  float v;
+  int i;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+__device__ Best block_argmax(Best mine, Best* scratch /* 32 */) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.v = __shfl_xor_sync(0xffffffffu, mine.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, mine.i, o);
+    mine = better(mine, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = mine;
+  __syncthreads();
+  if (warp == 0) {
+    Best b = scratch[lane];  // THREADS / 32 == 32 warps
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      Best other;
+      other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+      other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+      b = better(b, other);
+    }
+    if (lane == 0) scratch[0] = b;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const long long* __restrict__ seed,
+              const long long* __restrict__ counter, int V) {
+  __shared__ Best best_scratch[32];
+  __shared__ unsigned int count_hist[256];
+  __shared__ unsigned long long mass_hist[256];
+  __shared__ unsigned int sh_prefix;
+  __shared__ unsigned long long sh_above;
+  __shared__ unsigned int sh_rank;
+
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  const float temp = temperature[row];
+
+  if (!(temp > 0.f)) {
+    Best b{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < V; i += THREADS) b = better(b, Best{x[i], i});
+    b = block_argmax(b, best_scratch);
+    if (threadIdx.x == 0) out[row] = b.i < V ? b.i : 0;
+    return;
+  }
+
+  const int k = top_k[row];
+  const float p = top_p[row];
+  uint32_t thr_k = 0u, thr_p = 0u;  // keep entries whose ordered image is >= both
+
+  if (k > 0 && k < V) {
+    // the k-th largest z: walk the bits from the top, keeping the rank still wanted
+    if (threadIdx.x == 0) { sh_prefix = 0u; sh_rank = (unsigned)k; }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (threadIdx.x < 256) count_hist[threadIdx.x] = 0u;
+      __syncthreads();
+      const uint32_t prefix = sh_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = threadIdx.x; i < V; i += THREADS) {
+        const uint32_t u = ordered(x[i] / temp);
+        if ((u & mask) == prefix) atomicAdd(&count_hist[(u >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        unsigned want = sh_rank, seen = 0;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (seen + count_hist[b] >= want) break;
+          seen += count_hist[b];
+        }
+        sh_rank = want - seen;
+        sh_prefix = prefix | ((uint32_t)b << shift);
+      }
+      __syncthreads();
+    }
+    thr_k = sh_prefix;
+    __syncthreads();
+  }
+
+  if (p < 1.f) {
+    // max of the kept entries, then their total mass in fixed point
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+      const float z = x[i] / temp;
+      if (ordered(z) >= thr_k) mx = fmaxf(mx, z);
+    }
+    mx = block_argmax(Best{mx, 0}, best_scratch).v;
+    if (threadIdx.x == 0) { sh_prefix = 0u; sh_above = 0ull; }
+    unsigned long long target = 0ull;  // used by thread 0 only
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      if (threadIdx.x < 256) mass_hist[threadIdx.x] = 0ull;
+      __syncthreads();
+      const uint32_t prefix = sh_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = threadIdx.x; i < V; i += THREADS) {
+        const float z = x[i] / temp;
+        const uint32_t u = ordered(z);
+        if (u >= thr_k && (u & mask) == prefix) {
+          const unsigned long long q = (unsigned long long)(expf(z - mx) * 1099511627776.0f);
+          if (q) atomicAdd(&mass_hist[(u >> shift) & 255u], q);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        if (pass == 0) {
+          unsigned long long total = 0ull;
+          for (int b = 0; b < 256; ++b) total += mass_hist[b];
+          target = (unsigned long long)((double)total * (double)p);
+          if (target < 1ull) target = 1ull;
+        }
+        // first bin, from the top, at which the inclusive mass reaches the target
+        unsigned long long above = sh_above;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (above + mass_hist[b] >= target) break;
+          above += mass_hist[b];
+        }
+        sh_above = above;
+        sh_prefix = prefix | ((uint32_t)b << shift);
+      }
+      __syncthreads();
+    }
+    thr_p = sh_prefix;
+    __syncthreads();
+  }
+
+  const uint32_t thr = thr_k > thr_p ? thr_k : thr_p;
+  const uint64_t key = mix64((uint64_t)seed[row] ^ mix64((uint64_t)counter[row] + 0x9E3779B97F4A7C15ull));
+  Best b{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < V; i += THREADS) {
+    const float z = x[i] / temp;
+    if (ordered(z) < thr || !(z > -INFINITY)) continue;
+    const float u = uniform_for(key, i);
+    b = better(b, Best{z - logf(-logf(u)), i});
+  }
+  b = block_argmax(b, best_scratch);
+  if (threadIdx.x == 0) out[row] = b.i < V ? b.i : 0;
+}
+
+}  // namespace
+
+MI_API int mi_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                     const long long* seed, const long long* counter, int R, int V, cudaStream_t stream) {
+  MI_REQUIRE(R >= 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
+  if (R == 0) return 0;
+  sample_kernel<<<R, THREADS, 0, stream>>>(out, logits, temperature, top_k, top_p, seed, counter, V);
+  MI_LAUNCH_OK("sample");
+  return 0;
+}

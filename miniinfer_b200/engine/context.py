@@ -1,0 +1,70 @@
+"""What a step hands to the parts: the batch's device-side description and a workspace.
+
+The reference's counterpart is ``ForwardBatch`` (miniinfer/scheduler/scheduler_batch.py:235-442).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..kernels.ops import AttentionBatch
+
+
+class Workspace:
+  """Named activation buffers that keep their address from step to step, so that a captured step
+  can be replayed.  A buffer grows when a larger one is asked for (never while capturing)."""
+
+  def __init__(self, device):
+    self.device = device
+    self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+    self.frozen = False
+
+  def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+    n = 1
+    for s in shape:
+      n *= int(s)
+    key = (name, dtype)
+    buf = self._bufs.get(key)
+    if buf is None or buf.numel() < n:
+      if self.frozen:
+        raise RuntimeError(f"workspace buffer {name!r} would have to grow to {n} elements while frozen")
+      buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+      self._bufs[key] = buf
+    return buf[:n].view(*shape)
+
+  def bytes(self) -> int:
+    return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+class StepContext:
+  """Everything about the running step that a part may read.
+
+  ``positions[t]``, ``token_item[t]``: per token; ``q_start/q_len/ctx_len/seq_slot[b]``: per item;
+  ``slot_mapping[g][t]`` and ``block_tables[g]``: per group of paged layers; ``state_slots`` is
+  ``seq_slot`` (the row of a request in every per-request state tensor); ``host`` keeps the same
+  numbers as Python lists for parts that loop on the host."""
+
+  def __init__(self, dtype: torch.dtype, device, ws: Workspace):
+    self.dtype = dtype
+    self.device = device
+    self.ws = ws
+    self.num_tokens = 0
+    self.num_items = 0
+    self.ids: Optional[torch.Tensor] = None
+    self.positions: Optional[torch.Tensor] = None
+    self.token_item: Optional[torch.Tensor] = None
+    self.q_start: Optional[torch.Tensor] = None
+    self.q_len: Optional[torch.Tensor] = None
+    self.ctx_len: Optional[torch.Tensor] = None
+    self.seq_slot: Optional[torch.Tensor] = None
+    self.logit_rows: Optional[torch.Tensor] = None
+    self.slot_mapping: List[torch.Tensor] = []
+    self.block_tables: List[torch.Tensor] = []
+    self.attn: Optional[AttentionBatch] = None
+    self.host: Dict[str, list] = {}
+
+  @property
+  def state_slots(self) -> torch.Tensor:
+    return self.seq_slot

@@ -1,0 +1,231 @@
+"""The engine's device operations: thin checked wrappers over the sm_100a kernel libraries.
+
+Every function writes into tensors the caller passes, runs on the current CUDA stream and
+allocates nothing, so that a step can be captured in a CUDA graph.  There is no other
+implementation behind these names: if the libraries cannot be built or loaded, or a tensor is not
+on a CUDA device, the call raises.
+
+Large-M bf16 matrix products go to cuBLAS through ``torch.matmul`` - the reference uses the same
+library for all of its products (miniinfer/layers/linear.py:30-32); everything else is this
+package's own CUDA.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+SKINNY_MAX_M = 64
+
+
+class KernelError(RuntimeError):
+  """A kernel refused its arguments or failed to launch."""
+
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+def _load(name: str, path: str) -> ctypes.CDLL:
+  lib = ctypes.CDLL(path)
+  lib.mi_last_error.restype = ctypes.c_char_p
+  _libs[name] = lib
+  return lib
+
+
+def common_lib() -> ctypes.CDLL:
+  lib = _libs.get("common")
+  if lib is None:
+    lib = _load("common", build.build_common())
+  return lib
+
+
+def attention_lib(head_dim: int) -> ctypes.CDLL:
+  name = f"attn_hd{head_dim}"
+  lib = _libs.get(name)
+  if lib is None:
+    lib = _load(name, build.build_attention(head_dim))
+  return lib
+
+
+def loaded_libraries() -> Dict[str, str]:
+  return {k: v._name for k, v in _libs.items()}
+
+
+def _check(lib: ctypes.CDLL, code: int) -> None:
+  if code != 0:
+    raise KernelError(lib.mi_last_error().decode())
+
+
+def _dt(t: torch.Tensor) -> int:
+  if t.dtype == torch.float32:
+    return F32
+  if t.dtype == torch.bfloat16:
+    return BF16
+  raise KernelError(f"dtype {t.dtype} is not supported (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor], dtype: Optional[torch.dtype] = None) -> ctypes.c_void_p:
+  if t is None:
+    return ctypes.c_void_p(0)
+  if not t.is_cuda:
+    raise KernelError("the engine's kernels run on CUDA tensors only (got a CPU tensor)")
+  if not t.is_contiguous():
+    raise KernelError("kernel arguments must be contiguous")
+  if dtype is not None and t.dtype != dtype:
+    raise KernelError(f"expected {dtype}, got {t.dtype}")
+  return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+  return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# --------------------------------------------------------------------------------------------
+
+
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+  """out[t] = table[ids[t]] as float32.  ids: int32, already checked to lie in the vocabulary."""
+  lib = common_lib()
+  T, H = out.shape
+  if table.shape[1] != H or ids.shape[0] != T:
+    raise KernelError("embedding: shapes do not match")
+  _check(lib, lib.mi_embedding(_ptr(out, torch.float32), _ptr(table), _dt(table), _ptr(ids, torch.int32),
+                               T, H, _stream()))
+
+
+def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+  """out[r] = weight * norm(resid[row] + delta[row]); the sum goes back to resid if write_back."""
+  lib = common_lib()
+  R, H = out.shape
+  if resid.shape[1] != H or weight.shape[0] != H or (delta is not None and delta.shape != resid.shape):
+    raise KernelError("add_rmsnorm: shapes do not match")
+  if rows is None and resid.shape[0] != R:
+    raise KernelError("add_rmsnorm: out and resid differ in rows")
+  if rows is not None and rows.shape[0] != R:
+    raise KernelError("add_rmsnorm: rows and out differ in length")
+  _check(lib, lib.mi_add_rmsnorm(_ptr(out), _dt(out), _ptr(resid, torch.float32), _ptr(delta),
+                                 _dt(delta) if delta is not None else F32, _ptr(weight, torch.float32),
+                                 _ptr(rows, torch.int32) if rows is not None else _ptr(None), R, H,
+                                 ctypes.c_float(eps), int(bool(write_back)), _stream()))
+
+
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+  """out[M, N] = x[M, K] @ w[N, K]^T.  float32 operands: this package's fp32 FMA kernel (out float32).
+  bfloat16 operands: its skinny tensor-core kernel for M <= 64 (out bf16 or fp32), cuBLAS above
+  (out bf16; an fp32 out is produced in slices of 64 rows by the skinny kernel)."""
+  M, K = x.shape
+  N = w.shape[0]
+  if w.shape[1] != K or out.shape != (M, N):
+    raise KernelError(f"linear: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if M == 0:
+    return
+  lib = common_lib()
+  if x.dtype == torch.float32:
+    _check(lib, lib.mi_gemm_f32(_ptr(out, torch.float32), _ptr(x), _ptr(w, torch.float32), M, N, K, N, _stream()))
+    return
+  if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+    raise KernelError(f"linear: operands must both be float32 or both bfloat16, got {x.dtype} and {w.dtype}")
+  if M <= SKINNY_MAX_M:
+    _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, N, _stream()))
+  elif out.dtype == torch.bfloat16:
+    if not (out.is_cuda and out.is_contiguous()):
+      raise KernelError("linear: out must be a contiguous CUDA tensor")
+    torch.matmul(x, w.t(), out=out)
+  else:
+    for m0 in range(0, M, SKINNY_MAX_M):
+      m1 = min(M, m0 + SKINNY_MAX_M)
+      _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out[m0:m1]), _dt(out), _ptr(x[m0:m1]), _ptr(w), m1 - m0, N, K, N,
+                                          _stream()))
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                       cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
+                       slot_mapping: Optional[torch.Tensor], kv_layer: Optional[torch.Tensor],
+                       num_heads: int, num_kv_heads: int, head_dim: int, eps: float) -> None:
+  """In place on the fused QKV rows: per-head RMSNorm of q and k, rotary encoding from the table,
+  and the store of k and v into the layer's pages at ``slot_mapping`` (page * page_size + offset)."""
+  lib = common_lib()
+  T = qkv.shape[0]
+  if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+    raise KernelError("qk_norm_rope_store: qkv width does not match the head counts")
+  rotary_dim = 0
+  if cos_sin is not None:
+    rotary_dim = cos_sin.shape[1]
+  page_size = 0
+  if kv_layer is not None:
+    if kv_layer.dtype != qkv.dtype:
+      raise KernelError("qk_norm_rope_store: cache and activations differ in dtype")
+    if kv_layer.shape[1:] != (2, num_kv_heads, kv_layer.shape[3], head_dim):
+      raise KernelError(f"qk_norm_rope_store: cache layer has shape {tuple(kv_layer.shape)}")
+    page_size = kv_layer.shape[3]
+  _check(lib, lib.mi_qk_norm_rope_store(
+    _ptr(qkv), _dt(qkv), _ptr(q_weight, torch.float32) if q_weight is not None else _ptr(None),
+    _ptr(k_weight, torch.float32) if k_weight is not None else _ptr(None),
+    _ptr(cos_sin, torch.float32) if cos_sin is not None else _ptr(None), rotary_dim,
+    _ptr(positions, torch.int32), _ptr(slot_mapping, torch.int32) if slot_mapping is not None else _ptr(None),
+    _ptr(kv_layer), T, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(eps), _stream()))
+
+
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
+  lib = common_lib()
+  T, I = out.shape
+  if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+    raise KernelError("silu_mul: shapes or dtypes do not match")
+  _check(lib, lib.mi_silu_mul(_ptr(out), _ptr(gate_up), _dt(out), T, I, _stream()))
+
+
+def sample(out: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor) -> None:
+  """One token per row of float32 logits; see ``sampling/sampler.py`` for the rule."""
+  lib = common_lib()
+  R, V = logits.shape
+  for t in (out, temperature, top_k, top_p, seed, counter):
+    if t.shape[0] != R:
+      raise KernelError("sample: per-row arguments differ in length")
+  _check(lib, lib.mi_sample(_ptr(out, torch.int32), _ptr(logits, torch.float32), _ptr(temperature, torch.float32),
+                            _ptr(top_k, torch.int32), _ptr(top_p, torch.float32), _ptr(seed, torch.int64),
+                            _ptr(counter, torch.int64), R, V, _stream()))
+
+
+class AttentionBatch:
+  """Device-side description of a step for the attention kernels (all int32).
+
+  ``token_item[t]``: the batch item of token t; ``positions[t]``: its position in its request;
+  ``seq_slot[b]``: the block-table row of item b; ``q_start[b]``, ``q_len[b]``, ``ctx_len[b]``:
+  the item's first row, its number of new tokens and its length including them.
+  Host-side lists the launchers need: ``prefill_items`` / ``decode_items`` (device int32 lists of
+  item indices with more than one / exactly one new token), their lengths and the largest context."""
+
+  __slots__ = ("token_item", "positions", "seq_slot", "q_start", "q_len", "ctx_len", "num_tokens", "num_items",
+               "prefill_tiles", "num_prefill_tiles", "decode_items", "num_decode", "max_ctx_len", "decode_rows",
+               "scratch")
+
+  def __init__(self, **kw):
+    for k in self.__slots__:
+      setattr(self, k, kw.get(k))
+
+
+def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
+              batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+              window: Optional[int], force_generic: bool = False) -> None:
+  """out[t, h*hd:(h+1)*hd] = softmax(scale * q . K^T over the keys the token may see) V, reading
+  K and V through the block table.  ``qkv`` holds the step's fused rows; q is its first part."""
+  T = qkv.shape[0]
+  if out.shape != (T, num_heads * head_dim) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype:
+    raise KernelError("attention: shapes or dtypes do not match")
+  page_size = kv_layer.shape[3]
+  if kv_layer.shape[1:] != (2, num_kv_heads, page_size, head_dim):
+    raise KernelError(f"attention: cache layer has shape {tuple(kv_layer.shape)}")
+  win = int(window) if window else 0
+  lib = common_lib()
+  _check(lib, lib.mi_attention_generic(
+    _ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), _ptr(kv_layer), _ptr(block_table, torch.int32),
+    block_table.shape[1], _ptr(batch.token_item, torch.int32), _ptr(batch.positions, torch.int32),
+    _ptr(batch.seq_slot, torch.int32), T, num_heads, num_kv_heads, head_dim, page_size,
+    ctypes.c_float(scale), win, _stream()))

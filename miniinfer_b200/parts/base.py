@@ -1,0 +1,120 @@
+"""What every part of a layer is: a named holder of parameters with a forward method.
+
+A part knows its own sizes and constants (they are constructor arguments) and the names under
+which its tensors may appear in a weights file.  It does not know which model it is in, which
+layer it is, or what the other parts of its block are.
+
+Interfaces (see the concrete parts for examples):
+
+``Norm``           ``add_norm(resid, delta, ctx) -> x``: adds ``delta`` (or nothing) into the float32
+                   residual rows in place and returns the normalised rows in the compute dtype;
+                   ``norm_rows(resid, delta, rows, ctx) -> x``: the same for selected rows, without
+                   changing the residual.
+``Mixer``          ``cache_spec() -> CacheSpec | None`` and ``forward(x, ctx, cache) -> delta``: mixes
+                   information across the tokens of a request, using and updating ``cache``.
+``FeedForward``    ``forward(x, ctx) -> delta``: acts on each token alone.
+``PositionEncoding`` gives mixers what they need to encode positions (``rotary_table()``), and may
+                   act on the hidden state after the embedding (``apply_to_hidden``).
+``Block``          ``forward(resid, pending, ctx, cache) -> pending``: the arrangement of the above.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.specs import CacheSpec
+
+
+@dataclass(frozen=True)
+class Piece:
+  """A tensor of the weights file that fills rows ``row_start .. row_start + shape[0]`` of a parameter."""
+
+  file_name: str
+  row_start: int
+  shape: Tuple[int, ...]
+
+
+@dataclass
+class ParamSpec:
+  """A parameter: its shape, its role (``matrix``/``table``: kept in the compute dtype; ``vector``:
+  kept in float32; ``int``: kept as int32) and the alternative sets of file tensors that fill it."""
+
+  shape: Tuple[int, ...]
+  role: str
+  sources: List[List[Piece]]
+  init: str = "normal"            # random-weights mode: "normal" (std given by the model) or "ones_noise"
+
+  def __post_init__(self):
+    if self.role not in ("matrix", "table", "vector", "int"):
+      raise ValueError(f"unknown parameter role {self.role!r}")
+
+
+def whole(file_name: str, shape: Sequence[int]) -> List[Piece]:
+  return [Piece(file_name, 0, tuple(shape))]
+
+
+class Part:
+  """Base of all parts.  ``name`` is the prefix of the part's tensors in a weights file."""
+
+  def __init__(self, name: str):
+    self.name = name
+    self.params: Dict[str, torch.Tensor] = {}
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    return {}
+
+  def bind(self, params: Dict[str, torch.Tensor]) -> None:
+    """Receives the loaded parameters (device tensors) by local name."""
+    self.params = params
+    for k, v in params.items():
+      setattr(self, k, v)
+
+  def sub_parts(self) -> List["Part"]:
+    return []
+
+
+class Norm(Part):
+  def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+  def norm_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor, ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+
+class PositionEncoding(Part):
+  def rotary_table(self) -> Optional[torch.Tensor]:
+    """[positions, rotary_dim] float32, cos in the first half of a row and sin in the second; or None."""
+    return None
+
+  def max_positions(self) -> Optional[int]:
+    return None
+
+  def apply_to_hidden(self, resid: torch.Tensor, ctx) -> None:
+    """Acts on the float32 hidden state right after the embedding; default: nothing."""
+
+  def prepare(self, device, max_positions: int) -> None:
+    """Builds device tables for positions below ``max_positions``."""
+
+
+class Mixer(Part):
+  def cache_spec(self) -> Optional[CacheSpec]:
+    return None
+
+  def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    raise NotImplementedError
+
+
+class FeedForward(Part):
+  def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+
+class Block(Part):
+  def mixer_part(self) -> Optional[Mixer]:
+    return None
+
+  def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx, cache) -> Optional[torch.Tensor]:
+    raise NotImplementedError

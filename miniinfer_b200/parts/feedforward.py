@@ -1,0 +1,39 @@
+"""Dense SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))`` with gate and up in one matrix
+(miniinfer/models/fused_qwen3.py:111-138; order gate, up: miniinfer/loader/weight.py:87-93).
+"""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward, ParamSpec, Piece, whole
+
+
+class SwiGLUFeedForward(FeedForward):
+  def __init__(self, name: str, hidden_size: int, intermediate_size: int):
+    super().__init__(name)
+    self.hidden_size = hidden_size
+    self.intermediate_size = intermediate_size
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    H, I = self.hidden_size, self.intermediate_size
+    return {
+      "gate_up": ParamSpec((2 * I, H), "matrix", [
+        [Piece(f"{self.name}.gate_proj.weight", 0, (I, H)), Piece(f"{self.name}.up_proj.weight", I, (I, H))],
+        whole(f"{self.name}.gate_up_proj.weight", (2 * I, H)),
+      ]),
+      "down": ParamSpec((H, I), "matrix", [whole(f"{self.name}.down_proj.weight", (H, I))]),
+    }
+
+  def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    T = x.shape[0]
+    gu = ctx.ws.buffer("gate_up", (T, 2 * self.intermediate_size), ctx.dtype)
+    ops.linear(gu, x, self.gate_up)
+    act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)
+    ops.silu_mul(act, gu)
+    out = ctx.ws.buffer("ffn_out", (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, act, self.down)
+    return out
