@@ -64,6 +64,7 @@ class StepContext:
     self.block_tables: List[torch.Tensor] = []
     self.attn: Optional[AttentionBatch] = None
     self.host: Dict[str, list] = {}
+    self.extra: Dict[str, torch.Tensor] = {}
 
   @property
   def state_slots(self) -> torch.Tensor:

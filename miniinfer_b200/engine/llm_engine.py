@@ -1,0 +1,213 @@
+"""The Python entry point: ``LLMEngine(model, **options).generate(prompts, sampling_params)``.
+
+Names follow the reference (miniinfer/engine/llm_engine.py): ``LLMEngine(model, **kwargs)`` :87,
+``generate(prompts, sampling_params, use_tqdm)`` :898 returning a list of
+``{"text", "token_ids", "request_id"}`` ordered by request :966-1015, ``add_request`` :1309,
+``step`` :465, ``is_finished`` :1271, ``start``/``stop`` and use as a context manager :1301-1306.
+Prompts are lists of token ids, or strings when the model folder has a ``tokenizer.json``.
+One process, one GPU; no server, no worker processes.
+"""
+
+from __future__ import annotations
+
+import os
+import time
+from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache.manager import KVCacheManager
+from ..config import EngineConfig, build_model_spec, load_model_config
+from ..sampling import Sampler, SamplingParams, derive_seed
+from ..utils.logging import get_logger
+from ..weights import load_weights
+from .runner import ModelRunner, StepItem
+from .scheduler import Request, Scheduler, SchedulerOutput
+
+logger = get_logger(__name__)
+
+
+def size_cache_pages(layer_specs, page_size: int, dtype: torch.dtype, device: torch.device,
+                     utilization: float, max_num_seqs: int, max_model_len: int) -> int:
+  """Pages per group from the memory that is free now (the reference: a share of the free memory
+  divided by the bytes of one token, miniinfer/utils/memory_utils.py:85-144), capped at what
+  ``max_num_seqs`` requests of ``max_model_len`` tokens could ever hold."""
+  per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype)
+  cap = max_num_seqs * (-(-max_model_len // page_size))
+  if per_page == 0:
+    return 1
+  if device.type != "cuda":
+    return cap
+  free, total = torch.cuda.mem_get_info(device)
+  usable = free - (1.0 - utilization) * total
+  pages = int(usable * 0.9) // per_page
+  if pages < 2:
+    raise RuntimeError(f"not enough free device memory for the cache: {free >> 20} MiB free, "
+                       f"one page costs {per_page >> 10} KiB")
+  return min(pages, cap)
+
+
+class LLMEngine:
+  def __init__(self, model: str, **kwargs: Any):
+    self.config = EngineConfig.from_kwargs(model, **kwargs)
+    cfg = self.config
+    self.device = torch.device(cfg.device)
+    if self.device.type == "cuda":
+      torch.cuda.set_device(self.device)
+    self.model_config = load_model_config(cfg.model_path)
+    self.spec = build_model_spec(self.model_config)
+    t0 = time.time()
+    load_weights(self.spec, cfg.model_path, cfg.dtype, self.device)
+    logger.info("weights loaded in %.1f s", time.time() - t0)
+    cfg.max_context_len = min(cfg.max_context_len, self.model_config.max_position_embeddings)
+    layer_specs = self.spec.cache_layer_specs()
+    num_pages = cfg.num_pages
+    if num_pages is None:
+      num_pages = size_cache_pages(layer_specs, cfg.page_size, cfg.dtype, self.device, cfg.gpu_memory_utilization,
+                                   cfg.max_num_seqs, cfg.max_context_len)
+    self.cache = KVCacheManager(layer_specs, cfg.page_size, num_pages, cfg.max_num_seqs, cfg.max_context_len,
+                                cfg.dtype, self.device)
+    self.runner = ModelRunner(self.spec, self.cache, cfg.dtype, self.device)
+    self.scheduler = Scheduler(self.cache, cfg.max_num_seqs, cfg.max_num_batched_tokens, cfg.chunked_prefill_size,
+                               cfg.max_context_len, self.model_config.eos_ids())
+    self.tokenizer = self._load_tokenizer(cfg.model_path)
+    self._requests: Dict[Hashable, Request] = {}
+    self._next_id = 0
+    self._tokens_host: Optional[torch.Tensor] = None
+    self._tokens_dev: Optional[torch.Tensor] = None
+    self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+
+  # ------------------------------------------------------------------ life cycle (API parity)
+
+  def start(self) -> "LLMEngine":
+    return self
+
+  def stop(self) -> None:
+    pass
+
+  def __enter__(self) -> "LLMEngine":
+    return self.start()
+
+  def __exit__(self, *exc) -> None:
+    self.stop()
+
+  # ------------------------------------------------------------------ text
+
+  @staticmethod
+  def _load_tokenizer(model_dir: str):
+    path = os.path.join(model_dir, "tokenizer.json")
+    if not os.path.exists(path):
+      return None
+    try:
+      from tokenizers import Tokenizer
+    except ImportError:
+      return None
+    return Tokenizer.from_file(path)
+
+  def _encode(self, prompt: Union[str, Sequence[int]]) -> List[int]:
+    if isinstance(prompt, str):
+      if self.tokenizer is None:
+        raise ValueError("a text prompt needs tokenizer.json in the model folder; pass token ids instead")
+      return list(self.tokenizer.encode(prompt).ids)
+    return [int(t) for t in prompt]
+
+  def _decode(self, ids: Sequence[int]) -> Optional[str]:
+    return self.tokenizer.decode(list(ids)) if self.tokenizer is not None else None
+
+  # ------------------------------------------------------------------ requests
+
+  def add_request(self, prompt: Union[str, Sequence[int]], sampling_params: Optional[SamplingParams] = None,
+                  request_id: Optional[Hashable] = None) -> Hashable:
+    params = sampling_params or SamplingParams()
+    rid = request_id if request_id is not None else self._next_id
+    if rid in self._requests:
+      raise ValueError(f"request id {rid!r} is in use")
+    self._next_id += 1
+    req = Request(req_id=rid, prompt_ids=self._encode(prompt), params=params)
+    self.scheduler.add(req)
+    req.seed = params.seed if params.seed is not None else derive_seed(self.config.seed, req.number)
+    self._requests[rid] = req
+    return rid
+
+  def is_finished(self) -> bool:
+    return not self.scheduler.has_unfinished()
+
+  def has_unfinished(self) -> bool:
+    return self.scheduler.has_unfinished()
+
+  # ------------------------------------------------------------------ one step
+
+  def _token_buffers(self, n: int):
+    if self._tokens_dev is None or self._tokens_dev.numel() < n:
+      cap = max(n, 256)
+      self._tokens_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+      self._tokens_host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+    return self._tokens_dev, self._tokens_host
+
+  @torch.no_grad()
+  def step(self) -> List[Dict[str, Any]]:
+    """Schedules, runs and samples one step; returns the outputs of the requests that finished."""
+    out = self.scheduler.schedule()
+    if not out.items:
+      return []
+    items, sampling_reqs = [], []
+    for it in out.items:
+      n = len(it.tokens)
+      items.append(StepItem(it.request.req_id, it.tokens, (n - 1,) if it.samples else ()))
+      if it.samples:
+        sampling_reqs.append(it.request)
+    extras = Sampler.pack([r.params for r in sampling_reqs], [r.seed for r in sampling_reqs],
+                          [len(r.output_ids) for r in sampling_reqs]) if sampling_reqs else {}
+    logits, ctx = self.runner.step(items, extras, return_ctx=True)
+    sampled: Dict[Hashable, int] = {}
+    R = len(sampling_reqs)
+    if R:
+      dev, host = self._token_buffers(R)
+      Sampler.sample(logits, ctx.extra, dev[:R])
+      host[:R].copy_(dev[:R], non_blocking=True)
+      if self.device.type == "cuda":
+        torch.cuda.current_stream().synchronize()
+      toks = host[:R].tolist()
+      sampled = {r.req_id: t for r, t in zip(sampling_reqs, toks)}
+      self.stats["d2h_bytes"] += 4 * R
+    self.stats["steps"] += 1
+    self.stats["prefill_tokens"] += out.num_prefill_tokens
+    self.stats["decode_tokens"] += out.num_decode_tokens
+    done = self.scheduler.update(out, sampled)
+    return [self._output_of(r) for r in done]
+
+  def _output_of(self, req: Request) -> Dict[str, Any]:
+    return {"text": self._decode(req.output_ids), "token_ids": list(req.output_ids), "request_id": req.req_id,
+            "finish_reason": req.finish_reason}
+
+  # ------------------------------------------------------------------ generate
+
+  def generate(self, prompts: Union[str, Sequence[int], Sequence[Union[str, Sequence[int]]]],
+               sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+               use_tqdm: bool = False) -> List[Dict[str, Any]]:
+    """Runs all prompts to completion; returns one dict per prompt, in the order given."""
+    if isinstance(prompts, str) or (len(prompts) > 0 and isinstance(prompts[0], int)):
+      prompts = [prompts]  # type: ignore[list-item]
+    if sampling_params is None or isinstance(sampling_params, SamplingParams):
+      plist = [sampling_params or SamplingParams()] * len(prompts)
+    else:
+      plist = list(sampling_params)
+      if len(plist) != len(prompts):
+        raise ValueError("sampling_params and prompts differ in length")
+    ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+    bar = None
+    if use_tqdm:
+      from tqdm import tqdm
+      bar = tqdm(total=len(ids), desc="Generating")
+    results: Dict[Hashable, Dict[str, Any]] = {}
+    while not self.is_finished():
+      for o in self.step():
+        results[o["request_id"]] = o
+        if bar is not None:
+          bar.update(1)
+    if bar is not None:
+      bar.close()
+    for rid in ids:
+      self._requests.pop(rid, None)
+    return [results[rid] for rid in ids]

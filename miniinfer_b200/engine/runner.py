@@ -59,7 +59,7 @@ class ModelRunner:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
     self._meta_host: Optional[torch.Tensor] = None
     self._meta_dev: Optional[torch.Tensor] = None
-    self.kernel_launches = 0
+    self._copy_done = None
 
   # ------------------------------------------------------------------ metadata
 
@@ -71,7 +71,7 @@ class ModelRunner:
       self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
     return self._meta_host, self._meta_dev
 
-  def prepare(self, items: Sequence[StepItem]) -> StepContext:
+  def prepare(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
     """Reserves cache room for the items' tokens and builds the step's device-side description
     with one host-to-device copy."""
     cache = self.cache
@@ -127,12 +127,16 @@ class ModelRunner:
     sizes += [(f"slot_mapping{g}", T) for g in range(G)]
     sizes += [("q_start", B), ("q_len", B), ("ctx_len", B), ("seq_slot", B), ("logit_rows", R),
               ("decode_items", len(dec_items)), ("prefill_tiles", 2 * len(pre_tiles))]
+    extras = extras or {}
+    sizes += [(f"extra:{k}", len(v)) for k, v in extras.items()]
     offsets = {}
     total = 0
     for name, n in sizes:
       offsets[name] = (total, n)
       total += _pad4(n)
     host, dev = self._meta_buffers(total)
+    if self._copy_done is not None:
+      self._copy_done.synchronize()    # the staging buffer may still be feeding the previous copy
     h = host.numpy()
 
     def put(name, arr):
@@ -152,7 +156,12 @@ class ModelRunner:
     put("logit_rows", rows)
     put("decode_items", np.array(dec_items, dtype=np.int32))
     put("prefill_tiles", np.array(pre_tiles, dtype=np.int32).reshape(-1))
+    for k, v in extras.items():
+      put(f"extra:{k}", v)
     dev[:total].copy_(host[:total], non_blocking=True)
+    if self.device.type == "cuda":
+      self._copy_done = torch.cuda.Event()
+      self._copy_done.record()
     cache.sync()
 
     def view(name):
@@ -168,6 +177,7 @@ class ModelRunner:
     ctx.block_tables = [g.block_table for g in cache.paged_groups]
     ctx.host = {"q_len": q_len.tolist(), "q_start": q_start.tolist(), "start": starts,
                 "seq_slot": seq_slot.tolist(), "logit_rows": rows.tolist()}
+    ctx.extra = {k: view(f"extra:{k}") for k in extras}
     ctx.attn = AttentionBatch(
       token_item=ctx.token_item, positions=ctx.positions, seq_slot=ctx.seq_slot, q_start=ctx.q_start,
       q_len=ctx.q_len, ctx_len=ctx.ctx_len, num_tokens=T, num_items=B,
@@ -193,8 +203,8 @@ class ModelRunner:
     return spec.lm_head.forward(x, ctx)
 
   @torch.no_grad()
-  def step(self, items: Sequence[StepItem]) -> torch.Tensor:
-    ctx = self.prepare(items)
+  def step(self, items: Sequence[StepItem], extras: Optional[dict] = None, return_ctx: bool = False):
+    ctx = self.prepare(items, extras)
     try:
       logits = self.forward(ctx)
     except BaseException:
@@ -203,4 +213,4 @@ class ModelRunner:
       raise
     for it in items:
       self.cache.commit(it.req_id, len(it.tokens))
-    return logits
+    return (logits, ctx) if return_ctx else logits
