@@ -1,0 +1,131 @@
+"""The host side of the engine - cache manager, step metadata, scheduler, replay program - run on the
+CPU with the kernels replaced by their PyTorch statements (tests/torch_ops.py), against the plain
+implementation.  The CUDA kernels themselves are tested by the ``gpu`` tests."""
+import io
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import replay_cases as rc
+from tiny_configs import ALL
+
+LENGTHS = {"A": (5, 17, 33, 100, 64, 41), "B": (1, 9, 40, 71, 130, 65), "C": (90, 33, 150, 64, 7)}
+
+
+def make_runner(model_dir, page_size, max_tokens):
+  from miniinfer_b200.engine.replay import TraceRunner
+  return TraceRunner(model_dir, "float32", max_tokens, device="cpu", page_size=page_size)
+
+
+@pytest.mark.parametrize("tag,page", [("A", 16), ("B", 8), ("C", 8)])
+def test_every_cut_gives_the_plain_logits(cpu_kernels, model_dirs, tag, page):
+  d = model_dirs(tag)
+  reqs = rc.make_requests(ALL[tag]["vocab_size"], LENGTHS[tag], seed=5)
+  ref = rc.reference_logits(d, reqs)
+  budget = 4 * rc.round_up(max(LENGTHS[tag]), page)
+  for name, trace in (("whole", rc.whole(reqs)), ("tail", rc.tail_one_by_one(reqs)), ("portions", rc.portions(reqs)),
+                      ("mixed", rc.mixed(reqs, budget // 2, seed=1, granule=page))):
+    runner = make_runner(d, page, budget if name != "mixed" else budget // 2)
+    got = rc.run_in_process(runner, trace)
+    rc.compare(got, ref, 2e-5, f"{tag}/{name}")
+    runner.cache.check_invariants()
+    assert runner.cache.free_pages() == [g.num_pages for g in runner.cache.paged_groups]
+
+
+def test_trace_program_reads_steps_and_writes_files(cpu_kernels, model_dirs, tmp_path):
+  from miniinfer_b200.engine import replay
+  d = model_dirs("A")
+  reqs = rc.make_requests(256, (20, 9), seed=2)
+  trace = rc.mixed(reqs, 128, seed=3)
+  trace.append({"step": 99, "entries": [], "end": []})
+  out = io.StringIO()
+  code = replay.main(["--model", d, "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "128",
+                      "--device", "cpu"], stdin=io.StringIO("\n".join(json.dumps(r) for r in trace) + "\n"), stdout=out)
+  assert code == 0
+  assert out.getvalue().split("\n")[:-1] == [f"done {r['step']}" for r in trace]
+  outputs = {}
+  for r in trace:
+    path = tmp_path / "o" / f"{r['step']}.f32"
+    wanted = sum(len(e["want"]) for e in r["entries"])
+    assert path.exists() == (wanted > 0)
+    if wanted:
+      outputs[r["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, 256)
+  rc.compare(rc.collect(trace, outputs), rc.reference_logits(d, reqs), 2e-5, "trace program")
+
+
+def test_generate_equals_plain_generation(cpu_kernels, model_dirs):
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  d = model_dirs("B")
+  eng = LLMEngine(d, dtype="float32", device="cpu", page_size=8, num_pages=30, max_num_seqs=4, max_model_len=128,
+                  max_num_batched_tokens=13)
+  prompts = list(rc.make_requests(512, (1, 9, 40, 71), seed=0).values())
+  w, c = plain.read_weights(d), plain.read_config(d)
+  outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+  for p, o in zip(prompts, outs):
+    assert o["token_ids"] == plain.generate(w, c, p, 6) and o["finish_reason"] == "max_tokens"
+  sp = [SamplingParams(temperature=0.8, max_tokens=5, seed=i, top_k=(0, 20)[i % 2], top_p=(1.0, 0.9)[i // 2]) for i in range(4)]
+  outs = eng.generate(prompts, sp)
+  for p, o, s in zip(prompts, outs, sp):
+    assert o["token_ids"] == plain.generate(w, c, p, 5, temperature=0.8, top_k=s.top_k, top_p=s.top_p, seed=s.seed)
+  eng.cache.check_invariants()
+  assert eng.cache.free_pages() == [30]
+
+
+def test_generation_survives_preemption(cpu_kernels, model_dirs):
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  d = model_dirs("A")
+  prompts = list(rc.make_requests(256, (20, 24, 18), seed=4).values())
+  w, c = plain.read_weights(d), plain.read_config(d)
+  eng = LLMEngine(d, dtype="float32", device="cpu", page_size=16, num_pages=5, max_num_seqs=3, max_model_len=64,
+                  max_num_batched_tokens=32)
+  outs = eng.generate(prompts, SamplingParams(temperature=0.7, max_tokens=20, seed=9))
+  assert eng.scheduler.num_preemptions >= 1
+  for p, o in zip(prompts, outs):
+    assert o["token_ids"] == plain.generate(w, c, p, 20, temperature=0.7, seed=9)
+  assert eng.cache.free_pages() == [5]
+
+
+def test_run_list_and_shared_cache(cpu_kernels, model_dirs):
+  """A layer named twice and a layer that reads another layer's cache, against the plain implementation."""
+  from miniinfer_b200.cache import KVCacheManager
+  from miniinfer_b200.config import build_model_spec, load_model_config
+  from miniinfer_b200.engine import ModelRunner, StepItem
+  from miniinfer_b200.models import LayerRun
+  from miniinfer_b200.weights import load_weights
+  d = model_dirs("B")
+  spec = build_model_spec(load_model_config(d))
+  spec.run_list = [LayerRun(0), LayerRun(1, cache_of=0), LayerRun(2), LayerRun(1)]
+  spec.__post_init__()
+  load_weights(spec, d, torch.float32, "cpu")
+  assert [s is not None for s in spec.cache_layer_specs()] == [True, False, True, True]
+  cache = KVCacheManager(spec.cache_layer_specs(), 8, 20, 2, 128, torch.float32, "cpu")
+  runner = ModelRunner(spec, cache, torch.float32, "cpu")
+  ids = rc.make_requests(512, (45,), seed=6)["r0"]
+  cache.admit("x")
+  got = torch.cat([runner.step([StepItem("x", ids[:30], range(30))]).clone(),
+                   runner.step([StepItem("x", ids[30:37], range(7))]).clone()] +
+                  [runner.step([StepItem("x", [t], [0])]).clone() for t in ids[37:]])
+  ref = plain.forward(plain.read_weights(d), plain.read_config(d), ids,
+                      run_list=[(0, None), (1, 0), (2, None), (1, None)])
+  assert (got - ref).abs().max() < 2e-5
+
+
+def test_step_refuses_bad_input(cpu_kernels, model_dirs):
+  from miniinfer_b200.cache import OutOfPages
+  from miniinfer_b200.engine import StepItem
+  r = make_runner(model_dirs("A"), 16, 64)
+  r.cache.admit("a"); r.cache.admit("b")
+  with pytest.raises(ValueError, match="vocabulary"):
+    r.runner.step([StepItem("a", [256], [0])])
+  with pytest.raises(ValueError, match="twice"):
+    r.runner.step([StepItem("a", [1], []), StepItem("a", [2], [])])
+  with pytest.raises(ValueError, match="wanted place"):
+    r.runner.step([StepItem("a", [1, 2], [2])])
+  with pytest.raises(OutOfPages):
+    r.runner.step([StepItem("a", list(range(40)), []), StepItem("b", list(range(40)), [])])
+  assert r.cache.length_of("a") == 0 and r.cache.free_pages() == [4]
+  r.cache.check_invariants()

@@ -1,0 +1,24 @@
+"""The small configurations the tests run on.  A and B differ in every size and option; C adds a
+sliding window on some layers; all have sizes that are no power of two somewhere."""
+
+TINY_A = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=64,
+  num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+  rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=128, tie_word_embeddings=True,
+  attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
+
+TINY_B = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=96,
+  num_attention_heads=8, num_key_value_heads=1, head_dim=32, intermediate_size=160, vocab_size=512,
+  rope_theta=1000000.0, rms_norm_eps=1e-5, max_position_embeddings=256, tie_word_embeddings=False,
+  attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
+
+# windowed layers beside full ones, 3 query heads per kv head, head_dim 48, vocabulary 1000
+TINY_C = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=4, hidden_size=80,
+  num_attention_heads=6, num_key_value_heads=2, head_dim=48, intermediate_size=176, vocab_size=1000,
+  rope_theta=50000.0, rms_norm_eps=1e-5, max_position_embeddings=512, tie_word_embeddings=True,
+  attention_bias=False, use_sliding_window=True, sliding_window=40, max_window_layers=2,
+  hidden_act="silu", initializer_range=0.02)
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
