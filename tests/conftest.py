@@ -15,8 +15,21 @@ def pytest_configure(config):
   config.addinivalue_line("markers", "gpu: needs a CUDA device (NVIDIA B200)")
 
 
+ON_CPU = os.environ.get("MINIINFER_TEST_DEVICE") == "cpu"
+
+
+@pytest.fixture(autouse=True)
+def _statements_in_place_of_kernels(request, monkeypatch):
+  """With MINIINFER_TEST_DEVICE=cpu the gpu tests run on the CPU against the kernels' PyTorch
+  statements: a check of the tests' own logic where no GPU is at hand, not of the kernels."""
+  if ON_CPU and "gpu" in request.keywords:
+    import torch_ops
+    torch_ops.install(monkeypatch)
+  yield
+
+
 def pytest_collection_modifyitems(config, items):
-  if torch.cuda.is_available():
+  if torch.cuda.is_available() or ON_CPU:
     return
   skip = pytest.mark.skip(reason="no CUDA device")
   for item in items:

@@ -1,0 +1,244 @@
+"""Each CUDA kernel alone against its PyTorch statement (tests/torch_ops.py), at sizes other than the
+tiny models': widths and vocabularies that are no power of two, head sizes in steps of 16, odd head
+counts and groups, small and large pages."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import torch_ops as ref
+from gpu_helpers import DEV, make_attention_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+  from miniinfer_b200.kernels import ops as o
+  o.common_lib()
+  return o
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+  g = torch.Generator().manual_seed(seed)
+  return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def test_fails_loudly_on_cpu_tensors(ops):
+  with pytest.raises(ops.KernelError, match="CUDA"):
+    ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,T", [(1000, 136, 37), (17, 1024, 3)])
+def test_embedding(ops, dtype, V, H, T):
+  table = rnd(V, H, dtype=dtype)
+  ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+  out = torch.empty(T, H, device=DEV)
+  ops.embedding(out, table, ids)
+  assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,eps", [(5, 200, 1e-5), (3, 1024, 1e-6), (2, 5120, 1e-6), (1, 7, 1e-3)])
+def test_add_rmsnorm(ops, dtype, T, H, eps):
+  w = 1 + 0.1 * rnd(H, seed=1)
+  for delta_on, rows_on, wb in ((True, False, True), (False, False, True), (True, True, False), (False, True, False)):
+    resid = rnd(T, H, seed=2)
+    delta = rnd(T, H, dtype=dtype, seed=3) if delta_on else None
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV) if rows_on else None
+    R = 2 if rows_on else T
+    out, out_ref = torch.empty(R, H, dtype=dtype, device=DEV), torch.empty(R, H, dtype=dtype, device=DEV)
+    r1, r2 = resid.clone(), resid.clone()
+    ops.add_rmsnorm(out, r1, delta, w, eps, rows, wb)
+    ref.add_rmsnorm(out_ref, r2, delta, w, eps, rows, wb)
+    assert torch.allclose(r1, r2, atol=1e-6), "residual"
+    assert torch.allclose(out.float(), out_ref.float(), atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+    if not wb:
+      assert torch.equal(r1, resid)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (33, 130, 70), (257, 100, 333), (64, 1000, 96)])
+def test_linear_float32_is_true_float32_and_row_invariant(ops, M, N, K):
+  x, w = rnd(M, K, seed=1), rnd(N, K, seed=2)
+  out = torch.empty(M, N, device=DEV)
+  ops.linear(out, x, w)
+  exact = (x.double() @ w.double().t())
+  # TF32 would err by ~1e-3 here; true fp32 stays within a few ulp of the exact sum
+  assert (out.double() - exact).abs().max() < 1e-5 * math.sqrt(K) * 4
+  one = torch.empty(1, N, device=DEV)
+  ops.linear(one, x[M // 2:M // 2 + 1].contiguous(), w)
+  assert torch.equal(one[0], out[M // 2]), "a row's value must not depend on the other rows"
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("N,K", [(24, 64), (1000, 136), (4096, 1024), (333, 2048), (8, 8)])
+def test_linear_bf16_few_rows(ops, out_dtype, N, K):
+  w = rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+  xs = rnd(64, K, dtype=torch.bfloat16, seed=1)
+  full = None
+  for M in (64, 1, 3, 8, 9, 16, 17, 33):
+    x = xs[:M].contiguous()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear(out, x, w)
+    exact = x.float() @ w.float().t()
+    err = (out.float() - exact).abs().max().item()
+    bound = (1e-4 if out_dtype == torch.float32 else 1e-2) * max(1.0, exact.abs().max().item())
+    assert err <= bound, (M, err, bound)
+    if full is None:
+      full = out
+    else:
+      assert torch.equal(out, full[:M]), "a row's value must not depend on the other rows"
+
+
+def test_linear_bf16_many_rows_and_float32_logits(ops):
+  x = rnd(200, 136, dtype=torch.bfloat16, seed=1)
+  w = rnd(1000, 136, dtype=torch.bfloat16, seed=2, scale=0.05)
+  exact = x.float() @ w.float().t()
+  out = torch.empty(200, 1000, dtype=torch.bfloat16, device=DEV)
+  ops.linear(out, x, w)
+  assert (out.float() - exact).abs().max() < 2e-2 * exact.abs().max()
+  out32 = torch.empty(200, 1000, dtype=torch.float32, device=DEV)
+  ops.linear(out32, x, w)
+  assert (out32 - exact).abs().max() < 1e-4 * max(1.0, exact.abs().max().item())
+  with pytest.raises(ops.KernelError, match="multiple of 8"):
+    ops.linear(torch.empty(2, 5, dtype=torch.bfloat16, device=DEV), rnd(2, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,P", [(6, 2, 48, 8), (4, 4, 16, 16), (16, 8, 128, 64), (3, 1, 256, 32)])
+def test_qk_norm_rope_store(ops, dtype, nh, nkv, hd, P):
+  T, pages, max_pos = 23, 9, 300
+  g = torch.Generator().manual_seed(4)
+  for norm_on, rope_on, store_on in ((True, True, True), (False, True, True), (True, False, False), (True, True, False)):
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=5)
+    qw, kw = (1 + 0.1 * rnd(hd, seed=6), 1 + 0.1 * rnd(hd, seed=7)) if norm_on else (None, None)
+    rot = hd if hd != 48 else 32                              # a partial rotation for one case
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / rot))
+    fr = torch.outer(torch.arange(max_pos).float(), inv)
+    table = torch.cat((fr.cos(), fr.sin()), -1).to(DEV) if rope_on else None
+    pos = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32).to(DEV)
+    slot = torch.randperm(pages * P, generator=g)[:T].to(torch.int32).to(DEV)
+    slot[3] = -1                                              # a padded token stores nothing
+    kv1 = torch.zeros(pages, 2, nkv, P, hd, dtype=dtype, device=DEV)
+    kv2 = kv1.clone()
+    a, b = qkv.clone(), qkv.clone()
+    ops.qk_norm_rope_store(a, qw, kw, table, pos, slot if store_on else None, kv1 if store_on else None, nh, nkv, hd, 1e-5)
+    ref.qk_norm_rope_store(b, qw, kw, table, pos, slot if store_on else None, kv2 if store_on else None, nh, nkv, hd, 1e-5)
+    t = 3e-5 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(a.float(), b.float(), atol=t, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+    assert torch.allclose(kv1.float(), kv2.float(), atol=t, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+    if store_on:
+      assert kv1.abs().sum() > 0
+
+
+CASES = [
+  # (items (ctx, new), nh, nkv, hd, page, window)
+  ([(37, 37), (9, 1), (70, 5), (130, 1)], 6, 2, 48, 8, None),
+  ([(64, 64), (65, 1), (128, 2), (1, 1)], 4, 4, 16, 16, None),
+  ([(300, 77), (257, 1), (64, 1)], 16, 8, 128, 64, None),
+  ([(200, 150), (90, 1), (41, 2), (333, 1)], 6, 2, 32, 8, 40),
+  ([(129, 129), (100, 1)], 5, 1, 64, 64, 64),
+  ([(50, 3)], 2, 1, 256, 32, None),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", range(len(CASES)))
+def test_attention_over_pages(ops, dtype, case):
+  items, nh, nkv, hd, P, window = CASES[case]
+  qkv, kv, bt, batch = make_attention_case(items, nh, nkv, hd, P, dtype, seed=case)
+  T = qkv.shape[0]
+  out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+  want = torch.empty_like(out)
+  ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  assert torch.isfinite(out.float()).all()
+  assert (out.float() - want.float()).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
+  """Random data would hide a key that is skipped: make one key's score stand out."""
+  nh, nkv, hd, P = 4, 2, 64, 16
+  for window, far in ((None, 3), (None, 257), (100, 401), (100, 400)):
+    ctx = 501
+    qkv, kv, bt, batch = make_attention_case([(ctx, 1)], nh, nkv, hd, P, dtype, seed=1)
+    slot = int(batch.seq_slot[0])
+    page, off = int(bt[slot, far // P]), far % P
+    q = qkv.float().view(1, -1, hd)
+    kv[page, 0, :, off, :] = (q[0, :nh:nh // nkv] * 4.0).to(dtype)   # aligned with the group's first head
+    kv[page, 1, :, off, :] = 7.0
+    out = torch.empty((1, nh * hd), dtype=dtype, device=DEV)
+    want = torch.empty_like(out)
+    ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, 1.0, window)
+    ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, 1.0, window)
+    assert (out.float() - want.float()).abs().max() < (1e-4 if dtype == torch.float32 else 5e-2)
+    first_head = out.float()[0, :hd]
+    visible = window is None or far > (ctx - 1) - window
+    assert (first_head.mean() > 6.0) == visible, (window, far, first_head.mean())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,I", [(7, 176), (3, 3072), (1, 5)])
+def test_silu_mul(ops, dtype, T, I):
+  gu = rnd(T, 2 * I, dtype=dtype, scale=3.0)
+  out, want = torch.empty(T, I, dtype=dtype, device=DEV), torch.empty(T, I, dtype=dtype, device=DEV)
+  ops.silu_mul(out, gu)
+  ref.silu_mul(want, gu)
+  assert torch.allclose(out.float(), want.float(), atol=1e-6 if dtype == torch.float32 else 2e-2, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+def _sample(ops, logits, temp, k, p, seed, counter):
+  R = logits.shape[0]
+  out = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+  f = lambda v, dt: torch.tensor(v, dtype=dt, device=DEV)
+  ops.sample(out, logits, f(temp, torch.float32), f(k, torch.int32), f(p, torch.float32), f(seed, torch.int64), f(counter, torch.int64))
+  return out.tolist()
+
+
+def test_sampler_greedy_and_ties(ops):
+  logits = rnd(5, 1000, seed=3)
+  logits[1, 700] = logits[1, 40] = 50.0                      # equal maxima: the lowest index wins
+  logits[2, 999] = 60.0
+  got = _sample(ops, logits, [0.0] * 5, [0] * 5, [1.0] * 5, [1] * 5, [0] * 5)
+  assert got == logits.argmax(-1).tolist() and got[1] == 40 and got[2] == 999
+
+
+@pytest.mark.parametrize("V", [1000, 151936])
+def test_sampler_draws_match_the_statement(ops, V):
+  R = 6
+  logits = rnd(R, V, seed=5, scale=2.0)
+  temp = [0.8, 1.0, 0.5, 1.3, 0.7, 0.0]
+  k = [0, 20, 0, 50, 1, 0]
+  p = [1.0, 1.0, 0.9, 0.6, 1.0, 1.0]
+  seed = [11, 12, 13, 14, 15, 16]
+  counter = [0, 5, 7, 1, 2, 3]
+  got = _sample(ops, logits, temp, k, p, seed, counter)
+  again = _sample(ops, logits, temp, k, p, seed, counter)
+  assert got == again
+  for r in range(R):
+    if temp[r] == 0:
+      assert got[r] == int(logits[r].argmax())
+      continue
+    sc = ref.gumbel_scores(logits[r], temp[r], k[r], p[r], seed[r], counter[r])
+    assert torch.isfinite(sc[got[r]]), f"row {r}: token {got[r]} is outside the kept set"
+    assert sc[got[r]] >= sc.max() - 1e-4, f"row {r}: score {sc[got[r]]} vs best {sc.max()}"
+  assert got[4] == int(logits[4].argmax())                    # top_k = 1
+  other = _sample(ops, logits, temp, k, p, seed, [c + 1 for c in counter])
+  assert other[:4] != got[:4]
+
+
+def test_sampler_follows_the_distribution(ops):
+  logits = torch.tensor([[0.1, 2.0, 1.9, -1.0, 0.5, 0.3, -2.0]], device=DEV).repeat(64, 1)
+  counts = torch.zeros(7)
+  for c in range(40):
+    for t in _sample(ops, logits, [1.0] * 64, [0] * 64, [1.0] * 64, list(range(64)), [c] * 64):
+      counts[t] += 1
+  pr = torch.softmax(logits[0].cpu(), -1)
+  assert (counts / counts.sum() - pr).abs().max() < 0.03
+  counts = torch.zeros(7)
+  for t in _sample(ops, logits, [1.0] * 64, [3] * 64, [0.7] * 64, list(range(64)), [1] * 64):
+    counts[t] += 1
+  assert counts[[0, 3, 4, 5, 6]].sum() == 0                   # top-3 then top-p 0.7 keeps tokens 1 and 2

@@ -1,0 +1,120 @@
+"""The engine on the GPU against the plain implementation, through trace replay: each request alone
+and whole; most of it in one step and the last 32 tokens one by one; in portions of changing size
+down to two tokens; mixed, up to four live requests with so few pages that they are used again; long
+decoding; the first tokens of a sequence.  In float32 and in bfloat16, on three tiny configurations."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import replay_cases as rc
+from gpu_helpers import DEV
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LENGTHS = {"A": (5, 17, 33, 100, 64, 128, 41, 65), "B": (1, 9, 40, 71, 130, 65, 256, 2), "C": (90, 33, 150, 64, 7, 300, 129)}
+PAGES = {"A": 16, "B": 8, "C": 64}
+
+# float32: the bound the engine is built for.  bfloat16: 8 bits of mantissa; activations are rounded
+# about six times per layer, the errors add like a random walk over at most four layers and the
+# logits are of order one: 5 * sqrt(24) * 2^-9 = 0.05 of the largest logit bounds what rounding can do.
+def tolerance(dtype: str, ref) -> float:
+  if dtype == "float32":
+    return 1e-4
+  return 0.05 * max(float(v.abs().max()) for v in ref.values())
+
+
+_ref_cache = {}
+
+
+def reference(model_dir, tag, reqs):
+  key = (model_dir, tuple(reqs))
+  if key not in _ref_cache:
+    _ref_cache[key] = rc.reference_logits(model_dir, reqs)
+  return _ref_cache[key]
+
+
+def runner_for(model_dir, dtype, max_tokens, page):
+  from miniinfer_b200.engine.replay import TraceRunner
+  return TraceRunner(model_dir, dtype, max_tokens, device=DEV, page_size=page)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
+  d = model_dirs(tag)
+  page = PAGES[tag]
+  reqs = rc.make_requests(ALL[tag]["vocab_size"], LENGTHS[tag], seed=5)
+  ref = reference(d, tag, reqs)
+  longest = rc.round_up(max(LENGTHS[tag]), page)
+  if cut == "mixed":
+    # room for the longest request plus a little: requests must wait for pages that others give back
+    budget = longest + 2 * rc.round_up(70, page)
+    trace = rc.mixed(reqs, budget, seed=1, granule=page)
+    assert max(len(r["entries"]) for r in trace) >= 2
+  else:
+    budget = longest
+    trace = {"whole": rc.whole, "tail": rc.tail_one_by_one, "portions": rc.portions}[cut](reqs)
+  runner = runner_for(d, dtype, budget, page)
+  got = rc.run_in_process(runner, trace)
+  margin = 1e-3 if dtype == "float32" else None
+  rc.compare(got, ref, tolerance(dtype, ref), f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
+  runner.cache.check_invariants()
+  assert runner.cache.free_pages() == [g.num_pages for g in runner.cache.paged_groups]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(model_dirs, dtype):
+  d = model_dirs("C")
+  reqs = rc.make_requests(1000, (400,), seed=8)
+  ref = reference(d, "C", reqs)
+  # the first tokens one by one from an empty cache, then on and on past several pages and the window
+  trace = rc.tail_one_by_one(reqs, tail=399)
+  runner = runner_for(d, dtype, 448, 64)
+  got = rc.run_in_process(runner, trace)
+  assert len(got) == 400
+  rc.compare(got, ref, tolerance(dtype, ref), f"C/{dtype}/decode-400")
+  first = {k: v for k, v in got.items() if k[1] < 4}
+  rc.compare(first, ref, tolerance(dtype, ref), f"C/{dtype}/first-tokens")
+
+
+def test_float32_logits_do_not_depend_on_the_cut_at_all(model_dirs):
+  """Stronger than the tolerance: the 32-bit kernels add in an order that depends on the position
+  only, so every cut gives the same bits."""
+  d = model_dirs("B")
+  reqs = rc.make_requests(512, (71, 130, 40), seed=3)
+  results = []
+  for trace, budget in ((rc.whole(reqs), 192), (rc.portions(reqs), 192), (rc.mixed(reqs, 320, seed=2, granule=8), 320)):
+    results.append(rc.run_in_process(runner_for(d, "float32", budget, 8), trace))
+  for key, row in results[1].items():
+    assert np.array_equal(row, results[0][key]), key
+  for key, row in results[2].items():
+    assert np.array_equal(row, results[0][key]), key
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, tmp_path, dtype):
+  """bin/trace_run as a user calls it: a child process, steps on standard input, files out."""
+  d = model_dirs("A")
+  reqs = rc.make_requests(256, (100, 33, 64, 17, 128), seed=7)
+  trace = rc.mixed(reqs, 256, seed=4)
+  out = tmp_path / "out"
+  proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+                         "--out", str(out), "--max-tokens", "256"],
+                        input="\n".join(json.dumps(r) for r in trace) + "\n", capture_output=True, text=True, timeout=900)
+  assert proc.returncode == 0, proc.stderr[-3000:]
+  assert proc.stdout.split() == [w for r in trace for w in ("done", str(r["step"]))]
+  outputs = {}
+  for r in trace:
+    wanted = sum(len(e["want"]) for e in r["entries"])
+    if wanted:
+      outputs[r["step"]] = np.fromfile(out / f"{r['step']}.f32", dtype="<f4").reshape(wanted, 256)
+  ref = reference(d, "A", reqs)
+  rc.compare(rc.collect(trace, outputs), ref, tolerance(dtype, ref), f"trace_run/{dtype}")
