@@ -1,0 +1,305 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of a Qwen3-0.6B-shaped model (28 layers, hidden 1024, 16 query and
+8 kv heads of 128, intermediate 3072, vocabulary 151936, tied head) in bfloat16, 8 requests with a
+2048-token context each.  A step is one decode step of the whole batch.
+
+One JSON line is printed:
+  value      decoded tokens per second of the step function with sampling (CUDA-graph replay, device
+             timing with CUDA events around K steps; every step reads weights + cache, far more than L2)
+  e2e        the same through ``LLMEngine.step`` - scheduler, pinned-host token/metadata upload, graph
+             replay, sampled tokens back to the host - timed around K engine steps
+  prefill    one whole 2048-token prompt in one step: tokens/s, ms, fraction of the bf16 tensor peak
+  roofline   bytes the decode step must read (every weight once + the cache of the live requests)
+             divided by its time, against the measured HBM copy bandwidth
+  points     decode tokens/s at batch 1 and 64
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=28, hidden_size=1024,
+             num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936,
+             rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=True)
+CONTEXT = 2048
+GENERATED = 256
+MAX_MODEL_LEN = 4096
+PREFILL_TOKENS = 2048
+PAGE = 64
+
+
+def peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      d = json.load(f)
+    return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+  return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+  FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self):
+    self.samples = []
+    self.proc = None
+    self.thread = None
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(["nvidia-smi", "--id=0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                   stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+      return
+    self.thread = threading.Thread(target=self._read, daemon=True)
+    self.thread.start()
+
+  def _read(self):
+    for line in self.proc.stdout:
+      parts = [p.strip() for p in line.split(",")]
+      if len(parts) == 6:
+        self.samples.append(parts)
+
+  def stop(self) -> dict:
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    mhz, mx, reasons = [], None, set()
+    for s in self.samples:
+      try:
+        mhz.append(float(s[0]))
+        mx = float(s[1])
+      except ValueError:
+        continue
+      for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:]):
+        if v.lower().startswith("active"):
+          reasons.add(name)
+    mhz.sort()
+    return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def model_bytes(cfg: dict, layers: int) -> dict:
+  H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+  nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+  per_layer = ((nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I) * 2 + (2 * H + 2 * hd) * 4
+  head = V * H * 2
+  return {"weights": layers * per_layer + head + H * 4, "kv_per_token": layers * 2 * nkv * hd * 2}
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+  H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+  nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+  gemm = 2.0 * T * ((nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I) * layers + 2.0 * V * H
+  attn = layers * 2.0 * 2.0 * nh * hd * (T * (T + 1) / 2)
+  return gemm + attn
+
+
+def build_engine(model_dir: str, batch: int):
+  from miniinfer_b200 import LLMEngine
+  pages = batch * (-(-(CONTEXT + GENERATED + 64) // PAGE)) + 8
+  pages = max(pages, -(-PREFILL_TOKENS // PAGE) + 8)
+  return LLMEngine(model_dir, dtype="bfloat16", device="cuda:0", load_format="random", page_size=PAGE, num_pages=pages,
+                   max_num_seqs=max(batch, 1), max_model_len=MAX_MODEL_LEN, max_num_batched_tokens=PREFILL_TOKENS, seed=0)
+
+
+def fill_context(engine, batch: int, tokens: int, seed: int):
+  """Admits `batch` requests and runs their prompts through the step function in portions."""
+  import torch
+  from miniinfer_b200.engine import StepItem
+  g = torch.Generator().manual_seed(seed)
+  V = engine.model_config.vocab_size
+  ids = []
+  for b in range(batch):
+    rid = f"bench{b}"
+    engine.cache.admit(rid)
+    prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
+    for s in range(0, tokens, PREFILL_TOKENS):
+      engine.runner.step([StepItem(rid, prompt[s:s + PREFILL_TOKENS], ())])
+    ids.append(rid)
+  torch.cuda.synchronize()
+  return ids
+
+
+def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
+  """K decode steps of the step function with sampling, through the decode CUDA graph."""
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  rids = fill_context(engine, batch, CONTEXT, seed=batch)
+  params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+  tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+  last = [1] * batch
+  n = [0]
+
+  def one():
+    extras = Sampler.pack(params, list(range(batch)), [n[0]] * batch)
+    items = [StepItem(r, [t], (0,)) for r, t in zip(rids, last)]
+    engine.runner.step_and_sample(items, extras, Sampler.sample, tokens_dev)
+    n[0] += 1
+
+  for _ in range(max(warmup, 3)):
+    one()
+  torch.cuda.synchronize()
+  start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  start.record()
+  for _ in range(steps):
+    one()
+  end.record()
+  torch.cuda.synchronize()
+  ms = start.elapsed_time(end) / steps
+  launches = engine.runner.last_launches
+  mean_ctx = CONTEXT + max(warmup, 3) + steps / 2.0
+  for r in rids:
+    engine.cache.release_request(r)
+  return {"ms": ms, "tok_s": batch * 1000.0 / ms, "launches_per_step": launches, "mean_ctx": mean_ctx}
+
+
+def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
+  """The same decode steps through the Python entry point: host tokens in, host tokens out."""
+  import torch
+  from miniinfer_b200 import SamplingParams
+  g = torch.Generator().manual_seed(100 + batch)
+  V = engine.model_config.vocab_size
+  sp = SamplingParams(temperature=0.6, max_tokens=warmup + steps + 8, ignore_eos=True)
+  for b in range(batch):
+    engine.add_request(torch.randint(0, V, (CONTEXT,), generator=g).tolist(), sp)
+  while any(r.total_len - r.num_computed != 1 for r in engine.scheduler.running) or engine.scheduler.waiting:
+    engine.step()                      # prompts, in portions under the token budget
+  for _ in range(max(warmup, 3)):
+    engine.step()
+  torch.cuda.synchronize()
+  s0 = dict(engine.stats)
+  t0 = time.perf_counter()
+  for _ in range(steps):
+    engine.step()
+  torch.cuda.synchronize()
+  dt = time.perf_counter() - t0
+  s1 = engine.stats
+  assert s1["decode_tokens"] - s0["decode_tokens"] == batch * steps, "the timed steps were not pure decode steps"
+  while engine.has_unfinished():
+    engine.step()
+  return {"tok_s": batch * steps / dt, "ms": 1000.0 * dt / steps,
+          "h2d": (s1["h2d_bytes"] - s0["h2d_bytes"]) / steps, "d2h": (s1["d2h_bytes"] - s0["d2h_bytes"]) / steps,
+          "launches": (s1["launches"] - s0["launches"]) / steps}
+
+
+def time_prefill(engine, reps: int = 5) -> dict:
+  import torch
+  from miniinfer_b200.engine import StepItem
+  g = torch.Generator().manual_seed(7)
+  V = engine.model_config.vocab_size
+  times = []
+  for i in range(reps + 2):
+    rid = f"prefill{i}"
+    engine.cache.admit(rid)
+    prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    engine.runner.step([StepItem(rid, prompt, (PREFILL_TOKENS - 1,))])
+    end.record()
+    torch.cuda.synchronize()
+    if i >= 2:
+      times.append(start.elapsed_time(end))
+    engine.cache.release_request(rid)
+  times.sort()
+  return {"ms": times[len(times) // 2]}
+
+
+def reference_arm() -> int:
+  print(json.dumps({"impl": "reference", "unavailable": (
+    "the reference installs (pip --no-deps into baseline/_ref) but cannot be imported as installed: its pyproject "
+    "places the sub-packages at top level without a 'miniinfer' package and leaves out kernels/, and its engine needs "
+    "a tokenizer and a checkpoint from the hub, which cannot be fetched offline")}))
+  return 0
+
+
+def main() -> int:
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=128)
+  ap.add_argument("--warmup", type=int, default=8)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--batch", type=int, default=8)
+  ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+  ap.add_argument("--skip-points", action="store_true")
+  args = ap.parse_args()
+  if args.impl == "reference":
+    return reference_arm()
+  if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+    print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+    return 2
+
+  import torch
+  pk = peaks()
+  cfg = dict(MODEL, num_hidden_layers=args.layers)
+  warmup = max(args.warmup, 3)
+  with tempfile.TemporaryDirectory() as d:
+    with open(os.path.join(d, "config.json"), "w") as f:
+      json.dump(cfg, f)
+    clocks = ClockSampler()
+    engine = build_engine(d, args.batch)
+    clocks.start()
+    dec = time_decode(engine, args.batch, args.steps, warmup)
+    e2e = time_e2e(engine, args.batch, args.steps, warmup)
+    pre = time_prefill(engine)
+    clock_info = clocks.stop()
+    points = {}
+    if not args.skip_points:
+      for b in (1, 64):
+        del engine
+        torch.cuda.empty_cache()
+        engine = build_engine(d, b)
+        points[f"decode_b{b}"] = round(time_decode(engine, b, args.steps, warmup)["tok_s"], 1)
+
+  mb = model_bytes(cfg, args.layers)
+  step_bytes = mb["weights"] + args.batch * dec["mean_ctx"] * mb["kv_per_token"]
+  achieved = step_bytes / (dec["ms"] * 1e-3) / 1e9
+  flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
+  line = {
+    "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, 2048-token contexts, bf16)",
+    "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+    "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+    "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids", "impl": "ours",
+    "config": {"model": "Qwen3-0.6B shape", "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
+               "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+               "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+               "tied_head": True, "global_batch": args.batch, "seq_len": CONTEXT, "generated": GENERATED,
+               "max_model_len": MAX_MODEL_LEN, "page_size": PAGE, "parallelism": "single GPU",
+               "l2": "each step reads weights+cache (>1 GB), larger than L2", "sampling": "temperature 0.6",
+               "decode_path": "CUDA graph replay"},
+    "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "ms_per_step": round(e2e["ms"], 4),
+            "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])},
+    "gpu_launches": int(dec["launches_per_step"] * args.steps),
+    "launches_per_step": int(dec["launches_per_step"]),
+    "prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre["ms"], 3),
+                "frac": round(flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+    "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                 "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+    "points": points,
+    "clocks": clock_info,
+  }
+  print(json.dumps(line))
+  return 0
+
+
+if __name__ == "__main__":
+  sys.exit(main())

@@ -35,6 +35,7 @@ class EngineConfig:
   model_path: str
   dtype: Any = torch.bfloat16
   device: str = "cuda:0"
+  load_format: str = "safetensors"         # "random": config.json only, weights drawn on the device from `seed`
   # cache
   page_size: int = 64
   num_pages: Optional[int] = None          # pages of every cache group; None: from free memory
@@ -51,6 +52,8 @@ class EngineConfig:
 
   def __post_init__(self):
     self.dtype = parse_dtype(self.dtype)
+    if self.load_format not in ("safetensors", "random"):
+      raise ValueError("load_format must be 'safetensors' or 'random'")
     if self.page_size <= 0:
       raise ValueError("page_size must be positive")
     if self.num_pages is not None and self.num_pages < 1:

@@ -21,7 +21,7 @@ from ..cache.manager import KVCacheManager
 from ..config import EngineConfig, build_model_spec, load_model_config
 from ..sampling import Sampler, SamplingParams, derive_seed
 from ..utils.logging import get_logger
-from ..weights import load_weights
+from ..weights import init_random_on_device, load_weights
 from .runner import ModelRunner, StepItem
 from .scheduler import Request, Scheduler, SchedulerOutput
 
@@ -58,8 +58,11 @@ class LLMEngine:
     self.model_config = load_model_config(cfg.model_path)
     self.spec = build_model_spec(self.model_config)
     t0 = time.time()
-    load_weights(self.spec, cfg.model_path, cfg.dtype, self.device)
-    logger.info("weights loaded in %.1f s", time.time() - t0)
+    if cfg.load_format == "random":
+      init_random_on_device(self.spec, cfg.dtype, self.device, cfg.seed)
+    else:
+      load_weights(self.spec, cfg.model_path, cfg.dtype, self.device)
+    logger.info("weights ready in %.1f s", time.time() - t0)
     cfg.max_context_len = min(cfg.max_context_len, self.model_config.max_position_embeddings)
     layer_specs = self.spec.cache_layer_specs()
     num_pages = cfg.num_pages
@@ -76,7 +79,7 @@ class LLMEngine:
     self._next_id = 0
     self._tokens_host: Optional[torch.Tensor] = None
     self._tokens_dev: Optional[torch.Tensor] = None
-    self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0}
+    self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0}
 
   # ------------------------------------------------------------------ life cycle (API parity)
 
@@ -159,13 +162,14 @@ class LLMEngine:
         sampling_reqs.append(it.request)
     extras = Sampler.pack([r.params for r in sampling_reqs], [r.seed for r in sampling_reqs],
                           [len(r.output_ids) for r in sampling_reqs]) if sampling_reqs else {}
-    logits, ctx = self.runner.step(items, extras, return_ctx=True)
     sampled: Dict[Hashable, int] = {}
     R = len(sampling_reqs)
+    dev, host = self._token_buffers(max(R, 1))
+    toks_dev = self.runner.step_and_sample(items, extras, Sampler.sample, dev, use_graphs=not self.config.enforce_eager)
+    self.stats["h2d_bytes"] += self.runner.last_h2d_bytes
+    self.stats["launches"] += self.runner.last_launches
     if R:
-      dev, host = self._token_buffers(R)
-      Sampler.sample(logits, ctx.extra, dev[:R])
-      host[:R].copy_(dev[:R], non_blocking=True)
+      host[:R].copy_(toks_dev, non_blocking=True)
       if self.device.type == "cuda":
         torch.cuda.current_stream().synchronize()
       toks = host[:R].tolist()

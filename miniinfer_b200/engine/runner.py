@@ -8,22 +8,30 @@ scheduler's loop, the Python entry point, the benchmark and the trace-replay pro
 The reference has three entry modes (EXTEND, DECODE, MIXED: miniinfer/engine/model_runner.py:123-186,
 miniinfer/scheduler/scheduler_batch.py:320-429) and returns the last row of every sequence
 (miniinfer/models/fused_qwen3.py:317-342); here there is one mode and any set of rows.
+
+Steps that hold only decode tokens can be replayed from a CUDA graph (``step_and_sample`` with
+``use_graphs``): the same forward pass, captured once per batch-size bucket with the batch padded
+by entries that read and write the dummy page (the reference captures decode at power-of-two batch
+sizes as well, miniinfer/engine/cuda_graph_runner.py:121-131,289-381).
 """
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
 from ..cache.manager import KVCacheManager, OutOfPages
+from ..kernels import ops
 from ..kernels.ops import AttentionBatch
 from ..models.spec import ModelSpec
 from .context import StepContext, Workspace
 
 PREFILL_TILE = 64   # query rows of one prefill-attention tile
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
 @dataclass
@@ -37,6 +45,60 @@ class StepItem:
 
 def _pad4(n: int) -> int:
   return (n + 3) & ~3
+
+
+class _MetaBuffers:
+  """A pinned host array and its device twin; one copy moves a whole step's description."""
+
+  def __init__(self, device: torch.device, capacity: int = 4096):
+    self.device = device
+    self.host: Optional[torch.Tensor] = None
+    self.dev: Optional[torch.Tensor] = None
+    self.copy_done = None
+    self.bytes_copied = 0
+    self._ensure(capacity)
+
+  def _ensure(self, n: int) -> None:
+    if self.host is None or self.host.numel() < n:
+      cap = max(n, 4096)
+      self.host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+      self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+
+  def upload(self, arrays: "OrderedDict[str, np.ndarray]", fixed_capacity: bool = False) -> Dict[str, Tuple[int, int]]:
+    offsets: Dict[str, Tuple[int, int]] = {}
+    total = 0
+    for name, arr in arrays.items():
+      offsets[name] = (total, len(arr))
+      total += _pad4(len(arr))
+    if fixed_capacity and total > self.host.numel():
+      raise RuntimeError("step description is larger than the captured buffers")
+    self._ensure(total)
+    if self.copy_done is not None:
+      self.copy_done.synchronize()     # the staging array may still be feeding the previous copy
+    h = self.host.numpy()
+    for name, arr in arrays.items():
+      o, n = offsets[name]
+      h[o:o + n] = arr
+    self.dev[:total].copy_(self.host[:total], non_blocking=True)
+    if self.device.type == "cuda":
+      self.copy_done = torch.cuda.Event()
+      self.copy_done.record()
+    self.bytes_copied = 4 * total
+    return offsets
+
+
+class _DecodeGraph:
+  """A captured decode step for one batch-size bucket, with buffers of its own."""
+
+  def __init__(self, bucket: int, device: torch.device):
+    self.bucket = bucket
+    self.meta = _MetaBuffers(device)
+    self.ws = Workspace(device)
+    self.graph = None
+    self.ctx: Optional[StepContext] = None
+    self.logits: Optional[torch.Tensor] = None
+    self.tokens: Optional[torch.Tensor] = None
+    self.launches = 0
 
 
 class ModelRunner:
@@ -57,23 +119,16 @@ class ModelRunner:
         self.layer_caches.append(cache.layer_cache(i, writes=True))
       else:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
-    self._meta_host: Optional[torch.Tensor] = None
-    self._meta_dev: Optional[torch.Tensor] = None
-    self._copy_done = None
+    self.meta = _MetaBuffers(self.device)
+    self._graphs: Dict[int, _DecodeGraph] = {}
+    self.last_h2d_bytes = 0
+    self.last_launches = 0
 
-  # ------------------------------------------------------------------ metadata
+  # ------------------------------------------------------------------ reserving and describing a step
 
-  def _meta_buffers(self, n: int):
-    if self._meta_host is None or self._meta_host.numel() < n:
-      cap = max(n, 4096)
-      pin = self.device.type == "cuda"
-      self._meta_host = torch.empty(cap, dtype=torch.int32, pin_memory=pin)
-      self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
-    return self._meta_host, self._meta_dev
-
-  def prepare(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
-    """Reserves cache room for the items' tokens and builds the step's device-side description
-    with one host-to-device copy."""
+  def _check_and_reserve(self, items: Sequence[StepItem]) -> List[int]:
+    """Checks the items, then makes room for their tokens in every cache group (all or nothing).
+    Returns each request's length before the step."""
     cache = self.cache
     if not items:
       raise ValueError("a step needs at least one item")
@@ -87,7 +142,6 @@ class ModelRunner:
       for w in it.want:
         if not (0 <= w < len(it.tokens)):
           raise ValueError(f"request {it.req_id!r}: wanted place {w} is outside its {len(it.tokens)} tokens")
-    # all or nothing: the pages of every group must cover the whole step
     need = [0] * len(cache.paged_groups)
     for it in items:
       for g, n in enumerate(cache.pages_needed(it.req_id, len(it.tokens))):
@@ -95,11 +149,11 @@ class ModelRunner:
     for g, n in enumerate(need):
       if n > cache.paged_groups[g].allocator.num_free:
         raise OutOfPages(f"group {g}: the step needs {n} new pages, {cache.paged_groups[g].allocator.num_free} are free")
-    ids = np.concatenate([np.asarray(it.tokens, dtype=np.int64) for it in items])
-    if ids.min() < 0 or ids.max() >= self.vocab_size:
-      raise ValueError(f"token id outside the vocabulary of {self.vocab_size}")
     starts = []
     for it in items:
+      lo, hi = min(it.tokens), max(it.tokens)
+      if lo < 0 or hi >= self.vocab_size:
+        raise ValueError(f"token id outside the vocabulary of {self.vocab_size}")
       start = cache.length_of(it.req_id)
       if start + len(it.tokens) > self.max_position:
         raise ValueError(f"request {it.req_id!r} would reach position {start + len(it.tokens)}, "
@@ -107,84 +161,74 @@ class ModelRunner:
       starts.append(start)
     for it in items:
       cache.append(it.req_id, len(it.tokens))
+    return starts
 
+  def _describe(self, items: Sequence[StepItem], starts: Sequence[int], extras: Optional[dict]
+                ) -> "OrderedDict[str, np.ndarray]":
+    """The step as int32 arrays, in the order they are laid out on the device."""
+    cache = self.cache
     B = len(items)
-    T = sum(len(it.tokens) for it in items)
-    R = sum(len(it.want) for it in items)
     G = len(cache.paged_groups)
     q_len = np.array([len(it.tokens) for it in items], dtype=np.int32)
+    T = int(q_len.sum())
     q_start = np.zeros(B, dtype=np.int32)
     q_start[1:] = np.cumsum(q_len)[:-1]
     start_np = np.array(starts, dtype=np.int32)
-    token_item = np.repeat(np.arange(B, dtype=np.int32), q_len)
-    positions = (np.arange(T, dtype=np.int32) - np.repeat(q_start, q_len) + np.repeat(start_np, q_len)).astype(np.int32)
-    seq_slot = np.array([cache.slot_of(it.req_id) for it in items], dtype=np.int32)
-    rows = np.array([q_start[b] + w for b, it in enumerate(items) for w in it.want], dtype=np.int32)
-    pre_tiles = [(b, o) for b in range(B) if q_len[b] > 1 for o in range(0, int(q_len[b]), PREFILL_TILE)]
-    dec_items = [b for b in range(B) if q_len[b] == 1]
-
-    sizes = [("ids", T), ("positions", T), ("token_item", T)]
-    sizes += [(f"slot_mapping{g}", T) for g in range(G)]
-    sizes += [("q_start", B), ("q_len", B), ("ctx_len", B), ("seq_slot", B), ("logit_rows", R),
-              ("decode_items", len(dec_items)), ("prefill_tiles", 2 * len(pre_tiles))]
-    extras = extras or {}
-    sizes += [(f"extra:{k}", len(v)) for k, v in extras.items()]
-    offsets = {}
-    total = 0
-    for name, n in sizes:
-      offsets[name] = (total, n)
-      total += _pad4(n)
-    host, dev = self._meta_buffers(total)
-    if self._copy_done is not None:
-      self._copy_done.synchronize()    # the staging buffer may still be feeding the previous copy
-    h = host.numpy()
-
-    def put(name, arr):
-      o, n = offsets[name]
-      h[o:o + n] = arr
-
-    put("ids", ids.astype(np.int32))
-    put("positions", positions)
-    put("token_item", token_item)
+    a: "OrderedDict[str, np.ndarray]" = OrderedDict()
+    a["ids"] = np.concatenate([np.asarray(it.tokens, dtype=np.int32) for it in items])
+    a["positions"] = (np.arange(T, dtype=np.int32) - np.repeat(q_start, q_len) + np.repeat(start_np, q_len)).astype(np.int32)
+    a["token_item"] = np.repeat(np.arange(B, dtype=np.int32), q_len)
     for g in range(G):
-      put(f"slot_mapping{g}", np.concatenate(
-        [cache.slot_mapping(it.req_id, g, s, len(it.tokens)) for it, s in zip(items, starts)]))
-    put("q_start", q_start)
-    put("q_len", q_len)
-    put("ctx_len", start_np + q_len)
-    put("seq_slot", seq_slot)
-    put("logit_rows", rows)
-    put("decode_items", np.array(dec_items, dtype=np.int32))
-    put("prefill_tiles", np.array(pre_tiles, dtype=np.int32).reshape(-1))
-    for k, v in extras.items():
-      put(f"extra:{k}", v)
-    dev[:total].copy_(host[:total], non_blocking=True)
-    if self.device.type == "cuda":
-      self._copy_done = torch.cuda.Event()
-      self._copy_done.record()
-    cache.sync()
+      a[f"slot_mapping{g}"] = np.concatenate(
+        [cache.slot_mapping(it.req_id, g, s, len(it.tokens)) for it, s in zip(items, starts)])
+    a["q_start"] = q_start
+    a["q_len"] = q_len
+    a["ctx_len"] = start_np + q_len
+    a["seq_slot"] = np.array([cache.slot_of(it.req_id) for it in items], dtype=np.int32)
+    a["logit_rows"] = np.array([q_start[b] + w for b, it in enumerate(items) for w in it.want], dtype=np.int32)
+    a["decode_items"] = np.array([b for b in range(B) if q_len[b] == 1], dtype=np.int32)
+    a["prefill_tiles"] = np.array([(b, o) for b in range(B) if q_len[b] > 1
+                                   for o in range(0, int(q_len[b]), PREFILL_TILE)], dtype=np.int32).reshape(-1)
+    for k, v in (extras or {}).items():
+      a[f"extra:{k}"] = np.asarray(v, dtype=np.int32)
+    return a
 
+  def _context(self, a: "OrderedDict[str, np.ndarray]", offsets: Dict[str, Tuple[int, int]], dev: torch.Tensor,
+               ws: Workspace, max_ctx_len: Optional[int] = None) -> StepContext:
     def view(name):
       o, n = offsets[name]
       return dev[o:o + n]
 
-    ctx = StepContext(self.dtype, self.device, self.ws)
-    ctx.num_tokens, ctx.num_items = T, B
+    cache = self.cache
+    G = len(cache.paged_groups)
+    ctx = StepContext(self.dtype, self.device, ws)
+    ctx.num_tokens, ctx.num_items = len(a["ids"]), len(a["q_len"])
     ctx.ids, ctx.positions, ctx.token_item = view("ids"), view("positions"), view("token_item")
     ctx.q_start, ctx.q_len, ctx.ctx_len, ctx.seq_slot = view("q_start"), view("q_len"), view("ctx_len"), view("seq_slot")
     ctx.logit_rows = view("logit_rows")
     ctx.slot_mapping = [view(f"slot_mapping{g}") for g in range(G)]
     ctx.block_tables = [g.block_table for g in cache.paged_groups]
-    ctx.host = {"q_len": q_len.tolist(), "q_start": q_start.tolist(), "start": starts,
-                "seq_slot": seq_slot.tolist(), "logit_rows": rows.tolist()}
-    ctx.extra = {k: view(f"extra:{k}") for k in extras}
+    ctx.host = {"q_len": a["q_len"].tolist(), "q_start": a["q_start"].tolist(),
+                "start": (a["ctx_len"] - a["q_len"]).tolist(), "seq_slot": a["seq_slot"].tolist(),
+                "logit_rows": a["logit_rows"].tolist()}
+    ctx.extra = {k[len("extra:"):]: view(k) for k in a if k.startswith("extra:")}
     ctx.attn = AttentionBatch(
       token_item=ctx.token_item, positions=ctx.positions, seq_slot=ctx.seq_slot, q_start=ctx.q_start,
-      q_len=ctx.q_len, ctx_len=ctx.ctx_len, num_tokens=T, num_items=B,
-      prefill_tiles=view("prefill_tiles").view(-1, 2), num_prefill_tiles=len(pre_tiles),
-      decode_items=view("decode_items"), num_decode=len(dec_items),
-      max_ctx_len=int((start_np + q_len).max()), scratch=self.ws)
+      q_len=ctx.q_len, ctx_len=ctx.ctx_len, num_tokens=ctx.num_tokens, num_items=ctx.num_items,
+      prefill_tiles=view("prefill_tiles").view(-1, 2), num_prefill_tiles=len(a["prefill_tiles"]) // 2,
+      decode_items=view("decode_items"), num_decode=len(a["decode_items"]),
+      max_ctx_len=max_ctx_len if max_ctx_len is not None else int(a["ctx_len"].max()), scratch=ws)
     return ctx
+
+  def prepare(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
+    """Reserves cache room for the items' tokens and builds the step's device-side description
+    with one host-to-device copy."""
+    starts = self._check_and_reserve(items)
+    arrays = self._describe(items, starts, extras)
+    offsets = self.meta.upload(arrays)
+    self.last_h2d_bytes = self.meta.bytes_copied
+    self.cache.sync()
+    return self._context(arrays, offsets, self.meta.dev, self.ws)
 
   # ------------------------------------------------------------------ the forward pass
 
@@ -202,15 +246,118 @@ class ModelRunner:
     x = spec.final_norm.norm_rows(resid, pending, ctx.logit_rows, ctx)
     return spec.lm_head.forward(x, ctx)
 
+  def _finish(self, items: Sequence[StepItem], ok: bool) -> None:
+    for it in items:
+      if ok:
+        self.cache.commit(it.req_id, len(it.tokens))
+      else:
+        self.cache.cancel(it.req_id, len(it.tokens))
+
   @torch.no_grad()
   def step(self, items: Sequence[StepItem], extras: Optional[dict] = None, return_ctx: bool = False):
     ctx = self.prepare(items, extras)
+    before = ops.launch_count()
     try:
       logits = self.forward(ctx)
     except BaseException:
-      for it in items:
-        self.cache.cancel(it.req_id, len(it.tokens))
+      self._finish(items, False)
       raise
-    for it in items:
-      self.cache.commit(it.req_id, len(it.tokens))
+    self._finish(items, True)
+    self.last_launches = ops.launch_count() - before
     return (logits, ctx) if return_ctx else logits
+
+  # ------------------------------------------------------------------ sampling steps, with CUDA graphs for decode
+
+  @torch.no_grad()
+  def step_and_sample(self, items: Sequence[StepItem], sampling: Dict[str, np.ndarray],
+                      sample_fn: Callable[[torch.Tensor, Dict[str, torch.Tensor], torch.Tensor], None],
+                      tokens_out: torch.Tensor, use_graphs: bool = True) -> torch.Tensor:
+    """Runs the step and samples one token for each wanted row into ``tokens_out`` (int32, device).
+    ``sampling``: packed per-row options (``Sampler.pack``).  Returns the tokens' device view.
+    A step of decode tokens only, each wanting its one row, is replayed from a CUDA graph."""
+    R = sum(len(it.want) for it in items)
+    decode_only = all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items)
+    bucket = next((b for b in GRAPH_BUCKETS if b >= len(items)), None)
+    if use_graphs and decode_only and bucket is not None and self.device.type == "cuda":
+      return self._graph_step(items, sampling, sample_fn, tokens_out, bucket)
+    logits, ctx = self.step(items, sampling, return_ctx=True)
+    if R:
+      before = ops.launch_count()
+      sample_fn(logits, ctx.extra, tokens_out[:R])
+      self.last_launches += ops.launch_count() - before
+    return tokens_out[:R]
+
+  def _padded(self, a: "OrderedDict[str, np.ndarray]", bucket: int) -> "OrderedDict[str, np.ndarray]":
+    """Fills a decode-only description up to ``bucket`` entries.  The extra entries belong to the
+    padding slot, whose block table points at the dummy page: they read one key there and write there."""
+    B = len(a["q_len"])
+    n = bucket - B
+
+    def pad(arr, value, count=n):
+      return np.concatenate([arr, np.full(count, value, dtype=np.int32)])
+
+    out: "OrderedDict[str, np.ndarray]" = OrderedDict()
+    for k, v in a.items():
+      if k in ("ids", "positions") or k.startswith("slot_mapping"):
+        out[k] = pad(v, 0)
+      elif k in ("token_item", "q_start", "logit_rows", "decode_items"):
+        out[k] = np.arange(bucket, dtype=np.int32)
+      elif k in ("q_len", "ctx_len"):
+        out[k] = pad(v, 1)
+      elif k == "seq_slot":
+        out[k] = pad(v, self.cache.pad_slot)
+      elif k == "prefill_tiles":
+        out[k] = v
+      elif k == "extra:top_p":
+        out[k] = np.concatenate([v, np.full(n, 1.0, dtype=np.float32).view(np.int32)])
+      elif k in ("extra:seed", "extra:counter"):
+        out[k] = pad(v, 0, 2 * n)   # 64-bit values, two words each
+      elif k.startswith("extra:"):
+        out[k] = pad(v, 0)          # temperature 0: the padding rows take the arg-max
+      else:
+        raise KeyError(k)
+    return out
+
+  def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int) -> torch.Tensor:
+    starts = self._check_and_reserve(items)
+    B = len(items)
+    try:
+      arrays = self._padded(self._describe(items, starts, sampling), bucket)
+      g = self._graphs.get(bucket)
+      if g is None:
+        g = self._graphs[bucket] = _DecodeGraph(bucket, self.device)
+      offsets = g.meta.upload(arrays, fixed_capacity=g.graph is not None)
+      self.last_h2d_bytes = g.meta.bytes_copied
+      self.cache.sync()
+      if g.graph is None:
+        self._capture(g, arrays, offsets, sample_fn)
+      g.graph.replay()
+      self.last_launches = g.launches
+      tokens_out[:B].copy_(g.tokens[:B], non_blocking=True)
+    except BaseException:
+      self._finish(items, False)
+      raise
+    self._finish(items, True)
+    return tokens_out[:B]
+
+  def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn) -> None:
+    # lengths up to max_model_len must be served by the captured launch: size the split-KV grid for it
+    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=self.cache.max_model_len)
+    g.tokens = torch.zeros(g.bucket, dtype=torch.int32, device=self.device)
+
+    def run():
+      g.logits = self.forward(g.ctx)
+      sample_fn(g.logits, g.ctx.extra, g.tokens)
+
+    run()                                   # sizes the workspace and configures the kernels
+    torch.cuda.current_stream().synchronize()
+    g.ws.frozen = True
+    before = ops.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+      run()
+    g.launches = ops.launch_count() - before
+    g.graph = graph
+
+  def num_graphs(self) -> int:
+    return sum(1 for g in self._graphs.values() if g.graph is not None)

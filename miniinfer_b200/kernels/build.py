@@ -138,7 +138,7 @@ def build_attention(head_dim: int) -> str:
   return build_library(f"attn_hd{head_dim}", ATTENTION_SOURCES, {"MI_HEAD_DIM": str(head_dim)})
 
 
-def build_all(head_dims: Sequence[int] = ()) -> List[str]:
+def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
   paths = [build_common()]
   for hd in head_dims:
     paths.append(build_attention(hd))

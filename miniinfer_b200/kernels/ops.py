@@ -56,9 +56,20 @@ def loaded_libraries() -> Dict[str, str]:
   return {k: v._name for k, v in _libs.items()}
 
 
-def _check(lib: ctypes.CDLL, code: int) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+  """Kernels of this package launched so far by this process (launches recorded into a CUDA graph
+  are counted once, when they are recorded)."""
+  return _launches
+
+
+def _check(lib: ctypes.CDLL, code: int, kernels: int = 1) -> None:
+  global _launches
   if code != 0:
     raise KernelError(lib.mi_last_error().decode())
+  _launches += kernels
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -203,7 +214,7 @@ class AttentionBatch:
   item indices with more than one / exactly one new token), their lengths and the largest context."""
 
   __slots__ = ("token_item", "positions", "seq_slot", "q_start", "q_len", "ctx_len", "num_tokens", "num_items",
-               "prefill_tiles", "num_prefill_tiles", "decode_items", "num_decode", "max_ctx_len", "decode_rows",
+               "prefill_tiles", "num_prefill_tiles", "decode_items", "num_decode", "max_ctx_len", "decode_chunk",
                "scratch")
 
   def __init__(self, **kw):
@@ -223,9 +234,50 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
   if kv_layer.shape[1:] != (2, num_kv_heads, page_size, head_dim):
     raise KernelError(f"attention: cache layer has shape {tuple(kv_layer.shape)}")
   win = int(window) if window else 0
+  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256:
+    _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size)
+    return
   lib = common_lib()
   _check(lib, lib.mi_attention_generic(
     _ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), _ptr(kv_layer), _ptr(block_table, torch.int32),
     block_table.shape[1], _ptr(batch.token_item, torch.int32), _ptr(batch.positions, torch.int32),
     _ptr(batch.seq_slot, torch.int32), T, num_heads, num_kv_heads, head_dim, page_size,
     ctypes.c_float(scale), win, _stream()))
+
+
+DECODE_CHUNKS = (256, 128, 64)
+
+
+def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int) -> int:
+  """Keys per block of the split-KV decode kernel: the longest chunk that still gives every SM about
+  two blocks, so that a small batch is spread over the whole GPU."""
+  for c in DECODE_CHUNKS:
+    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
+      return c
+  return DECODE_CHUNKS[-1]
+
+
+def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, win, page_size) -> None:
+  """Tensor-core kernel for the items with several new tokens, split-KV kernel for the decode items;
+  the two write disjoint rows of ``out``."""
+  lib = attention_lib(hd)
+  if batch.num_prefill_tiles:
+    _check(lib, lib.mi_attention_prefill_bf16(
+      _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+      _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
+      _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
+      nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
+  if batch.num_decode:
+    span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
+    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span)
+    max_splits = -(-span // chunk) + 1
+    n = batch.num_decode * nh * max_splits * (hd + 2)
+    if batch.scratch is not None:
+      scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
+    else:
+      scratch = torch.empty(n, dtype=torch.float32, device=qkv.device)
+    _check(lib, lib.mi_attention_decode_bf16(
+      _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+      _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
+      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), batch.num_decode, nh, nkv, page_size,
+      ctypes.c_float(scale), win, chunk, max_splits, _stream()), kernels=2)

@@ -141,18 +141,28 @@ CASES = [
   ([(200, 150), (90, 1), (41, 2), (333, 1)], 6, 2, 32, 8, 40),
   ([(129, 129), (100, 1)], 5, 1, 64, 64, 64),
   ([(50, 3)], 2, 1, 256, 32, None),
+
+
+  # more query heads per kv head than one pass of the decode kernel takes; long contexts; many splits
+  ([(2100, 1), (1000, 1), (257, 1), (2048, 1), (1, 1), (640, 1), (300, 300), (511, 2)], 24, 2, 64, 64, None),
+  ([(900, 1), (1500, 1), (77, 1)], 7, 7, 128, 16, 300),
+  ([(700, 500), (64, 64), (1200, 130)], 4, 2, 128, 64, None),
+  ([(333, 333), (100, 1)], 3, 1, 80, 8, 50),
+  ([(150, 1), (150, 150)], 2, 2, 256, 64, None),
+  ([(260, 1), (150, 150)], 8, 1, 16, 32, None),
 ]
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["float32", "bfloat16", "bfloat16-generic"])
 @pytest.mark.parametrize("case", range(len(CASES)))
-def test_attention_over_pages(ops, dtype, case):
+def test_attention_over_pages(ops, mode, case):
+  dtype = torch.float32 if mode == "float32" else torch.bfloat16
   items, nh, nkv, hd, P, window = CASES[case]
   qkv, kv, bt, batch = make_attention_case(items, nh, nkv, hd, P, dtype, seed=case)
   T = qkv.shape[0]
   out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
   want = torch.empty_like(out)
-  ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window, force_generic=mode.endswith("generic"))
   ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
   assert torch.isfinite(out.float()).all()
   assert (out.float() - want.float()).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2)
