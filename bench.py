@@ -114,7 +114,7 @@ def prefill_flops(cfg: dict, layers: int, T: int) -> float:
 
 def build_engine(model_dir: str, batch: int):
   from miniinfer_b200 import LLMEngine
-  pages = batch * (-(-(CONTEXT + GENERATED + 64) // PAGE)) + 8
+  pages = batch * (-(-(CONTEXT + GENERATED + 128) // PAGE)) + 8
   pages = max(pages, -(-PREFILL_TOKENS // PAGE) + 8)
   return LLMEngine(model_dir, dtype="bfloat16", device="cuda:0", load_format="random", page_size=PAGE, num_pages=pages,
                    max_num_seqs=max(batch, 1), max_model_len=MAX_MODEL_LEN, max_num_batched_tokens=PREFILL_TOKENS, seed=0)
@@ -178,7 +178,7 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
   from miniinfer_b200 import SamplingParams
   g = torch.Generator().manual_seed(100 + batch)
   V = engine.model_config.vocab_size
-  sp = SamplingParams(temperature=0.6, max_tokens=warmup + steps + 8, ignore_eos=True)
+  sp = SamplingParams(temperature=0.6, max_tokens=max(warmup, 3) + steps + batch + 16, ignore_eos=True)
   for b in range(batch):
     engine.add_request(torch.randint(0, V, (CONTEXT,), generator=g).tolist(), sp)
   while any(r.total_len - r.num_computed != 1 for r in engine.scheduler.running) or engine.scheduler.waiting:
