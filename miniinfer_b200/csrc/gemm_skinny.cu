@@ -77,33 +77,51 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 #pragma unroll
   for (int j = 0; j < NT; ++j) wrow[j] = w + (size_t)min(n0 + j * 8 + g, N - 1) * K;
 
+  // k-blocks are taken U at a time; the loads of the next group are issued before the products of
+  // this one, so a warp always has a whole group of 16-byte loads in flight.
+  constexpr int U = (2 * MT + NT) <= 3 ? 4 : ((2 * MT + NT) <= 6 ? 2 : 1);
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  uint4 wv[NT], wnext[NT];
-  if (kb_begin < kb_end) {
-    const int k = kb_begin * 32 + 8 * t;
+  uint4 wv[U][NT], xa[U][MT], xb[U][MT];
+  uint4 wn[U][NT], xan[U][MT], xbn[U][MT];
+
+  auto load_group = [&](int kb0, uint4 (&w_)[U][NT], uint4 (&a_)[U][MT], uint4 (&b_)[U][MT]) {
 #pragma unroll
-    for (int j = 0; j < NT; ++j) wv[j] = k < K ? ld_stream(wrow[j] + k) : zero;
-  }
-  for (int kb = kb_begin; kb < kb_end; ++kb) {
-    const int k = kb * 32 + 8 * t;
-    if (kb + 1 < kb_end) {
-      const int k2 = k + 32;
+    for (int u = 0; u < U; ++u) {
+      const int k = (kb0 + u) * 32 + 8 * t;
+      const bool in = (kb0 + u) < kb_end && k < K;
 #pragma unroll
-      for (int j = 0; j < NT; ++j) wnext[j] = k2 < K ? ld_stream(wrow[j] + k2) : zero;
-    }
+      for (int j = 0; j < NT; ++j) w_[u][j] = in ? ld_stream(wrow[j] + k) : zero;
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
-      const int ma = i * 16 + g, mb = ma + 8;
-      const uint4 xa = (ma < M && k < K) ? ld_cached(x + (size_t)ma * K + k) : zero;
-      const uint4 xb = (mb < M && k < K) ? ld_cached(x + (size_t)mb * K + k) : zero;
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        mma_bf16(acc[i][j], xa.x, xb.x, xa.y, xb.y, wv[j].x, wv[j].y);
-        mma_bf16(acc[i][j], xa.z, xb.z, xa.w, xb.w, wv[j].z, wv[j].w);
+      for (int i = 0; i < MT; ++i) {
+        const int ma = i * 16 + g, mb = ma + 8;
+        a_[u][i] = (in && ma < M) ? ld_cached(x + (size_t)ma * K + k) : zero;
+        b_[u][i] = (in && mb < M) ? ld_cached(x + (size_t)mb * K + k) : zero;
       }
     }
+  };
+
+  if (kb_begin < kb_end) load_group(kb_begin, wv, xa, xb);
+  for (int kb = kb_begin; kb < kb_end; kb += U) {
+    const bool more = kb + U < kb_end;
+    if (more) load_group(kb + U, wn, xan, xbn);
 #pragma unroll
-    for (int j = 0; j < NT; ++j) wv[j] = wnext[j];
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          mma_bf16(acc[i][j], xa[u][i].x, xb[u][i].x, xa[u][i].y, xb[u][i].y, wv[u][j].x, wv[u][j].y);
+          mma_bf16(acc[i][j], xa[u][i].z, xb[u][i].z, xa[u][i].w, xb[u][i].w, wv[u][j].z, wv[u][j].w);
+        }
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) wv[u][j] = wn[u][j];
+#pragma unroll
+        for (int i = 0; i < MT; ++i) { xa[u][i] = xan[u][i]; xb[u][i] = xbn[u][i]; }
+      }
+    }
   }
 
   // partial tiles -> shared memory; fragment element c of (i, j): row i*16 + g + 8*(c/2), col j*8 + 2t + (c&1)

@@ -38,6 +38,55 @@ __global__ void add_rmsnorm_kernel(TOut* __restrict__ out, float* __restrict__ r
   }
 }
 
+// The serving case in 16-byte steps: bf16 output and delta, H a multiple of 4, a row kept in
+// registers between the two passes (up to 4 * 256 * VPT values).
+template <int VPT>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ resid,
+                            const __nv_bfloat16* __restrict__ delta, const float* __restrict__ w,
+                            const int* __restrict__ rows, int H, float eps, int write_back) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int row = rows ? rows[r] : r;
+  float4* x = reinterpret_cast<float4*>(resid + (size_t)row * H);
+  const uint2* d = delta ? reinterpret_cast<const uint2*>(delta + (size_t)row * H) : nullptr;
+  const int H4 = H / 4;
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) {
+      v[i] = x[h];
+      if (d) {
+        const uint2 raw = d[h];
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[i].x += a.x; v[i].y += a.y; v[i].z += b.x; v[i].w += b.y;
+        if (write_back) x[h] = v[i];
+      }
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+  }
+  const float total = mi::block_sum(ss, scratch);
+  const float rstd = rsqrtf(total / (float)H + eps);
+  uint2* o = reinterpret_cast<uint2*>(out + (size_t)r * H);
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) {
+      const float4 ww = w4[h];
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(ww.x * (v[i].x * rstd), ww.y * (v[i].y * rstd));
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(ww.z * (v[i].z * rstd), ww.w * (v[i].w * rstd));
+      uint2 packed;
+      packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+      o[h] = packed;
+    }
+  }
+}
+
 }  // namespace
 
 MI_API int mi_add_rmsnorm(void* out, int out_dtype, float* resid, const void* delta, int delta_dtype,
@@ -47,6 +96,20 @@ MI_API int mi_add_rmsnorm(void* out, int out_dtype, float* resid, const void* de
   MI_REQUIRE(eps > 0.f, "rmsnorm: eps must be positive");
   if (R == 0) return 0;
   const int threads = 256;  // fixed: the order of the reduction must not depend on the batch
+  const bool aligned = ((uintptr_t)out % 8) == 0 && ((uintptr_t)resid % 16) == 0 && ((uintptr_t)delta % 8) == 0 && ((uintptr_t)w % 16) == 0;
+  if (out_dtype == MI_BF16 && (delta == nullptr || delta_dtype == MI_BF16) && H % 4 == 0 && H <= 8192 && aligned) {
+    const int vpt = (H / 4 + 255) / 256;
+    if (vpt <= 1)
+      add_rmsnorm_bf16_vec_kernel<1><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+    else if (vpt <= 2)
+      add_rmsnorm_bf16_vec_kernel<2><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+    else if (vpt <= 4)
+      add_rmsnorm_bf16_vec_kernel<4><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+    else
+      add_rmsnorm_bf16_vec_kernel<8><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+    MI_LAUNCH_OK("add_rmsnorm");
+    return 0;
+  }
 #define MI_NORM_LAUNCH(TO, TD) \
   add_rmsnorm_kernel<TO, TD><<<R, threads, 0, stream>>>((TO*)out, resid, (const TD*)delta, w, rows, H, eps, write_back)
   if (out_dtype == MI_BF16 && delta_dtype == MI_BF16) MI_NORM_LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -27,13 +27,15 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, co
   const int tkn = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nh + 2 * nkv;
+  const int h = blockIdx.y * WARPS + warp;     // one warp per (token, head)
+  if (h >= heads) return;
   T* row = qkv + (size_t)tkn * heads * hd;
   const int pos = positions[tkn];
   const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
   const int half = rotary_dim / 2;
   const float* cs = cos_sin ? cos_sin + (size_t)pos * rotary_dim : nullptr;
 
-  for (int h = warp; h < heads; h += WARPS) {
+  {
     T* x = row + (size_t)h * hd;
     const bool is_q = h < nh;
     const bool is_k = !is_q && h < nh + nkv;
@@ -46,7 +48,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, co
     if (!is_q && !is_k) {  // v: copy to the cache
       if (dst)
         for (int d = lane; d < hd; d += 32) dst[d] = x[d];
-      continue;
+      return;
     }
     const float* w = is_q ? q_w : k_w;
     float ss = 0.f;
@@ -74,7 +76,90 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, co
       x[d] = r;
       if (dst) dst[d] = r;
     }
-    __syncwarp();
+  }
+}
+
+// The common case in one pass over registers: bf16, the whole head rotated, head_dim a multiple of
+// 128 (so that a lane's partner elements d and d + head_dim/2 are its own).  A lane holds pairs of
+// neighbouring elements (32-bit loads and stores).
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                               const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                               const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ kv_layer, int nh, int nkv,
+                               int page_size, float eps) {
+  constexpr int HALF = HD / 2;
+  constexpr int NP = HALF / 64;                 // bf16 pairs per lane in each half
+  const int tkn = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nh + 2 * nkv;
+  const int h = blockIdx.y * WARPS + warp;
+  if (h >= heads) return;
+  __nv_bfloat16* x = qkv + ((size_t)tkn * heads + h) * HD;
+  const bool is_q = h < nh;
+  const bool is_k = !is_q && h < nh + nkv;
+  const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
+  __nv_bfloat16* dst = nullptr;
+  if (!is_q && slot >= 0) {
+    const int page = slot / page_size, off = slot % page_size;
+    dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD;
+  }
+  uint32_t raw[2][NP];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    raw[0][i] = *reinterpret_cast<const uint32_t*>(x + 64 * i + 2 * lane);
+    raw[1][i] = *reinterpret_cast<const uint32_t*>(x + HALF + 64 * i + 2 * lane);
+  }
+  if (!is_q && !is_k) {
+    if (dst) {
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        *reinterpret_cast<uint32_t*>(dst + 64 * i + 2 * lane) = raw[0][i];
+        *reinterpret_cast<uint32_t*>(dst + HALF + 64 * i + 2 * lane) = raw[1][i];
+      }
+    }
+    return;
+  }
+  const float* w = is_q ? q_w : k_w;
+  const float* cs = cos_sin ? cos_sin + (size_t)positions[tkn] * HD : nullptr;
+  float2 v[2][NP];
+  float ss = 0.f;
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      v[hf][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[hf][i]));
+      ss += v[hf][i].x * v[hf][i].x + v[hf][i].y * v[hf][i].y;
+    }
+  float rstd = 1.f;
+  if (w) {
+    ss = mi::warp_sum(ss);
+    rstd = rsqrtf(ss / (float)HD + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int j = 64 * i + 2 * lane;                  // index in the first half
+    float2 a = v[0][i], b = v[1][i];
+    if (w) {
+      const float2 wa = *reinterpret_cast<const float2*>(w + j), wb = *reinterpret_cast<const float2*>(w + HALF + j);
+      a.x *= rstd * wa.x; a.y *= rstd * wa.y;
+      b.x *= rstd * wb.x; b.y *= rstd * wb.y;
+    }
+    if (cs) {
+      const float2 c = *reinterpret_cast<const float2*>(cs + j), s = *reinterpret_cast<const float2*>(cs + HALF + j);
+      const float2 ra = make_float2(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
+      const float2 rb = make_float2(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+      a = ra; b = rb;
+    }
+    const __nv_bfloat162 oa = __floats2bfloat162_rn(a.x, a.y), ob = __floats2bfloat162_rn(b.x, b.y);
+    const uint32_t ua = *reinterpret_cast<const uint32_t*>(&oa), ub = *reinterpret_cast<const uint32_t*>(&ob);
+    *reinterpret_cast<uint32_t*>(x + j) = ua;
+    *reinterpret_cast<uint32_t*>(x + HALF + j) = ub;
+    if (dst) {
+      *reinterpret_cast<uint32_t*>(dst + j) = ua;
+      *reinterpret_cast<uint32_t*>(dst + HALF + j) = ub;
+    }
   }
 }
 
@@ -89,11 +174,24 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
              "qk_norm_rope: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, hd);
   MI_REQUIRE(!kv_layer || page_size > 0, "qk_norm_rope: page_size must be positive");
   if (T == 0) return 0;
+  const dim3 grid(T, (nh + 2 * nkv + WARPS - 1) / WARPS);
+  MI_REQUIRE(grid.y <= 65535, "qk_norm_rope: too many heads for one launch");
+  const bool whole = !cos_sin || rotary_dim == hd;
+  if (dtype == MI_BF16 && whole && (hd == 128 || hd == 256)) {
+    if (hd == 128)
+      qk_norm_rope_store_fast_kernel<128><<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+                                                                           slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
+    else
+      qk_norm_rope_store_fast_kernel<256><<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+                                                                           slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
+    MI_LAUNCH_OK("qk_norm_rope_store");
+    return 0;
+  }
   if (dtype == MI_BF16)
-    qk_norm_rope_store_kernel<<<T, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+    qk_norm_rope_store_kernel<<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, hd, page_size, eps);
   else if (dtype == MI_F32)
-    qk_norm_rope_store_kernel<<<T, WARPS * 32, 0, stream>>>((float*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+    qk_norm_rope_store_kernel<<<grid, WARPS * 32, 0, stream>>>((float*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
                                                            slot_mapping, (float*)kv_layer, nh, nkv, hd, page_size, eps);
   else
     return mi_fail("qk_norm_rope: unknown dtype %d", dtype);

@@ -15,6 +15,11 @@
 // of z: counts per bin for top-k, probability mass per bin for top-p.  Mass is held as 64-bit
 // fixed point (exp(z - max) * 2^40, integer adds), so the walk does not depend on the order in
 // which threads add.  Entries equal to a threshold are all kept.
+//
+// Two launches: (1) one block per row finds the row's threshold (rows without top-k/top-p leave at
+// once); (2) the vocabulary of each row is cut into slices, one block per (slice, row) finds the
+// slice's best perturbed score, and the last block of a row to finish picks the row's best.  The
+// arg-max with its lowest-index rule is associative, so the slicing does not change the result.
 #include "common.cuh"
 
 namespace {
@@ -77,10 +82,11 @@ __device__ Best block_argmax(Best mine, Best* scratch /* 32 */) {
   return scratch[0];
 }
 
+// Launch 1: thresholds.  thr[row] = smallest ordered image that is kept (0: everything).
 __global__ void __launch_bounds__(THREADS)
-sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ temperature,
-              const int* __restrict__ top_k, const float* __restrict__ top_p, const long long* __restrict__ seed,
-              const long long* __restrict__ counter, int V) {
+sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict__ logits,
+                        const float* __restrict__ temperature, const int* __restrict__ top_k,
+                        const float* __restrict__ top_p, int V) {
   __shared__ Best best_scratch[32];
   __shared__ unsigned int count_hist[256];
   __shared__ unsigned long long mass_hist[256];
@@ -91,20 +97,16 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const flo
   const int row = blockIdx.x;
   const float* x = logits + (size_t)row * V;
   const float temp = temperature[row];
-
-  if (!(temp > 0.f)) {
-    Best b{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += THREADS) b = better(b, Best{x[i], i});
-    b = block_argmax(b, best_scratch);
-    if (threadIdx.x == 0) out[row] = b.i < V ? b.i : 0;
-    return;
-  }
-
   const int k = top_k[row];
   const float p = top_p[row];
+  const bool use_k = k > 0 && k < V, use_p = p < 1.f;
+  if (!(temp > 0.f) || (!use_k && !use_p)) {
+    if (threadIdx.x == 0) thr_out[row] = 0u;
+    return;
+  }
   uint32_t thr_k = 0u, thr_p = 0u;  // keep entries whose ordered image is >= both
 
-  if (k > 0 && k < V) {
+  if (use_k) {
     // the k-th largest z: walk the bits from the top, keeping the rank still wanted
     if (threadIdx.x == 0) { sh_prefix = 0u; sh_rank = (unsigned)k; }
     for (int pass = 0; pass < 4; ++pass) {
@@ -134,7 +136,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const flo
     __syncthreads();
   }
 
-  if (p < 1.f) {
+  if (use_p) {
     // max of the kept entries, then their total mass in fixed point
     float mx = -INFINITY;
     for (int i = threadIdx.x; i < V; i += THREADS) {
@@ -179,29 +181,93 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const flo
       __syncthreads();
     }
     thr_p = sh_prefix;
-    __syncthreads();
   }
+  if (threadIdx.x == 0) thr_out[row] = thr_k > thr_p ? thr_k : thr_p;
+}
 
-  const uint32_t thr = thr_k > thr_p ? thr_k : thr_p;
-  const uint64_t key = mix64((uint64_t)seed[row] ^ mix64((uint64_t)counter[row] + 0x9E3779B97F4A7C15ull));
+constexpr int PICK_THREADS = 256;
+
+// Launch 2: best perturbed score of each slice; the last block of a row picks the row's best.
+__global__ void __launch_bounds__(PICK_THREADS)
+sample_pick_kernel(int* __restrict__ out, const float* __restrict__ logits, const float* __restrict__ temperature,
+                   const long long* __restrict__ seed, const long long* __restrict__ counter,
+                   const uint32_t* __restrict__ thr_in, float* __restrict__ part_v, int* __restrict__ part_i,
+                   int* __restrict__ arrivals, int V, int slices, int slice_len) {
+  __shared__ Best scratch[PICK_THREADS / 32];
+  __shared__ int s_last;
+  const int row = blockIdx.y, slice = blockIdx.x;
+  const float* x = logits + (size_t)row * V;
+  const float temp = temperature[row];
+  const int begin = slice * slice_len, end = min(V, begin + slice_len);
   Best b{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += THREADS) {
-    const float z = x[i] / temp;
-    if (ordered(z) < thr || !(z > -INFINITY)) continue;
-    const float u = uniform_for(key, i);
-    b = better(b, Best{z - logf(-logf(u)), i});
+  if (!(temp > 0.f)) {
+    for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) b = better(b, Best{x[i], i});
+  } else {
+    const uint32_t thr = thr_in[row];
+    const uint64_t key = mix64((uint64_t)seed[row] ^ mix64((uint64_t)counter[row] + 0x9E3779B97F4A7C15ull));
+    for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) {
+      const float z = x[i] / temp;
+      if (ordered(z) < thr || !(z > -INFINITY)) continue;
+      const float u = uniform_for(key, i);
+      b = better(b, Best{z - logf(-logf(u)), i});
+    }
   }
-  b = block_argmax(b, best_scratch);
-  if (threadIdx.x == 0) out[row] = b.i < V ? b.i : 0;
+  // block arg-max
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+    b = better(b, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) scratch[warp] = b;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < PICK_THREADS / 32; ++w) b = better(b, scratch[w]);
+    part_v[(size_t)row * slices + slice] = b.v;
+    part_i[(size_t)row * slices + slice] = b.i;
+    __threadfence();
+    const int prev = atomicAdd(&arrivals[row], 1);
+    s_last = prev == slices - 1;
+    if (s_last) arrivals[row] = 0;     // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last || warp != 0) return;
+  __threadfence();
+  Best r{-INFINITY, 0x7fffffff};
+  for (int s = lane; s < slices; s += 32)
+    r = better(r, Best{__ldcg(part_v + (size_t)row * slices + s), __ldcg(part_i + (size_t)row * slices + s)});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.v = __shfl_xor_sync(0xffffffffu, r.v, o);
+    other.i = __shfl_xor_sync(0xffffffffu, r.i, o);
+    r = better(r, other);
+  }
+  if (lane == 0) out[row] = r.i < V ? r.i : 0;
 }
 
 }  // namespace
 
+// Scratch: `scratch_words` 32-bit words laid out as thr[R], part_v[R * slices], part_i[R * slices];
+// `arrivals[R]` must be zero before the first launch (the kernel leaves it zero).
+MI_API int mi_sample_scratch_words(int R, int slices) { return R + 2 * R * slices; }
+
 MI_API int mi_sample(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
-                     const long long* seed, const long long* counter, int R, int V, cudaStream_t stream) {
+                     const long long* seed, const long long* counter, void* scratch, int* arrivals, int R, int V,
+                     int slices, cudaStream_t stream) {
   MI_REQUIRE(R >= 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
+  MI_REQUIRE(slices >= 1 && slices <= 65535 && R <= 65535, "sample: bad slicing R=%d slices=%d", R, slices);
   if (R == 0) return 0;
-  sample_kernel<<<R, THREADS, 0, stream>>>(out, logits, temperature, top_k, top_p, seed, counter, V);
-  MI_LAUNCH_OK("sample");
+  uint32_t* thr = (uint32_t*)scratch;
+  float* part_v = (float*)scratch + R;
+  int* part_i = (int*)scratch + R + (size_t)R * slices;
+  sample_threshold_kernel<<<R, THREADS, 0, stream>>>(thr, logits, temperature, top_k, top_p, V);
+  MI_LAUNCH_OK("sample thresholds");
+  const int slice_len = (V + slices - 1) / slices;
+  sample_pick_kernel<<<dim3(slices, R), PICK_THREADS, 0, stream>>>(out, logits, temperature, seed, counter, thr, part_v,
+                                                                  part_i, arrivals, V, slices, slice_len);
+  MI_LAUNCH_OK("sample pick");
   return 0;
 }

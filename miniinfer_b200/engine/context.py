@@ -34,6 +34,18 @@ class Workspace:
       self._bufs[key] = buf
     return buf[:n].view(*shape)
 
+  def zeros(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+    """A buffer that starts at zero and is left to its users afterwards (counters that kernels reset
+    themselves, status words)."""
+    key = (name, dtype)
+    buf = self._bufs.get(key)
+    if buf is None or buf.numel() < n:
+      if self.frozen:
+        raise RuntimeError(f"workspace buffer {name!r} would have to grow to {n} elements while frozen")
+      buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+      self._bufs[key] = buf
+    return buf[:n]
+
   def bytes(self) -> int:
     return sum(b.numel() * b.element_size() for b in self._bufs.values())
 

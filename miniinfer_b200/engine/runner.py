@@ -270,7 +270,7 @@ class ModelRunner:
 
   @torch.no_grad()
   def step_and_sample(self, items: Sequence[StepItem], sampling: Dict[str, np.ndarray],
-                      sample_fn: Callable[[torch.Tensor, Dict[str, torch.Tensor], torch.Tensor], None],
+                      sample_fn: Callable[..., None],
                       tokens_out: torch.Tensor, use_graphs: bool = True) -> torch.Tensor:
     """Runs the step and samples one token for each wanted row into ``tokens_out`` (int32, device).
     ``sampling``: packed per-row options (``Sampler.pack``).  Returns the tokens' device view.
@@ -283,7 +283,7 @@ class ModelRunner:
     logits, ctx = self.step(items, sampling, return_ctx=True)
     if R:
       before = ops.launch_count()
-      sample_fn(logits, ctx.extra, tokens_out[:R])
+      sample_fn(logits, ctx.extra, tokens_out[:R], self.ws)
       self.last_launches += ops.launch_count() - before
     return tokens_out[:R]
 
@@ -347,7 +347,7 @@ class ModelRunner:
 
     def run():
       g.logits = self.forward(g.ctx)
-      sample_fn(g.logits, g.ctx.extra, g.tokens)
+      sample_fn(g.logits, g.ctx.extra, g.tokens, g.ws)
 
     run()                                   # sizes the workspace and configures the kernels
     torch.cuda.current_stream().synchronize()

@@ -192,16 +192,28 @@ def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
 
 
 def sample(out: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor) -> None:
-  """One token per row of float32 logits; see ``sampling/sampler.py`` for the rule."""
+           top_p: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor, workspace=None) -> None:
+  """One token per row of float32 logits; see ``sampling/sampler.py`` for the rule.  ``workspace``
+  (a ``Workspace``) lends the scratch for the per-slice results; without it scratch is allocated."""
   lib = common_lib()
   R, V = logits.shape
   for t in (out, temperature, top_k, top_p, seed, counter):
     if t.shape[0] != R:
       raise KernelError("sample: per-row arguments differ in length")
+  if R == 0:
+    return
+  slices = max(1, min(64, 296 // R, -(-V // 1024)))
+  words = R + 2 * R * slices
+  if workspace is not None:
+    scratch = workspace.buffer("sample_partials", (words,), torch.int32)
+    arrivals = workspace.zeros("sample_arrivals", R, torch.int32)
+  else:
+    scratch = torch.empty(words, dtype=torch.int32, device=logits.device)
+    arrivals = torch.zeros(R, dtype=torch.int32, device=logits.device)
   _check(lib, lib.mi_sample(_ptr(out, torch.int32), _ptr(logits, torch.float32), _ptr(temperature, torch.float32),
                             _ptr(top_k, torch.int32), _ptr(top_p, torch.float32), _ptr(seed, torch.int64),
-                            _ptr(counter, torch.int64), R, V, _stream()))
+                            _ptr(counter, torch.int64), _ptr(scratch), _ptr(arrivals, torch.int32), R, V, slices,
+                            _stream()), kernels=2)
 
 
 class AttentionBatch:
@@ -245,13 +257,16 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     ctypes.c_float(scale), win, _stream()))
 
 
-DECODE_CHUNKS = (256, 128, 64)
+DECODE_CHUNKS = (128, 64, 32)
 
 
-def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int) -> int:
+def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
   """Keys per block of the split-KV decode kernel: the longest chunk that still gives every SM about
-  two blocks, so that a small batch is spread over the whole GPU."""
+  two blocks, so that a small batch is spread over the whole GPU.  Large heads take shorter chunks
+  (K and V of a chunk sit in shared memory)."""
   for c in DECODE_CHUNKS:
+    if c * head_dim > 128 * 128:
+      continue
     if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
       return c
   return DECODE_CHUNKS[-1]
@@ -269,15 +284,26 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
-    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span)
+    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
     max_splits = -(-span // chunk) + 1
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
       scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
+      counters = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv + 1, torch.int32)
     else:
       scratch = torch.empty(n, dtype=torch.float32, device=qkv.device)
+      counters = torch.zeros(batch.num_decode * nkv + 1, dtype=torch.int32, device=qkv.device)
     _check(lib, lib.mi_attention_decode_bf16(
       _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
       _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
-      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), batch.num_decode, nh, nkv, page_size,
-      ctypes.c_float(scale), win, chunk, max_splits, _stream()), kernels=2)
+      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32), _ptr(counters[:1], torch.int32),
+      batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _stream()))
+    if batch.scratch is None:
+      if int(counters[0]) != 0:
+        raise KernelError("attention_decode: a bounded wait on the copy barrier ran out")
+
+
+def device_status(ws) -> int:
+  """The status word that kernels with bounded waits set when a wait ran out (0: all well)."""
+  buf = ws._bufs.get(("attention_decode_counters", torch.int32))
+  return int(buf[0]) if buf is not None else 0

@@ -46,8 +46,10 @@ class Sampler:
     }
 
   @staticmethod
-  def sample(logits: torch.Tensor, extra: Dict[str, torch.Tensor], out: torch.Tensor) -> torch.Tensor:
-    """``extra``: the device views of what ``pack`` made; ``out``: int32 [rows]."""
+  def sample(logits: torch.Tensor, extra: Dict[str, torch.Tensor], out: torch.Tensor, workspace=None) -> torch.Tensor:
+    """``extra``: the device views of what ``pack`` made; ``out``: int32 [rows]; ``workspace`` lends
+    the kernel's scratch (needed when the call is captured in a CUDA graph)."""
     ops.sample(out, logits, extra["temperature"].view(torch.float32), extra["top_k"],
-               extra["top_p"].view(torch.float32), extra["seed"].view(torch.int64), extra["counter"].view(torch.int64))
+               extra["top_p"].view(torch.float32), extra["seed"].view(torch.int64), extra["counter"].view(torch.int64),
+               workspace)
     return out

@@ -138,7 +138,7 @@ def gumbel_scores(logits_row, temperature, top_k, top_p, seed, counter):
   return z - torch.log(-torch.log(u))
 
 
-def sample(out, logits, temperature, top_k, top_p, seed, counter):
+def sample(out, logits, temperature, top_k, top_p, seed, counter, workspace=None):
   R = logits.shape[0]
   for r in range(R):
     t = float(temperature[r])
