@@ -224,6 +224,44 @@ def time_prefill(engine, reps: int = 5) -> dict:
   return {"ms": times[len(times) // 2]}
 
 
+def kernel_table(engine, batch: int, steps: int = 6) -> str:
+  """Device time of every kernel of a decode step, from the CUPTI records of a few graph replays."""
+  import torch
+  from torch.profiler import ProfilerActivity, profile
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  rids = fill_context(engine, batch, CONTEXT, seed=batch)
+  params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+  tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+  def one(i):
+    extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+    engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev)
+
+  for i in range(4):
+    one(i)
+  torch.cuda.synchronize()
+  with profile(activities=[ProfilerActivity.CUDA]) as prof:
+    for i in range(steps):
+      one(10 + i)
+    torch.cuda.synchronize()
+  for r in rids:
+    engine.cache.release_request(r)
+  rows = []
+  total = 0.0
+  for ev in prof.key_averages():
+    t = getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0)
+    if t <= 0:
+      continue
+    rows.append((t / steps, ev.count / steps, ev.key))
+    total += t / steps
+  rows.sort(reverse=True)
+  lines = [f"decode step, batch {batch}: {total:.1f} us of kernels per step"]
+  for t, c, name in rows[:24]:
+    lines.append(f"{t:9.1f} us/step  {c:6.1f} launches/step  {t / max(c, 1e-9):7.2f} us each  {name[:110]}")
+  return "\n".join(lines)
+
+
 def reference_arm() -> int:
   print(json.dumps({"impl": "reference", "unavailable": (
     "the reference installs (pip --no-deps into baseline/_ref) but cannot be imported as installed: its pyproject "
@@ -241,6 +279,7 @@ def main() -> int:
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
   ap.add_argument("--skip-points", action="store_true")
+  ap.add_argument("--kernel-table", action="store_true", help="print the device time of each kernel of a decode step and exit")
   args = ap.parse_args()
   if args.impl == "reference":
     return reference_arm()
@@ -255,6 +294,9 @@ def main() -> int:
   with tempfile.TemporaryDirectory() as d:
     with open(os.path.join(d, "config.json"), "w") as f:
       json.dump(cfg, f)
+    if args.kernel_table:
+      print(kernel_table(build_engine(d, args.batch), args.batch))
+      return 0
     clocks = ClockSampler()
     engine = build_engine(d, args.batch)
     clocks.start()

@@ -9,7 +9,8 @@
 // instructions; several blocks per SM keep the memory system full.  Then, from shared memory:
 //   1. scores: lanes share a key 8 elements (16 bytes) each, dot with all query heads of this kv
 //      head (held in registers), reduce across the lanes of the key;
-//   2. softmax statistics of the chunk in float32 (max, exp, sum);
+//   2. softmax statistics in float32, first per warp over the warp's own keys (no block barrier),
+//      merged across the four warps at the end;
 //   3. values (behind their own mbarrier, so they stream in while 1 and 2 run): the same lane
 //      layout accumulates p * V in float32; partial sums are reduced by shuffles, then across warps.
 // Each (request, head, chunk) writes an unnormalised partial output with its max and sum to scratch
@@ -105,12 +106,11 @@ decode_split_kernel(DecodeArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [chunk][HD]
   __nv_bfloat16* v_s = k_s + (size_t)a.chunk * HD;                            // [chunk][HD]
-  float* s_scores = reinterpret_cast<float*>(v_s + (size_t)a.chunk * HD);     // [GT][chunk]
-  float* s_red = s_scores + GT * a.chunk;                                     // [WARPS][GT][HD]
-  float* s_stat = s_red + WARPS * GT * HD;                                    // [WARPS][GT]
-  float* s_m = s_stat + WARPS * GT;                                           // [GT]
-  float* s_l = s_m + GT;                                                      // [GT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_l + GT);   // [2]; the float count before it is even, so 8-byte aligned
+  float* s_scores = reinterpret_cast<float*>(v_s + (size_t)a.chunk * HD);     // [WARPS][GT][chunk / WARPS]: a warp's own keys
+  const int chunk64 = (a.chunk + 63) / 64 * 64;                               // room for every warp's keys at any head size
+  float* s_red = s_scores + GT * chunk64;                                     // [WARPS][GT][HD]
+  float* s_stat = s_red + WARPS * GT * HD;                                    // [WARPS][GT][2]: max, sum
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_stat + WARPS * GT * 2);      // [2]; the float count before it is even
   __shared__ int s_last;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -133,6 +133,7 @@ decode_split_kernel(DecodeArgs a) {
   const size_t page_elems = (size_t)2 * a.nkv * a.page_size * HD;
   const size_t head_off = (size_t)kvh * a.page_size * HD;
   const size_t v_off = (size_t)a.nkv * a.page_size * HD;
+  const float scale2 = a.scale * 1.4426950408889634f;      // scores are kept in the base-2 domain
 
   // ---- ask for the chunk's K and V: one bulk copy per page piece, each counted on its barrier
   if (threadIdx.x == 0) {
@@ -158,6 +159,12 @@ decode_split_kernel(DecodeArgs a) {
     }
   }
 
+  // A warp's keys are jj = it * (WARPS * KPW) + warp * KPW + ks; its own index for them is it * KPW + ks.
+  const int per_warp = chunk64 / WARPS;                    // at least the most keys a warp can have
+  float* my_scores = s_scores + (size_t)warp * GT * per_warp;
+  int my_n = 0;                                            // keys of this warp: same for all its lanes
+  for (int base = 0; base < n; base += WARPS * KPW) my_n += min(KPW, max(0, n - base - warp * KPW));
+
   bool ok = mbar_wait(&bars[0], 0);
   if (__syncthreads_or(!ok)) {
     if (threadIdx.x == 0) atomicExch(a.status, 1);
@@ -178,11 +185,11 @@ decode_split_kernel(DecodeArgs a) {
         for (int i = 0; i < VEC; ++i) q[g][i] = 0.f;
       }
     }
-    // 1. scores.  The loop bound is the same for every lane of the block (the shuffles need whole
+    // 1. scores of the warp's keys.  The loop bound is the same for every lane (the shuffles need whole
     // warps); lanes whose key is past the end carry zeros.
 #pragma unroll 2
-    for (int base = 0; base < n; base += WARPS * KPW) {
-      const int jj = base + warp * KPW + ks;
+    for (int it = 0; it * (WARPS * KPW) < n; ++it) {
+      const int jj = it * (WARPS * KPW) + warp * KPW + ks;
       const bool has_key = jj < n;
       float kf[VEC];
       if (active && has_key) {
@@ -198,45 +205,28 @@ decode_split_kernel(DecodeArgs a) {
         for (int i = 0; i < VEC; ++i) s = fmaf(q[g][i], kf[i], s);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (dl == 0 && has_key) s_scores[g * a.chunk + jj] = s * a.scale;
+        if (dl == 0 && has_key) my_scores[g * per_warp + it * KPW + ks] = s * scale2;
       }
     }
-    __syncthreads();
-    // 2. max and sum of exp per head
+    __syncwarp();
+    // 2. the warp's own max and sum of exp2 per head
+    float m_w[GT], l_w[GT];
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
       float mx = -INFINITY;
-      for (int jj = threadIdx.x; jj < n; jj += WARPS * 32) mx = fmaxf(mx, s_scores[g * a.chunk + jj]);
+      for (int i = lane; i < my_n; i += 32) mx = fmaxf(mx, my_scores[g * per_warp + i]);
       mx = mi::warp_max(mx);
-      if (lane == 0) s_stat[warp * GT + g] = mx;
-    }
-    __syncthreads();
-    if (threadIdx.x < GT) {
-      float mx = s_stat[threadIdx.x];
-#pragma unroll
-      for (int w = 1; w < WARPS; ++w) mx = fmaxf(mx, s_stat[w * GT + threadIdx.x]);
-      s_m[threadIdx.x] = mx;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      const float mx = s_m[g];
+      const float m_use = mx == -INFINITY ? 0.f : mx;      // a warp without keys
       float sum = 0.f;
-      for (int jj = threadIdx.x; jj < n; jj += WARPS * 32) {
-        const float pe = expf(s_scores[g * a.chunk + jj] - mx);
-        s_scores[g * a.chunk + jj] = pe;
+      for (int i = lane; i < my_n; i += 32) {
+        const float pe = exp2f(my_scores[g * per_warp + i] - m_use);
+        my_scores[g * per_warp + i] = pe;
         sum += pe;
       }
-      sum = mi::warp_sum(sum);
-      if (lane == 0) s_stat[warp * GT + g] = sum;
+      m_w[g] = mx;
+      l_w[g] = mi::warp_sum(sum);
     }
-    __syncthreads();
-    if (threadIdx.x < GT) {
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < WARPS; ++w) sum += s_stat[w * GT + threadIdx.x];
-      s_l[threadIdx.x] = sum;
-    }
+    __syncwarp();
     // 3. values, once they are there
     if (g0 == 0) {
       ok = mbar_wait(&bars[1], 0);
@@ -252,18 +242,19 @@ decode_split_kernel(DecodeArgs a) {
       for (int i = 0; i < VEC; ++i) acc[g][i] = 0.f;
     if (active) {
 #pragma unroll 2
-      for (int jj = warp * KPW + ks; jj < n; jj += WARPS * KPW) {
+      for (int it = 0; it * (WARPS * KPW) + warp * KPW + ks < n; ++it) {
+        const int jj = it * (WARPS * KPW) + warp * KPW + ks;
         float vf[VEC];
         unpack8(*reinterpret_cast<const uint4*>(v_s + (size_t)jj * HD + dl * VEC), vf);
 #pragma unroll
         for (int g = 0; g < GT; ++g) {
-          const float pe = s_scores[g * a.chunk + jj];
+          const float pe = my_scores[g * per_warp + it * KPW + ks];
 #pragma unroll
           for (int i = 0; i < VEC; ++i) acc[g][i] = fmaf(pe, vf[i], acc[g][i]);
         }
       }
     }
-    // across the key slots of the warp, then across warps
+    // across the key slots of the warp
 #pragma unroll
     for (int g = 0; g < GT; ++g)
 #pragma unroll
@@ -279,21 +270,36 @@ decode_split_kernel(DecodeArgs a) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) s_red[(warp * GT + g) * HD + dl * VEC + i] = acc[g][i];
     }
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        s_stat[(warp * GT + g) * 2] = m_w[g];
+        s_stat[(warp * GT + g) * 2 + 1] = l_w[g];
+      }
+    }
     __syncthreads();
+    // across the warps: the chunk's max, sum and unnormalised output, in a fixed order
     for (int idx = threadIdx.x; idx < GT * HD; idx += WARPS * 32) {
       const int g = idx / HD, d = idx % HD;
       if (g0 + g >= G) continue;
-      float v = 0.f;
+      float m = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < WARPS; ++w) v += s_red[(w * GT + g) * HD + d];
+      for (int w = 0; w < WARPS; ++w) m = fmaxf(m, s_stat[(w * GT + g) * 2]);
+      float v = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float mw = s_stat[(w * GT + g) * 2];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+        v = fmaf(s_red[(w * GT + g) * HD + d], f, v);
+        l = fmaf(s_stat[(w * GT + g) * 2 + 1], f, l);
+      }
       const int head = kvh * G + g0 + g;
       a.part_o[(((size_t)e * a.nh + head) * a.max_splits + split) * HD + d] = v;
-    }
-    if (threadIdx.x < GT && g0 + threadIdx.x < G) {
-      const int head = kvh * G + g0 + threadIdx.x;
-      float* ml = a.part_ml + (((size_t)e * a.nh + head) * a.max_splits + split) * 2;
-      ml[0] = s_m[threadIdx.x];
-      ml[1] = s_l[threadIdx.x];
+      if (d == 0) {
+        float* ml = a.part_ml + (((size_t)e * a.nh + head) * a.max_splits + split) * 2;
+        ml[0] = m;
+        ml[1] = l;
+      }
     }
     __syncthreads();
   }
@@ -308,40 +314,43 @@ decode_split_kernel(DecodeArgs a) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int g = warp; g < G; g += WARPS) {
+  // work items: (head of this kv head, 32 dims); a warp takes items in turn, a lane one dim
+  constexpr int DS = (HD + 31) / 32;
+  for (int item_idx = warp; item_idx < G * DS; item_idx += WARPS) {
+    const int g = item_idx / DS, d = (item_idx % DS) * 32 + lane;
     const int head = kvh * G + g;
     const float* ml = a.part_ml + ((size_t)e * a.nh + head) * a.max_splits * 2;
     const float* po = a.part_o + ((size_t)e * a.nh + head) * a.max_splits * HD;
+    // lanes over chunks: max and sum
     float m = -INFINITY;
     for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, __ldcg(ml + 2 * s));
     m = mi::warp_max(m);
-    float l = 0.f;
-    for (int s = lane; s < n_splits; s += 32) l += __ldcg(ml + 2 * s + 1) * expf(__ldcg(ml + 2 * s) - m);
+    float l = 0.f, w_lane = 0.f;
+    for (int s = lane; s < n_splits; s += 32) {
+      const float f = exp2f(__ldcg(ml + 2 * s) - m);
+      if (s < 32) w_lane = f;
+      l = fmaf(__ldcg(ml + 2 * s + 1), f, l);
+    }
     l = mi::warp_sum(l);
     const float inv = 1.f / l;
-    __nv_bfloat16* dst = a.out + (size_t)row * a.nh * HD + (size_t)head * HD;
-    float o[(HD + 31) / 32];
-#pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) o[i] = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float w = expf(__ldcg(ml + 2 * s) - m);
-#pragma unroll
-      for (int i = 0; i < (HD + 31) / 32; ++i) {
-        const int d = lane + 32 * i;
-        if (d < HD) o[i] = fmaf(__ldcg(po + (size_t)s * HD + d), w, o[i]);
-      }
+    float o = 0.f;
+    const int first = min(n_splits, 32);
+#pragma unroll 4
+    for (int s = 0; s < first; ++s) {
+      const float f = __shfl_sync(0xffffffffu, w_lane, s);
+      if (d < HD) o = fmaf(__ldcg(po + (size_t)s * HD + d), f, o);
     }
-#pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) {
-      const int d = lane + 32 * i;
-      if (d < HD) dst[d] = __float2bfloat16_rn(o[i] * inv);
+    for (int s = 32; s < n_splits; ++s) {
+      const float f = exp2f(__ldcg(ml + 2 * s) - m);
+      if (d < HD) o = fmaf(__ldcg(po + (size_t)s * HD + d), f, o);
     }
+    if (d < HD) a.out[(size_t)row * a.nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(o * inv);
   }
 }
 
 size_t smem_bytes(int chunk, int gt) {
-  return (size_t)2 * chunk * HD * 2 + (size_t)gt * chunk * 4 + (size_t)WARPS * gt * HD * 4 + (size_t)WARPS * gt * 4 +
-         (size_t)(2 * gt + 2) * 4 + 2 * 8 + 16;
+  return (size_t)2 * chunk * HD * 2 + (size_t)gt * ((chunk + 63) / 64 * 64) * 4 + (size_t)WARPS * gt * HD * 4 + (size_t)WARPS * gt * 2 * 4 +
+         2 * 8 + 16;
 }
 
 template <int GT>
@@ -373,7 +382,7 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
                                     int* counters, int* status, int n_dec, int nh, int nkv, int page_size, float scale,
                                     int window, int chunk, int max_splits, cudaStream_t stream) {
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts nh=%d nkv=%d", nh, nkv);
-  MI_REQUIRE(chunk >= 16 && chunk <= MAX_CHUNK && chunk % 16 == 0, "attention_decode: chunk=%d must be a multiple of 16 up to %d", chunk, MAX_CHUNK);
+  MI_REQUIRE(chunk >= 32 && chunk <= MAX_CHUNK && chunk % 32 == 0, "attention_decode: chunk=%d must be a multiple of 32 up to %d", chunk, MAX_CHUNK);
   MI_REQUIRE(max_splits >= 1 && max_splits <= 65535, "attention_decode: max_splits=%d", max_splits);
   MI_REQUIRE(page_size > 0 && q_stride % 8 == 0, "attention_decode: bad page_size=%d or q_stride=%d", page_size, q_stride);
   MI_REQUIRE(n_dec <= 65535 && nkv <= 65535, "attention_decode: too many entries for one launch");

@@ -6,9 +6,10 @@
 // eighth of K; it streams its weights with 16-byte loads that bypass L1 (each byte is used once),
 // reads the matching activations (small, L1/L2 resident) and multiplies on the tensor cores with
 // mma.m16n8k16 (activations as the 16-row operand, 8 weight rows as the 8-column operand).  The
-// eight warps of a block cover K between them and add their partial tiles in shared memory in a
-// fixed order.  No split across blocks, no atomics: the value of an output element is a function
-// of K alone, so a request's logits do not depend on what else is in the batch.
+// warps that share a group of weight rows (1, 2, 4 or 8 of them, chosen from N alone) cover K
+// between them and add their partial tiles in shared memory in a fixed order.  No split across
+// blocks, no atomics: the value of an output element is a function of (N, K) alone, so a request's
+// logits do not depend on what else is in the batch.
 //
 // The k index inside a 32-wide block is permuted the same way for both operands so that a thread's
 // 16-byte load is exactly its fragment of two consecutive MMAs (thread t of a quad loads
@@ -49,20 +50,24 @@ __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// MT: 16-row tiles of x (M <= 16*MT).  NT: 8-row tiles of w per warp.
-template <int MT, int NT, typename TOut>
+// MT: 16-row tiles of x (M <= 16*MT; HALF: M <= 8, the upper 8 rows of the tile are never loaded).
+// NT: 8-row tiles of w per warp.  KSPLIT: warps that share a group of weight rows and split K between
+// them; a block's 8 warps hold 8 / KSPLIT such groups.  KSPLIT is chosen from N alone.
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
   extern __shared__ float red[];  // [WARPS][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
+  constexpr int GROUPS = WARPS / KSPLIT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * (NT * 8);
+  const int group = warp / KSPLIT, kpart = warp % KSPLIT;
+  const int n0 = (blockIdx.x * GROUPS + group) * (NT * 8);
 
   const int nkb = (K + 31) / 32;
-  const int per = (nkb + WARPS - 1) / WARPS;
-  const int kb_begin = warp * per;
+  const int per = (nkb + KSPLIT - 1) / KSPLIT;
+  const int kb_begin = kpart * per;
   const int kb_end = min(nkb, kb_begin + per);
 
   float acc[MT][NT][4];
@@ -79,12 +84,13 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 
   // k-blocks are taken U at a time; the loads of the next group are issued before the products of
   // this one, so a warp always has a whole group of 16-byte loads in flight.
-  constexpr int U = (2 * MT + NT) <= 3 ? 4 : ((2 * MT + NT) <= 6 ? 2 : 1);
+  constexpr int LOADS = (HALF ? MT : 2 * MT) + NT;
+  constexpr int U = LOADS <= 3 ? 4 : (LOADS <= 6 ? 2 : 1);
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  uint4 wv[U][NT], xa[U][MT], xb[U][MT];
-  uint4 wn[U][NT], xan[U][MT], xbn[U][MT];
+  uint4 wv[U][NT], xa[U][MT], xb[U][HALF ? 1 : MT];
+  uint4 wn[U][NT], xan[U][MT], xbn[U][HALF ? 1 : MT];
 
-  auto load_group = [&](int kb0, uint4 (&w_)[U][NT], uint4 (&a_)[U][MT], uint4 (&b_)[U][MT]) {
+  auto load_group = [&](int kb0, uint4 (&w_)[U][NT], uint4 (&a_)[U][MT], uint4 (&b_)[U][HALF ? 1 : MT]) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb0 + u) * 32 + 8 * t;
@@ -95,7 +101,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       for (int i = 0; i < MT; ++i) {
         const int ma = i * 16 + g, mb = ma + 8;
         a_[u][i] = (in && ma < M) ? ld_cached(x + (size_t)ma * K + k) : zero;
-        b_[u][i] = (in && mb < M) ? ld_cached(x + (size_t)mb * K + k) : zero;
+        if (!HALF) b_[u][i] = (in && mb < M) ? ld_cached(x + (size_t)mb * K + k) : zero;
       }
     }
   };
@@ -110,8 +116,9 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          mma_bf16(acc[i][j], xa[u][i].x, xb[u][i].x, xa[u][i].y, xb[u][i].y, wv[u][j].x, wv[u][j].y);
-          mma_bf16(acc[i][j], xa[u][i].z, xb[u][i].z, xa[u][i].w, xb[u][i].w, wv[u][j].z, wv[u][j].w);
+          const uint4 b = HALF ? zero : xb[u][HALF ? 0 : i];
+          mma_bf16(acc[i][j], xa[u][i].x, b.x, xa[u][i].y, b.y, wv[u][j].x, wv[u][j].y);
+          mma_bf16(acc[i][j], xa[u][i].z, b.z, xa[u][i].w, b.w, wv[u][j].z, wv[u][j].w);
         }
     if (more) {
 #pragma unroll
@@ -119,12 +126,29 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 #pragma unroll
         for (int j = 0; j < NT; ++j) wv[u][j] = wn[u][j];
 #pragma unroll
-        for (int i = 0; i < MT; ++i) { xa[u][i] = xan[u][i]; xb[u][i] = xbn[u][i]; }
+        for (int i = 0; i < MT; ++i) {
+          xa[u][i] = xan[u][i];
+          if (!HALF) xb[u][i] = xbn[u][i];
+        }
       }
     }
   }
 
-  // partial tiles -> shared memory; fragment element c of (i, j): row i*16 + g + 8*(c/2), col j*8 + 2t + (c&1)
+  const int rows = min(M, MT * 16);
+  if (KSPLIT == 1) {
+    // no partner: straight from the fragments; element c of (i, j): row i*16 + g + 8*(c/2), col j*8 + 2t + (c&1)
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int m = i * 16 + g + 8 * (c >> 1), n = n0 + j * 8 + 2 * t + (c & 1);
+          if (m < rows && n < N) store_out<TOut>(out + (size_t)m * ldo + n, acc[i][j][c]);
+        }
+    return;
+  }
+  // partial tiles -> shared memory, then the KSPLIT partials of a group are added in a fixed order
   float* mine = red + (size_t)warp * (MT * 16) * RS;
 #pragma unroll
   for (int i = 0; i < MT; ++i)
@@ -134,46 +158,64 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       for (int c = 0; c < 4; ++c)
         mine[(i * 16 + g + 8 * (c >> 1)) * RS + j * 8 + 2 * t + (c & 1)] = acc[i][j][c];
   __syncthreads();
-  const int rows = min(M, MT * 16);
-  for (int idx = threadIdx.x; idx < rows * (NT * 8); idx += WARPS * 32) {
+  constexpr int PER_GROUP = KSPLIT * 32;           // threads of a group
+  const int tid_in_group = kpart * 32 + lane;
+  for (int idx = tid_in_group; idx < rows * (NT * 8); idx += PER_GROUP) {
     const int m = idx / (NT * 8), c = idx % (NT * 8);
     const int n = n0 + c;
     if (n >= N) continue;
     float s = 0.f;
 #pragma unroll
-    for (int ww = 0; ww < WARPS; ++ww) s += red[((size_t)ww * (MT * 16) + m) * RS + c];
+    for (int ww = 0; ww < KSPLIT; ++ww) s += red[((size_t)(group * KSPLIT + ww) * (MT * 16) + m) * RS + c];
     store_out<TOut>(out + (size_t)m * ldo + n, s);
   }
 }
 
-template <int MT, int NT, typename TOut>
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut>
 int launch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
            cudaStream_t stream) {
-  const size_t smem = (size_t)WARPS * (MT * 16) * (NT * 8 + 1) * sizeof(float);
-  auto kernel = gemm_skinny_kernel<MT, NT, TOut>;
+  const size_t smem = KSPLIT == 1 ? 0 : (size_t)WARPS * (MT * 16) * (NT * 8 + 1) * sizeof(float);
+  auto kernel = gemm_skinny_kernel<MT, NT, KSPLIT, HALF, TOut>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return mi_fail("gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
-  const int blocks = (N + NT * 8 - 1) / (NT * 8);
+  const int rows_per_block = (WARPS / KSPLIT) * NT * 8;
+  const int blocks = (N + rows_per_block - 1) / rows_per_block;
   kernel<<<blocks, WARPS * 32, smem, stream>>>(out, x, w, M, N, K, ldo);
   MI_LAUNCH_OK("gemm_skinny");
   return 0;
 }
 
+template <int MT, int NT, bool HALF, typename TOut>
+int pick_ksplit(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
+                cudaStream_t stream) {
+  // As few warps per group of rows as still gives every SM about two blocks: long-lived warps that
+  // stream many rows keep more bytes in flight than many short-lived blocks.  A function of N only,
+  // so that the order of the additions behind an output does not depend on the batch.
+  const int target = 296;
+  int ks = 1;
+  while (ks < 8 && (N + (WARPS / ks) * NT * 8 - 1) / ((WARPS / ks) * NT * 8) < target) ks *= 2;
+  if (K < 64 * ks) ks = 1;   // nothing to split
+  switch (ks) {
+    case 1: return launch<MT, NT, 1, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
+    case 2: return launch<MT, NT, 2, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
+    case 4: return launch<MT, NT, 4, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
+    default: return launch<MT, NT, 8, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
+  }
+}
+
 template <typename TOut>
 int dispatch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
              cudaStream_t stream) {
-  // Wider warp tiles re-use the activation fragments; narrower ones make more blocks.  Take the
-  // widest tile that still leaves at least two blocks for each of the 148 SMs.
-  const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
-  int nt = mt;
-  while (nt > 1 && (N + nt * 8 - 1) / (nt * 8) < 296) nt >>= 1;
-#define MI_SK(MT_, NT_) \
-  if (mt == MT_ && nt == NT_) return launch<MT_, NT_, TOut>(out, x, w, M, N, K, ldo, stream)
-  MI_SK(1, 1); MI_SK(2, 1); MI_SK(2, 2); MI_SK(4, 1); MI_SK(4, 2); MI_SK(4, 4);
-#undef MI_SK
-  return mi_fail("gemm_skinny: no kernel for M=%d", M);
+  // Wider warp tiles re-use the activation fragments; narrower ones make more blocks.
+  if (M <= 8) return pick_ksplit<1, 1, true, TOut>(out, x, w, M, N, K, ldo, stream);
+  if (M <= 16) return pick_ksplit<1, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
+  const bool wide = N >= 2048;
+  if (M <= 32) return wide ? pick_ksplit<2, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)
+                           : pick_ksplit<2, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
+  return wide ? pick_ksplit<4, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)
+              : pick_ksplit<4, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
 }
 
 }  // namespace

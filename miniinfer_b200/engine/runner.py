@@ -32,6 +32,7 @@ from .context import StepContext, Workspace
 
 PREFILL_TILE = 64   # query rows of one prefill-attention tile
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+GRAPH_CONTEXT_STEP = 1024   # a captured decode step serves contexts up to a multiple of this
 
 
 @dataclass
@@ -99,6 +100,7 @@ class _DecodeGraph:
     self.logits: Optional[torch.Tensor] = None
     self.tokens: Optional[torch.Tensor] = None
     self.launches = 0
+    self.max_ctx_len = 0
 
 
 class ModelRunner:
@@ -120,7 +122,7 @@ class ModelRunner:
       else:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
     self.meta = _MetaBuffers(self.device)
-    self._graphs: Dict[int, _DecodeGraph] = {}
+    self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
     self.last_h2d_bytes = 0
     self.last_launches = 0
 
@@ -323,9 +325,13 @@ class ModelRunner:
     B = len(items)
     try:
       arrays = self._padded(self._describe(items, starts, sampling), bucket)
-      g = self._graphs.get(bucket)
+      # the split-KV grid is part of the capture: one graph per (bucket, context class)
+      longest = int(arrays["ctx_len"].max())
+      ctx_class = min(self.cache.max_model_len, -(-longest // GRAPH_CONTEXT_STEP) * GRAPH_CONTEXT_STEP)
+      g = self._graphs.get((bucket, ctx_class))
       if g is None:
-        g = self._graphs[bucket] = _DecodeGraph(bucket, self.device)
+        g = self._graphs[(bucket, ctx_class)] = _DecodeGraph(bucket, self.device)
+        g.max_ctx_len = ctx_class
       offsets = g.meta.upload(arrays, fixed_capacity=g.graph is not None)
       self.last_h2d_bytes = g.meta.bytes_copied
       self.cache.sync()
@@ -333,16 +339,15 @@ class ModelRunner:
         self._capture(g, arrays, offsets, sample_fn)
       g.graph.replay()
       self.last_launches = g.launches
-      tokens_out[:B].copy_(g.tokens[:B], non_blocking=True)
     except BaseException:
       self._finish(items, False)
       raise
     self._finish(items, True)
-    return tokens_out[:B]
+    return g.tokens[:B]
 
   def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn) -> None:
-    # lengths up to max_model_len must be served by the captured launch: size the split-KV grid for it
-    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=self.cache.max_model_len)
+    # every length of the context class must be served by the captured launch: size the split-KV grid for it
+    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=g.max_ctx_len)
     g.tokens = torch.zeros(g.bucket, dtype=torch.int32, device=self.device)
 
     def run():
