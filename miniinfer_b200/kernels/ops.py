@@ -13,6 +13,7 @@ package's own CUDA.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -257,16 +258,16 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     ctypes.c_float(scale), win, _stream()))
 
 
-DECODE_CHUNKS = (128, 64, 32)
+DECODE_CHUNKS = (512, 256, 128, 64)
 
 
 def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
   """Keys per block of the split-KV decode kernel: the longest chunk that still gives every SM about
-  two blocks, so that a small batch is spread over the whole GPU.  Large heads take shorter chunks
-  (K and V of a chunk sit in shared memory)."""
+  two blocks, so that a small batch is spread over the whole GPU."""
+  forced = os.environ.get("MINIINFER_B200_DECODE_CHUNK")
+  if forced:
+    return int(forced)
   for c in DECODE_CHUNKS:
-    if c * head_dim > 128 * 128:
-      continue
     if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
       return c
   return DECODE_CHUNKS[-1]
@@ -289,21 +290,12 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
       scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
-      counters = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv + 1, torch.int32)
+      counters = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv, torch.int32)
     else:
       scratch = torch.empty(n, dtype=torch.float32, device=qkv.device)
-      counters = torch.zeros(batch.num_decode * nkv + 1, dtype=torch.int32, device=qkv.device)
+      counters = torch.zeros(batch.num_decode * nkv, dtype=torch.int32, device=qkv.device)
     _check(lib, lib.mi_attention_decode_bf16(
       _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
       _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
-      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32), _ptr(counters[:1], torch.int32),
+      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters, torch.int32),
       batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _stream()))
-    if batch.scratch is None:
-      if int(counters[0]) != 0:
-        raise KernelError("attention_decode: a bounded wait on the copy barrier ran out")
-
-
-def device_status(ws) -> int:
-  """The status word that kernels with bounded waits set when a wait ran out (0: all well)."""
-  buf = ws._bufs.get(("attention_decode_counters", torch.int32))
-  return int(buf[0]) if buf is not None else 0
