@@ -1,0 +1,622 @@
+// Decode attention over the paged cache in bf16, fed by TMA: the kernel for page sizes that are
+// multiples of 64 and head sizes that are multiples of 64 (the other sizes take the cp.async kernel
+// of attention_decode.cu, which computes the same thing).
+//
+// Reading K and V once from HBM is all the time this kernel should take, and at B200's bandwidth
+// per SM that leaves no room for per-thread copy instructions or for blocks that start and stop:
+//   * one persistent block per SM walks a list of work items (request, chunk of keys, kv head);
+//   * a producer warp asks the TMA engine for 64-key tiles of K and V - one tensor copy per
+//     64 x 64-element box, written to shared memory in the 128-byte swizzle that makes the later
+//     ldmatrix reads conflict-free - several tiles ahead, across item boundaries, counted on
+//     mbarriers (full / empty per stage);
+//   * three consumer warps take tiles in turn; the number of stages is a multiple of three, so a
+//     stage always goes to the same warp and that warp sees every phase of the stage's barriers
+//     (a parity wait cannot tell phases two apart).  Each warp computes S = Q K^T and O += P V for its whole tile on the tensor cores (mma.m16n8k16, bf16
+//     in, fp32 accumulate; the query heads that share the kv head are the rows of the 16-row tile)
+//     with an online softmax in float32 (base 2, scale folded in);
+//   * at the end of an item the three warps' (max, sum, O) are merged in shared memory in the
+//     order of the tiles they took.  If the item is the request's only chunk, that is the output.  Otherwise it is written
+//     as the chunk's partial result and handed to an epilogue warp, which does what needs round
+//     trips through L2 off the consumers' path: it counts the item on a counter per (request, kv
+//     head); the block whose count is the last one merges the chunks (the recurrence the reference
+//     sketches in flash_decode_splitk.py:76-87,129-146) and writes the output rows.
+// Which chunks exist, which tiles a chunk has and which warp takes which tile depend on the
+// context length (and window) alone, so the order of every sum is fixed.
+//
+// No block waits for another block.  Inside a block every wait on an mbarrier is bounded: a wait
+// that runs out raises a flag in shared memory that ends all later waits at once, sets the status
+// word in global memory, and the block runs to its end (its results are then garbage and the host
+// raises an error when it reads the status).
+//
+// Stands where the reference calls FlashInfer's / FlashAttention's decode kernels
+// (miniinfer/layers/attention_backend/flashinfer_backend.py:323-327).
+//
+// Compiled once per head size: -DMI_HEAD_DIM=<multiple of 16, 16..256>.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef MI_HEAD_DIM
+#error "compile with -DMI_HEAD_DIM=<head size>"
+#endif
+
+#if MI_HEAD_DIM % 64 == 0
+
+namespace {
+
+constexpr int HD = MI_HEAD_DIM;
+constexpr int CONSUMERS = 3;                 // consumer warps; the number of stages is a multiple of it
+constexpr int THREADS = (CONSUMERS + 2) * 32;   // + producer warp + epilogue warp
+constexpr int NI = 4;                        // items in flight between producer, consumers and epilogue
+constexpr int BK = 64;                       // keys of a tile
+constexpr int NBOX = HD / 64;                // 64-element (128-byte) boxes across a row
+constexpr int BOX_BYTES = BK * 128;          // 64 rows x 128 bytes
+constexpr int TILE_BYTES = NBOX * BOX_BYTES; // K (or V) of one tile
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+constexpr int KSTEPS = HD / 16;
+constexpr int NT_O = HD / 8;
+constexpr int MAX_STAGES = 12;
+constexpr int WAIT_LIMIT = 1 << 18;          // polls of an mbarrier before giving up
+
+struct Item {                                // what the producer tells the consumers about an item
+  int nb;                                    // tiles; -1: no more items
+  int e, kvh, split, n_splits;
+  int j0;                                    // first key of tile 0 (a multiple of 64)
+  int k_lo, k_end;                           // keys that count: k_lo <= j < k_end
+  int row;                                   // the request's row in the step
+  int pad;                                   // keeps the size a multiple of 8 bytes
+};
+
+struct Args {
+  __nv_bfloat16* out;            // [T, nh * HD]
+  const __nv_bfloat16* q_base;   // fused QKV rows; q first
+  int q_stride;
+  const int* block_table;
+  int bt_stride;
+  const int* decode_items;
+  const int* q_start;
+  const int* ctx_len;
+  const int* seq_slot;
+  float* part_o;                 // [n_dec, nh, max_splits, HD]
+  float* part_ml;                // [n_dec, nh, max_splits, 2]
+  int* counters;                 // [n_dec, nkv], zero between launches
+  int* status;
+  int n_dec, nh, nkv, page_size, window, chunk, max_splits, stages, gp;   // gp = min(G, 16)
+  float scale;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait.  `abort` is a flag in shared memory: once any wait has run out, all waits return.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return;
+    if ((i & 63) == 63 && *abort) return;
+  }
+  *abort = 1;
+  atomicExch(status, 1);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory"); }
+// Barrier of the consumer warps that also tells every one of them whether any passed a true flag.
+__device__ __forceinline__ bool consumer_any(bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, 1, %2, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(out) : "r"((uint32_t)flag), "n"(CONSUMERS * 32) : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+// Address of the 16-byte chunk `c` (0 .. HD/8) of row `r` (0 .. 63) of a swizzled tile.
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int c) {
+  return tile + (uint32_t)((c >> 3) * BOX_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the swizzle pattern is a function of the address: the tiles start on a 1024-byte boundary
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  // [stages][K tile, V tile] | q[NI][gp][HD] bf16 | red [4][gp][HD] + [4][gp][2] floats | items[NI] | barriers | flag
+  unsigned char* stage0 = smem;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + (size_t)a.stages * STAGE_BYTES);
+  float* red = reinterpret_cast<float*>(q_s + NI * a.gp * HD);
+  Item* items = reinterpret_cast<Item*>(red + CONSUMERS * a.gp * (HD + 2));
+  uint64_t* full = reinterpret_cast<uint64_t*>(items + NI);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* qfull = empty + MAX_STAGES;     // item described and its queries landed
+  uint64_t* qempty = qfull + NI;            // consumers and epilogue are done with the item's slot
+  uint64_t* efull = qempty + NI;            // the item's partial results are written
+  volatile int* abort = reinterpret_cast<volatile int*>(efull + NI);
+  float* merge_s = reinterpret_cast<float*>(efull + NI) + 4;   // [gp][max_splits][2]: the epilogue warp's scratch
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = a.nh / a.nkv;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < NI; ++i) {
+      mbar_init(&qfull[i], 1);
+      mbar_init(&qempty[i], CONSUMERS + 1);
+      mbar_init(&efull[i], 1);
+    }
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == CONSUMERS) {
+    // ------------------------------------------------------------------ producer (one lane)
+    if (lane != 0) return;
+    const size_t total = (size_t)a.n_dec * a.max_splits * a.nkv;
+    int it = 0, blk = 0;
+    for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
+      const int kvh = (int)(t % a.nkv);
+      const int split = (int)((t / a.nkv) % a.max_splits);
+      const int e = (int)(t / ((size_t)a.nkv * a.max_splits));
+      const int item = a.decode_items[e];
+      const int p = a.ctx_len[item] - 1;
+      const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+      const int c0 = lo / a.chunk;
+      const int n_splits = p / a.chunk - c0 + 1;
+      if (split >= n_splits) continue;
+      const int chunk_idx = c0 + split;
+      const int k_lo = max(lo, chunk_idx * a.chunk);
+      const int k_end = min(p + 1, (chunk_idx + 1) * a.chunk);
+      const int j0 = k_lo / BK * BK;
+      const int nb = (k_end - j0 + BK - 1) / BK;
+      const int row = a.q_start[item];
+      const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
+
+      const int qp = it % NI;
+      mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
+      Item d;
+      d.nb = nb; d.e = e; d.kvh = kvh; d.split = split; d.n_splits = n_splits;
+      d.j0 = j0; d.k_lo = k_lo; d.k_end = k_end; d.row = row;
+      items[qp] = d;
+      // the query heads of this kv head are neighbours in the row: one copy
+      mbar_expect_tx(&qfull[qp], (uint32_t)(G * HD * 2));
+      bulk_load_1d(q_s + (size_t)qp * a.gp * HD, a.q_base + (size_t)row * a.q_stride + (size_t)kvh * G * HD, (uint32_t)(G * HD * 2), &qfull[qp]);
+
+      for (int b = 0; b < nb; ++b, ++blk) {
+        const int s = blk % a.stages;
+        mbar_wait(&empty[s], ((blk / a.stages) & 1) ^ 1, abort, a.status);
+        const int jb = j0 + b * BK;
+        const int page = bt[jb / a.page_size];
+        const int y_k = ((page * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
+        const int y_v = y_k + a.nkv * a.page_size;
+        unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
+#pragma unroll
+        for (int x = 0; x < NBOX; ++x) {
+          tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
+          tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+        }
+      }
+      ++it;
+    }
+    // no more items
+    const int qp = it % NI;
+    mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
+    items[qp].nb = -1;
+    mbar_arrive(&qfull[qp]);
+    return;
+  }
+
+  if (warp == CONSUMERS + 1) {
+    // ------------------------------------------------------------------ epilogue warp
+    // Items whose request has several chunks: count the item; the block that counts last merges.
+    for (int it = 0;; ++it) {
+      const int qp = it % NI;
+      mbar_wait(&efull[qp], (it / NI) & 1, abort, a.status);
+      const Item d = items[qp];
+      if (d.nb < 0 || *abort) break;
+      if (d.n_splits > 1) {
+        int prev = 0;
+        if (lane == 0) {
+          __threadfence();                 // the consumers' partial results (ordered before by the barrier) go first
+          prev = atomicAdd(&a.counters[d.e * a.nkv + d.kvh], 1);
+        }
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        const bool last = prev == d.n_splits - 1;
+        if (last && lane == 0) a.counters[d.e * a.nkv + d.kvh] = 0;     // ready for the next launch
+        if (last) {
+          __threadfence();
+          // All heads of this kv head at once, in two round trips through L2: (1) every chunk's max
+          // and sum into shared memory, from which the weights follow; (2) every chunk's partial
+          // output, many loads in flight per lane.
+          constexpr int DS = (HD + 31) / 32;
+          const int ns = d.n_splits;
+          const float* ml0 = a.part_ml + ((size_t)d.e * a.nh + (size_t)d.kvh * G) * a.max_splits * 2;
+          const float* po0 = a.part_o + ((size_t)d.e * a.nh + (size_t)d.kvh * G) * a.max_splits * HD;
+          for (int idx = lane; idx < G * ns; idx += 32) {
+            const int gh = idx / ns, sp = idx % ns;
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(ml0 + ((size_t)gh * a.max_splits + sp) * 2));
+            merge_s[2 * idx] = v.x;
+            merge_s[2 * idx + 1] = v.y;
+          }
+          __syncwarp();
+          for (int gh = 0; gh < G; ++gh) {
+            float m = -INFINITY;
+            for (int sp = lane; sp < ns; sp += 32) m = fmaxf(m, merge_s[2 * (gh * ns + sp)]);
+            m = mi::warp_max(m);
+            float l = 0.f;
+            for (int sp = lane; sp < ns; sp += 32) l = fmaf(merge_s[2 * (gh * ns + sp) + 1], exp2f(merge_s[2 * (gh * ns + sp)] - m), l);
+            l = mi::warp_sum(l);
+            const float inv = 1.f / l;
+            __syncwarp();
+            for (int sp = lane; sp < ns; sp += 32) merge_s[2 * (gh * ns + sp)] = exp2f(merge_s[2 * (gh * ns + sp)] - m) * inv;   // the chunk's weight
+          }
+          __syncwarp();
+          for (int gh = 0; gh < G; ++gh) {
+            float acc[DS];
+#pragma unroll
+            for (int i = 0; i < DS; ++i) acc[i] = 0.f;
+            const float* po = po0 + (size_t)gh * a.max_splits * HD;
+            int sp = 0;
+            for (; sp + 4 <= ns; sp += 4) {          // 4 * DS independent loads per lane
+              float v[4][DS];
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < DS; ++i) {
+                  const int dd = i * 32 + lane;
+                  v[u][i] = dd < HD ? __ldcg(po + (size_t)(sp + u) * HD + dd) : 0.f;
+                }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float f = merge_s[2 * (gh * ns + sp + u)];
+#pragma unroll
+                for (int i = 0; i < DS; ++i) acc[i] = fmaf(v[u][i], f, acc[i]);
+              }
+            }
+            for (; sp < ns; ++sp) {
+              const float f = merge_s[2 * (gh * ns + sp)];
+#pragma unroll
+              for (int i = 0; i < DS; ++i) {
+                const int dd = i * 32 + lane;
+                if (dd < HD) acc[i] = fmaf(__ldcg(po + (size_t)sp * HD + dd), f, acc[i]);
+              }
+            }
+            const int head = d.kvh * G + gh;
+#pragma unroll
+            for (int i = 0; i < DS; ++i) {
+              const int dd = i * 32 + lane;
+              if (dd < HD) a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(acc[i]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qempty[qp]);
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  const int g = lane >> 2, t4 = lane & 3;
+  const int lm = lane >> 3, lr = lane & 7;
+  const float scale2 = a.scale * 1.4426950408889634f;
+  const int gp = a.gp;
+  int blk_base = 0;
+  for (int it = 0;; ++it) {
+    const int qp = it % NI;
+    mbar_wait(&qfull[qp], (it / NI) & 1, abort, a.status);
+    const Item d = items[qp];
+    // all consumer warps take the same decision, or the barriers below would not be met by all
+    if (consumer_any(d.nb < 0 || *abort != 0)) {
+      if (threadIdx.x == 0) mbar_arrive(&efull[qp]);     // the epilogue warp sees the end as well
+      break;
+    }
+
+    for (int g0 = 0; g0 < G; g0 += 16) {       // more than 16 heads per kv head: the tiles are walked again
+      const int heads = min(16, G - g0);
+      // query fragments: rows g and g + 8 of the 16-row tile, zero past `heads`
+      uint32_t qf[KSTEPS][4];
+      {
+        const __nv_bfloat16* qrow = q_s + (size_t)qp * gp * HD + (size_t)g0 * HD;
+#pragma unroll
+        for (int k = 0; k < KSTEPS; ++k) {
+          const int c0 = k * 16 + 2 * t4;
+          qf[k][0] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + c0) : 0u;
+          qf[k][1] = g + 8 < heads ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + c0) : 0u;
+          qf[k][2] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + c0 + 8) : 0u;
+          qf[k][3] = g + 8 < heads ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + c0 + 8) : 0u;
+        }
+      }
+      float o[NT_O][4];
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+      float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+      // tile gb of this block's stream goes to warp gb mod 3 (it owns the stages gb mod `stages` can be);
+      // `rank` is the warp's place among the item's tiles, which fixes the order of the merge
+      const int rank = (warp + CONSUMERS - blk_base % CONSUMERS) % CONSUMERS;
+      for (int b = rank; b < d.nb; b += CONSUMERS) {
+        const int gb = blk_base + b;
+        const int s = gb % a.stages;
+        if (g0 == 0) mbar_wait(&full[s], (gb / a.stages) & 1, abort, a.status);
+        const uint32_t kt = smem_u32(stage0 + (size_t)s * STAGE_BYTES);
+        const uint32_t vt = kt + TILE_BYTES;
+
+        // S = Q K^T: 16 heads x 64 keys
+        float sc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) sc[i][c] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+          for (int nbk = 0; nbk < 4; ++nbk) {
+            // matrices: (keys nbk*16 + 0..7, d k*16 + 0..7), (same keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
+            uint32_t kf[4];
+            ldmatrix_x4(kf, tile_addr(kt, nbk * 16 + (lm >> 1) * 8 + lr, k * 2 + (lm & 1)));
+            mma_bf16(sc[2 * nbk], qf[k], kf[0], kf[1]);
+            mma_bf16(sc[2 * nbk + 1], qf[k], kf[2], kf[3]);
+          }
+        }
+        // keys outside k_lo .. k_end do not count; softmax update per row (rows g and g + 8)
+        const int jb = d.j0 + b * BK;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int j = jb + i * 8 + 2 * t4 + (c & 1);
+            const float v = (j >= d.k_lo && j < d.k_end) ? sc[i][c] * scale2 : -INFINITY;
+            sc[i][c] = v;
+            mx[c >> 1] = fmaxf(mx[c >> 1], v);
+          }
+        float alpha[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+          const float m_new = fmaxf(m_run[h], mx[h]);
+          m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+          alpha[h] = exp2f(m_run[h] - m_use[h]);
+          m_run[h] = m_new;
+          l_run[h] *= alpha[h];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float pe = exp2f(sc[i][c] - m_use[c >> 1]);
+            sc[i][c] = pe;
+            l_run[c >> 1] += pe;
+          }
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+          o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+          o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          uint32_t pa[4];
+          pa[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+          pa[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+          pa[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+          pa[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+          for (int nb2 = 0; nb2 < HD / 16; ++nb2) {
+            // transposed: (keys kk*16 + 0..7, d nb2*16 + 0..7), (keys + 8, d), (keys, d + 8), (keys + 8, d + 8)
+            uint32_t vf[4];
+            ldmatrix_x4_trans(vf, tile_addr(vt, kk * 16 + (lm & 1) * 8 + lr, nb2 * 2 + (lm >> 1)));
+            mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
+            mma_bf16(o[2 * nb2 + 1], pa, vf[2], vf[3]);
+          }
+        }
+        if (g0 + 16 >= G) {          // last pass over this tile: hand the stage back
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+        }
+      }
+
+      // ---- the four warps' results -> shared memory, merged in warp order
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+      }
+      float* red_o = red + (size_t)rank * gp * HD;
+      float* red_ml = red + (size_t)CONSUMERS * gp * HD;
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i) {
+        if (g < heads) {
+          red_o[g * HD + i * 8 + 2 * t4] = o[i][0];
+          red_o[g * HD + i * 8 + 2 * t4 + 1] = o[i][1];
+        }
+        if (g + 8 < heads) {
+          red_o[(g + 8) * HD + i * 8 + 2 * t4] = o[i][2];
+          red_o[(g + 8) * HD + i * 8 + 2 * t4 + 1] = o[i][3];
+        }
+      }
+      if (t4 == 0) {
+        if (g < heads) { red_ml[(rank * gp + g) * 2] = m_run[0]; red_ml[(rank * gp + g) * 2 + 1] = l_run[0]; }
+        if (g + 8 < heads) { red_ml[(rank * gp + g + 8) * 2] = m_run[1]; red_ml[(rank * gp + g + 8) * 2 + 1] = l_run[1]; }
+      }
+      consumer_sync();
+      for (int idx = threadIdx.x; idx < heads * HD; idx += CONSUMERS * 32) {
+        const int r = idx / HD, dd = idx % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) m = fmaxf(m, red_ml[(w * gp + r) * 2]);
+        float v = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < CONSUMERS; ++w) {
+          const float mw = red_ml[(w * gp + r) * 2];
+          const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+          v = fmaf(red[((size_t)w * gp + r) * HD + dd], f, v);
+          l = fmaf(red_ml[(w * gp + r) * 2 + 1], f, l);
+        }
+        const int head = d.kvh * G + g0 + r;
+        if (d.n_splits == 1) {            // the only chunk: this is the output
+          a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(v / l);
+        } else {
+          a.part_o[(((size_t)d.e * a.nh + head) * a.max_splits + d.split) * HD + dd] = v;
+          if (dd == 0) {
+            float* pml = a.part_ml + (((size_t)d.e * a.nh + head) * a.max_splits + d.split) * 2;
+            pml[0] = m;
+            pml[1] = l;
+          }
+        }
+      }
+      consumer_sync();      // red is free again; the results of this pass are written
+    }
+    blk_base += d.nb;
+    // hand the item to the epilogue warp and go on
+    if (threadIdx.x == 0) mbar_arrive(&efull[qp]);
+    if (lane == 0) mbar_arrive(&qempty[qp]);
+  }
+}
+
+
+size_t smem_bytes(int stages, int gp, int max_splits) {
+  return (size_t)stages * STAGE_BYTES + (size_t)NI * gp * HD * 2 + (size_t)CONSUMERS * gp * (HD + 2) * 4 + NI * sizeof(Item) +
+         (size_t)(2 * MAX_STAGES + 3 * NI) * 8 + 16 + (size_t)gp * max_splits * 2 * 4 + 1024;
+}
+
+}  // namespace
+
+// Describes one layer of the cache - [page, 2, kv head, token, HD] seen as rows of HD elements - to
+// the TMA engine: boxes of 64 rows x 64 elements, 128-byte swizzle.  `out_map` receives 128 bytes.
+MI_API int mi_kv_tensor_map(void* out_map, const void* kv_layer, long long rows) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return mi_fail("kv_tensor_map: the driver does not offer cuTensorMapEncodeTiled");
+    encode = (EncodeFn)fn;
+  }
+  MI_REQUIRE(((uintptr_t)kv_layer % 128) == 0, "kv_tensor_map: the cache layer must be 128-byte aligned");
+  MI_REQUIRE(rows > 0, "kv_tensor_map: no rows");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)BK};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv_layer), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mi_fail("kv_tensor_map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  memcpy(out_map, &map, sizeof(map));
+  return 0;
+}
+
+MI_API int mi_attention_decode_tma_supported() { return 1; }
+
+// counters: n_dec * nkv ints, zero before the first launch; status: one int, 0 until a wait runs out.
+MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, const void* kv_map,
+                                   const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
+                                   const int* ctx_len, const int* seq_slot, float* scratch, int* counters, int* status,
+                                   int n_dec, int nh, int nkv, int page_size, float scale, int window, int chunk,
+                                   int max_splits, int num_sms, cudaStream_t stream) {
+  MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode_tma: bad head counts nh=%d nkv=%d", nh, nkv);
+  MI_REQUIRE(page_size % BK == 0, "attention_decode_tma: page_size=%d must be a multiple of %d", page_size, BK);
+  MI_REQUIRE(chunk >= BK && chunk % BK == 0, "attention_decode_tma: chunk=%d must be a multiple of %d", chunk, BK);
+  MI_REQUIRE(max_splits >= 1 && max_splits <= 512 && q_stride % 8 == 0, "attention_decode_tma: bad max_splits=%d (1..512) or q_stride=%d", max_splits, q_stride);
+  MI_REQUIRE(((uintptr_t)q_base % 16) == 0, "attention_decode_tma: q must be 16-byte aligned");
+  MI_REQUIRE(num_sms > 0, "attention_decode_tma: num_sms");
+  if (n_dec == 0) return 0;
+  const int G = nh / nkv;
+  MI_REQUIRE(G <= 16, "attention_decode_tma: at most 16 query heads per kv head (got %d)", G);
+  Args a;
+  a.out = (__nv_bfloat16*)out;
+  a.q_base = (const __nv_bfloat16*)q_base;
+  a.q_stride = q_stride;
+  a.block_table = block_table;
+  a.bt_stride = bt_stride;
+  a.decode_items = decode_items;
+  a.q_start = q_start;
+  a.ctx_len = ctx_len;
+  a.seq_slot = seq_slot;
+  a.part_o = scratch;
+  a.part_ml = scratch + (size_t)n_dec * nh * max_splits * HD;
+  a.counters = counters;
+  a.status = status;
+  a.n_dec = n_dec; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.chunk = chunk;
+  a.max_splits = max_splits;
+  a.gp = G < 16 ? G : 16;
+  a.scale = scale;
+  int stages = MAX_STAGES;
+  while (stages > CONSUMERS && smem_bytes(stages, a.gp, max_splits) > 220 * 1024) stages -= CONSUMERS;
+  MI_REQUIRE(smem_bytes(stages, a.gp, max_splits) <= 227 * 1024, "attention_decode_tma: shared memory does not suffice");
+  a.stages = stages;
+  const size_t smem = smem_bytes(stages, a.gp, max_splits);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (err != cudaSuccess) return mi_fail("attention_decode_tma: cannot get shared memory: %s", cudaGetErrorString(err));
+    configured = 227 * 1024;
+  }
+  CUtensorMap map;
+  memcpy(&map, kv_map, sizeof(map));
+  const size_t total = (size_t)n_dec * max_splits * nkv;
+  const int grid = (int)(total < (size_t)num_sms ? total : (size_t)num_sms);
+  decode_tma_kernel<<<grid, THREADS, smem, stream>>>(map, a);
+  MI_LAUNCH_OK("attention_decode_tma");
+  return 0;
+}
+
+#else  // head sizes that are not multiples of 64 have no TMA kernel
+
+#include <string.h>
+
+MI_API int mi_attention_decode_tma_supported() { return 0; }
+MI_API int mi_kv_tensor_map(void*, const void*, long long) { return mi_fail("kv_tensor_map: head size %d has no TMA kernel", MI_HEAD_DIM); }
+MI_API int mi_attention_decode_tma(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,
+                                   const int*, float*, int*, int*, int, int, int, int, float, int, int, int, int, cudaStream_t) {
+  return mi_fail("attention_decode_tma: head size %d has no TMA kernel", MI_HEAD_DIM);
+}
+
+#endif

@@ -261,14 +261,17 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
 DECODE_CHUNKS = (512, 256, 128, 64)
 
 
-def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
-  """Keys per block of the split-KV decode kernel: the longest chunk that still gives every SM about
-  two blocks, so that a small batch is spread over the whole GPU."""
+def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int, persistent: bool = False) -> int:
+  """Keys per work item of the split-KV decode kernels: the longest chunk that still gives every SM a
+  few items, so that a small batch is spread over the whole GPU."""
   forced = os.environ.get("MINIINFER_B200_DECODE_CHUNK")
   if forced:
     return int(forced)
-  for c in DECODE_CHUNKS:
-    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
+  # the persistent kernel balances items over one block per SM: it wants a few items for each;
+  # the other kernel wants about two blocks per SM and holds a chunk's partial sums per block
+  want = 296
+  for c in ((8192, 4096, 2048, 1024) + DECODE_CHUNKS if persistent else DECODE_CHUNKS):
+    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= want:
       return c
   return DECODE_CHUNKS[-1]
 
@@ -285,17 +288,59 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
       nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
-    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
+    G = nh // nkv
+    use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 16 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
+    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd, use_tma)
     max_splits = -(-span // chunk) + 1
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
       scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
-      counters = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv, torch.int32)
+      counters = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv + 1, torch.int32)
     else:
       scratch = torch.empty(n, dtype=torch.float32, device=qkv.device)
-      counters = torch.zeros(batch.num_decode * nkv, dtype=torch.int32, device=qkv.device)
-    _check(lib, lib.mi_attention_decode_bf16(
-      _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
-      _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
-      _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters, torch.int32),
-      batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _stream()))
+      counters = torch.zeros(batch.num_decode * nkv + 1, dtype=torch.int32, device=qkv.device)
+    if use_tma:
+      _check(lib, lib.mi_attention_decode_tma(
+        _ptr(out), _ptr(qkv), qkv.shape[1], _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
+        _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32), _ptr(counters[:1], torch.int32),
+        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _num_sms(qkv.device), _stream()))
+      if batch.scratch is None and int(counters[0]) != 0:
+        raise KernelError("attention_decode_tma: a bounded wait on a copy barrier ran out")
+    else:
+      _check(lib, lib.mi_attention_decode_bf16(
+        _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
+        _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32),
+        batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _stream()))
+
+
+_tensor_maps: Dict[tuple, ctypes.Array] = {}
+_sm_counts: Dict[int, int] = {}
+
+
+def _num_sms(device) -> int:
+  idx = device.index if device.index is not None else torch.cuda.current_device()
+  if idx not in _sm_counts:
+    _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+  return _sm_counts[idx]
+
+
+def _kv_tensor_map(lib, kv_layer: torch.Tensor):
+  """The TMA descriptor of a cache layer (made once per layer: it holds the layer's address)."""
+  key = (kv_layer.data_ptr(), tuple(kv_layer.shape))
+  m = _tensor_maps.get(key)
+  if m is None:
+    m = ctypes.create_string_buffer(128)
+    rows = kv_layer.shape[0] * kv_layer.shape[1] * kv_layer.shape[2] * kv_layer.shape[3]
+    code = lib.mi_kv_tensor_map(m, _ptr(kv_layer), ctypes.c_longlong(rows))
+    if code != 0:
+      raise KernelError(lib.mi_last_error().decode())
+    _tensor_maps[key] = m
+  return m
+
+
+def device_status(ws) -> int:
+  """The status word that kernels with bounded waits set when a wait ran out (0: all well)."""
+  buf = ws._bufs.get(("attention_decode_counters", torch.int32))
+  return int(buf[0]) if buf is not None else 0
