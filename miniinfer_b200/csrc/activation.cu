@@ -6,6 +6,7 @@ namespace {
 
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total) {
+  mi::grid_dependency_sync();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -18,6 +19,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
 
 // bf16 with I a multiple of 8: 16-byte loads and stores.
 __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I8, size_t total8) {
+  mi::grid_dependency_sync();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I8;
     const int i = (int)(idx - t * I8);
@@ -47,11 +49,11 @@ MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaS
   if (dtype == MI_BF16 && I % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gu % 16) == 0) {
     const size_t total8 = total / 8;
     const int b8 = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
-    silu_mul_bf16x8_kernel<<<b8, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I / 8, total8);
+    mi::launch(silu_mul_bf16x8_kernel, dim3(b8), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I / 8, total8);
   } else if (dtype == MI_BF16)
-    silu_mul_kernel<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, total);
+    mi::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, total);
   else if (dtype == MI_F32)
-    silu_mul_kernel<<<blocks, threads, 0, stream>>>((float*)out, (const float*)gu, I, total);
+    mi::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out, (const float*)gu, I, total);
   else
     return mi_fail("silu_mul: unknown dtype %d", dtype);
   MI_LAUNCH_OK("silu_mul");

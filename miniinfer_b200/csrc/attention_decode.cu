@@ -114,6 +114,7 @@ __device__ __forceinline__ void load_block(__nv_bfloat16* ks, __nv_bfloat16* vs,
 
 __global__ void __launch_bounds__(WARPS * 32, 3)
 decode_split_kernel(DecodeArgs a) {
+  mi::grid_dependency_sync();
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][LDS]
   __nv_bfloat16* stage0 = q_s + 16 * LDS;                            // [STAGES][2 (k, v)][BK][LDS]
@@ -386,7 +387,7 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
     if (err != cudaSuccess) return mi_fail("attention_decode: cannot get %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(err));
     configured = true;
   }
-  decode_split_kernel<<<dim3(nkv, max_splits, n_dec), WARPS * 32, SMEM_BYTES, stream>>>(a);
+  mi::launch(decode_split_kernel, dim3(dim3(nkv, max_splits, n_dec)), dim3(WARPS * 32), SMEM_BYTES, stream, a);
   MI_LAUNCH_OK("attention_decode");
   return 0;
 }

@@ -151,6 +151,7 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int c) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
+  mi::grid_dependency_sync();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzle pattern is a function of the address: the tiles start on a 1024-byte boundary
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -603,7 +604,7 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
   memcpy(&map, kv_map, sizeof(map));
   const size_t total = (size_t)n_dec * max_splits * nkv;
   const int grid = (int)(total < (size_t)num_sms ? total : (size_t)num_sms);
-  decode_tma_kernel<<<grid, THREADS, smem, stream>>>(map, a);
+  mi::launch(decode_tma_kernel, dim3(grid), dim3(THREADS), smem, stream, map, a);
   MI_LAUNCH_OK("attention_decode_tma");
   return 0;
 }

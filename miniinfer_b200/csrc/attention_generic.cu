@@ -60,6 +60,7 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
                          const int* __restrict__ token_item, const int* __restrict__ positions,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, int page_size,
                          float scale, int window) {
+  mi::grid_dependency_sync();
   __shared__ float qs[WARPS][MAX_HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int tkn = blockIdx.y;
@@ -136,11 +137,11 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
   if (T == 0) return 0;
   dim3 grid((nh + WARPS - 1) / WARPS, T);
   if (dtype == MI_BF16)
-    attention_generic_kernel<<<grid, WARPS * 32, 0, stream>>>(
+    mi::launch(attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q_base, q_stride, (const __nv_bfloat16*)kv_layer, block_table,
         bt_stride, token_item, positions, seq_slot, nh, nkv, hd, page_size, scale, window);
   else if (dtype == MI_F32)
-    attention_generic_kernel<<<grid, WARPS * 32, 0, stream>>>(
+    mi::launch(attention_generic_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (float*)out, (const float*)q_base, q_stride, (const float*)kv_layer, block_table, bt_stride, token_item,
         positions, seq_slot, nh, nkv, hd, page_size, scale, window);
   else

@@ -102,6 +102,7 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* ks, __nv_bfloat16* 
 
 __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(PrefillArgs a) {
+  mi::grid_dependency_sync();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BQ][LDS]
   __nv_bfloat16* kbuf = qs + BQ * LDS;                              // [2][BK][LDS]
@@ -297,7 +298,7 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
     if (e != cudaSuccess) return mi_fail("attention_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  attention_prefill_kernel<<<dim3(n_tiles, nh), WARPS * 32, smem, stream>>>(a);
+  mi::launch(attention_prefill_kernel, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), smem, stream, a);
   MI_LAUNCH_OK("attention_prefill");
   return 0;
 }

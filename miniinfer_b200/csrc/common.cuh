@@ -11,6 +11,9 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <utility>
 
 #define MI_API extern "C" __attribute__((visibility("default")))
 
@@ -42,6 +45,43 @@ inline int mi_fail(const char* fmt, ...) {
   MI_API const char* mi_last_error() { return mi_error_text; }
 
 namespace mi {
+
+// Programmatic dependent launch, off unless MINIINFER_B200_PDL=1: a kernel launched with the
+// attribute may start while its predecessor in the stream is still running.  Every kernel of these
+// libraries begins with grid_dependency_sync(): it first lets its own successor start launching,
+// then waits until the predecessor has completed and its memory operations are visible.  Nothing is
+// read or written before that wait, so the order of the work is what plain stream order gives.
+// Measured on a decode step of 257 short kernels it did not pay (1.73 ms against 1.62 ms without):
+// the successors' blocks sit on the SMs while they wait.  Without the attribute both instructions
+// do nothing.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MINIINFER_B200_PDL");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+__device__ __forceinline__ void grid_dependency_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }

@@ -8,6 +8,7 @@ namespace {
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int H) {
+  mi::grid_dependency_sync();
   const int t = blockIdx.x;
   const T* row = table + (size_t)ids[t] * H;
   float* o = out + (size_t)t * H;
@@ -23,9 +24,9 @@ MI_API int mi_embedding(float* out, const void* table, int table_dtype, const in
   if (T == 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == MI_BF16)
-    embedding_kernel<<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H);
+    mi::launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, out, (const __nv_bfloat16*)table, ids, H);
   else if (table_dtype == MI_F32)
-    embedding_kernel<<<T, threads, 0, stream>>>(out, (const float*)table, ids, H);
+    mi::launch(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, out, (const float*)table, ids, H);
   else
     return mi_fail("embedding: unknown table dtype %d", table_dtype);
   MI_LAUNCH_OK("embedding");

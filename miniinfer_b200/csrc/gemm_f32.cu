@@ -14,6 +14,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                 int M, int N, int K, int ldo) {
+  mi::grid_dependency_sync();
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -69,7 +70,7 @@ MI_API int mi_gemm_f32(float* out, const float* x, const float* w, int M, int N,
   if (M == 0) return 0;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   MI_REQUIRE(grid.y <= 65535, "gemm_f32: M=%d is too large for one launch", M);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(out, x, w, M, N, K, ldo);
+  mi::launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, out, x, w, M, N, K, ldo);
   MI_LAUNCH_OK("gemm_f32");
   return 0;
 }

@@ -57,6 +57,7 @@ template <int MT, int NT, int KSPLIT, bool HALF, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
+  mi::grid_dependency_sync();
   extern __shared__ float red[];  // [WARPS][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
   constexpr int GROUPS = WARPS / KSPLIT;
@@ -182,7 +183,7 @@ int launch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int
   }
   const int rows_per_block = (WARPS / KSPLIT) * NT * 8;
   const int blocks = (N + rows_per_block - 1) / rows_per_block;
-  kernel<<<blocks, WARPS * 32, smem, stream>>>(out, x, w, M, N, K, ldo);
+  mi::launch(kernel, dim3(blocks), dim3(WARPS * 32), smem, stream, out, x, w, M, N, K, ldo);
   MI_LAUNCH_OK("gemm_skinny");
   return 0;
 }

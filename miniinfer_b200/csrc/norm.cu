@@ -16,6 +16,7 @@ template <typename TOut, typename TDelta>
 __global__ void add_rmsnorm_kernel(TOut* __restrict__ out, float* __restrict__ resid,
                                    const TDelta* __restrict__ delta, const float* __restrict__ w,
                                    const int* __restrict__ rows, int H, float eps, int write_back) {
+  mi::grid_dependency_sync();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
@@ -45,6 +46,7 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ resid,
                             const __nv_bfloat16* __restrict__ delta, const float* __restrict__ w,
                             const int* __restrict__ rows, int H, float eps, int write_back) {
+  mi::grid_dependency_sync();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int row = rows ? rows[r] : r;
@@ -100,18 +102,18 @@ MI_API int mi_add_rmsnorm(void* out, int out_dtype, float* resid, const void* de
   if (out_dtype == MI_BF16 && (delta == nullptr || delta_dtype == MI_BF16) && H % 4 == 0 && H <= 8192 && aligned) {
     const int vpt = (H / 4 + 255) / 256;
     if (vpt <= 1)
-      add_rmsnorm_bf16_vec_kernel<1><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+      mi::launch(add_rmsnorm_bf16_vec_kernel<1>, dim3(R), dim3(threads), 0, stream, (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
     else if (vpt <= 2)
-      add_rmsnorm_bf16_vec_kernel<2><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+      mi::launch(add_rmsnorm_bf16_vec_kernel<2>, dim3(R), dim3(threads), 0, stream, (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
     else if (vpt <= 4)
-      add_rmsnorm_bf16_vec_kernel<4><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+      mi::launch(add_rmsnorm_bf16_vec_kernel<4>, dim3(R), dim3(threads), 0, stream, (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
     else
-      add_rmsnorm_bf16_vec_kernel<8><<<R, threads, 0, stream>>>((__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
+      mi::launch(add_rmsnorm_bf16_vec_kernel<8>, dim3(R), dim3(threads), 0, stream, (__nv_bfloat16*)out, resid, (const __nv_bfloat16*)delta, w, rows, H, eps, write_back);
     MI_LAUNCH_OK("add_rmsnorm");
     return 0;
   }
 #define MI_NORM_LAUNCH(TO, TD) \
-  add_rmsnorm_kernel<TO, TD><<<R, threads, 0, stream>>>((TO*)out, resid, (const TD*)delta, w, rows, H, eps, write_back)
+  mi::launch(add_rmsnorm_kernel<TO, TD>, dim3(R), dim3(threads), 0, stream, (TO*)out, resid, (const TD*)delta, w, rows, H, eps, write_back)
   if (out_dtype == MI_BF16 && delta_dtype == MI_BF16) MI_NORM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else if (out_dtype == MI_F32 && delta_dtype == MI_F32) MI_NORM_LAUNCH(float, float);
   else if (out_dtype == MI_BF16 && delta_dtype == MI_F32) MI_NORM_LAUNCH(__nv_bfloat16, float);

@@ -23,6 +23,7 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, co
                           const float* __restrict__ cos_sin, int rotary_dim,
                           const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                           T* __restrict__ kv_layer, int nh, int nkv, int hd, int page_size, float eps) {
+  mi::grid_dependency_sync();
   __shared__ float buf[WARPS][MAX_HEAD_DIM];
   const int tkn = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -88,6 +89,7 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
                                const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ kv_layer, int nh, int nkv,
                                int page_size, float eps) {
+  mi::grid_dependency_sync();
   constexpr int HALF = HD / 2;
   constexpr int NP = HALF / 64;                 // bf16 pairs per lane in each half
   const int tkn = blockIdx.x;
@@ -179,19 +181,19 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
   const bool whole = !cos_sin || rotary_dim == hd;
   if (dtype == MI_BF16 && whole && (hd == 128 || hd == 256)) {
     if (hd == 128)
-      qk_norm_rope_store_fast_kernel<128><<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(grid), dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     else
-      qk_norm_rope_store_fast_kernel<256><<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<256>, dim3(grid), dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     MI_LAUNCH_OK("qk_norm_rope_store");
     return 0;
   }
   if (dtype == MI_BF16)
-    qk_norm_rope_store_kernel<<<grid, WARPS * 32, 0, stream>>>((__nv_bfloat16*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+    mi::launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, hd, page_size, eps);
   else if (dtype == MI_F32)
-    qk_norm_rope_store_kernel<<<grid, WARPS * 32, 0, stream>>>((float*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
+    mi::launch(qk_norm_rope_store_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, (float*)qkv, q_w, k_w, cos_sin, rotary_dim, positions,
                                                            slot_mapping, (float*)kv_layer, nh, nkv, hd, page_size, eps);
   else
     return mi_fail("qk_norm_rope: unknown dtype %d", dtype);

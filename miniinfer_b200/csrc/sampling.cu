@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(THREADS)
 sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict__ logits,
                         const float* __restrict__ temperature, const int* __restrict__ top_k,
                         const float* __restrict__ top_p, int V) {
+  mi::grid_dependency_sync();
   __shared__ Best best_scratch[32];
   __shared__ unsigned int count_hist[256];
   __shared__ unsigned long long mass_hist[256];
@@ -193,6 +194,7 @@ sample_pick_kernel(int* __restrict__ out, const float* __restrict__ logits, cons
                    const long long* __restrict__ seed, const long long* __restrict__ counter,
                    const uint32_t* __restrict__ thr_in, float* __restrict__ part_v, int* __restrict__ part_i,
                    int* __restrict__ arrivals, int V, int slices, int slice_len) {
+  mi::grid_dependency_sync();
   __shared__ Best scratch[PICK_THREADS / 32];
   __shared__ int s_last;
   const int row = blockIdx.y, slice = blockIdx.x;
@@ -263,10 +265,10 @@ MI_API int mi_sample(int* out, const float* logits, const float* temperature, co
   uint32_t* thr = (uint32_t*)scratch;
   float* part_v = (float*)scratch + R;
   int* part_i = (int*)scratch + R + (size_t)R * slices;
-  sample_threshold_kernel<<<R, THREADS, 0, stream>>>(thr, logits, temperature, top_k, top_p, V);
+  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), 0, stream, thr, logits, temperature, top_k, top_p, V);
   MI_LAUNCH_OK("sample thresholds");
   const int slice_len = (V + slices - 1) / slices;
-  sample_pick_kernel<<<dim3(slices, R), PICK_THREADS, 0, stream>>>(out, logits, temperature, seed, counter, thr, part_v,
+  mi::launch(sample_pick_kernel, dim3(dim3(slices, R)), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr, part_v,
                                                                   part_i, arrivals, V, slices, slice_len);
   MI_LAUNCH_OK("sample pick");
   return 0;
