@@ -273,3 +273,58 @@ MI_API int mi_sample(int* out, const float* logits, const float* temperature, co
   MI_LAUNCH_OK("sample pick");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in no_alloc_api.h).  Its scratch is a
+// fixed array in the library's device image instead of memory the caller passes.
+#include "no_alloc_api.h"
+
+#define MI_SAMPLE_STATIC_WORDS 1024   /* thr[R] + best value and index per (row, slice): R + 2 * R * slices <= 256 + 2 * 296 */
+#define MI_SAMPLE_STATIC_MAX_DEVICES 64
+
+// 4 KiB of per-slice results and thresholds, then one arrival counter per row.
+static __device__ __align__(256) unsigned int g_sample_static_scratch[MI_SAMPLE_STATIC_WORDS + MI_SAMPLE_STATIC_MAX_ROWS];
+static_assert(sizeof(g_sample_static_scratch) == MI_SAMPLE_STATIC_SCRATCH_BYTES, "the header states the size");
+
+// In host code the array's name is only a handle; the kernels need its address on the device,
+// which differs from GPU to GPU.  Looked up once per device.
+static void* g_sample_static_addr[MI_SAMPLE_STATIC_MAX_DEVICES] = {};
+
+MI_API int mi_sample_static(int* out, const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                            const long long* seed, const long long* counter, int R, int V, cudaStream_t stream) {
+  MI_REQUIRE(R >= 0 && V > 0, "sample_static: bad sizes R=%d V=%d", R, V);
+  MI_REQUIRE(R <= MI_SAMPLE_STATIC_MAX_ROWS, "sample_static: R=%d rows is more than the %d this entry point has scratch for",
+             R, MI_SAMPLE_STATIC_MAX_ROWS);
+  if (R == 0) return 0;
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return mi_fail("sample_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  MI_REQUIRE(device >= 0 && device < MI_SAMPLE_STATIC_MAX_DEVICES, "sample_static: device %d is out of range", device);
+  if (!g_sample_static_addr[device]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sample_static_scratch);
+    if (e != cudaSuccess || !p) return mi_fail("sample_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_sample_static_addr[device] = p;
+  }
+  unsigned int* base = (unsigned int*)g_sample_static_addr[device];
+  // the same slicing rule as the callers of mi_sample use
+  int slices = 296 / R;
+  if (slices > 64) slices = 64;
+  if (slices > (V + 1023) / 1024) slices = (V + 1023) / 1024;
+  if (slices < 1) slices = 1;
+  MI_REQUIRE(R + 2 * R * slices <= MI_SAMPLE_STATIC_WORDS, "sample_static: scratch too small for R=%d slices=%d", R, slices);
+  uint32_t* thr = base;
+  float* part_v = (float*)base + R;
+  int* part_i = (int*)base + R + (size_t)R * slices;
+  int* arrivals = (int*)base + MI_SAMPLE_STATIC_WORDS;
+  // the arrival counters must start at zero whatever an earlier call left behind
+  e = cudaMemsetAsync(arrivals, 0, sizeof(int) * R, stream);
+  if (e != cudaSuccess) return mi_fail("sample_static: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), 0, stream, thr, logits, temperature, top_k, top_p, V);
+  MI_LAUNCH_OK("sample_static thresholds");
+  const int slice_len = (V + slices - 1) / slices;
+  mi::launch(sample_pick_kernel, dim3(slices, R), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr,
+             part_v, part_i, arrivals, V, slices, slice_len);
+  MI_LAUNCH_OK("sample_static pick");
+  return 0;
+}
