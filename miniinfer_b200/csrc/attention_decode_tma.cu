@@ -4,7 +4,8 @@
 //
 // Reading K and V once from HBM is all the time this kernel should take, and at B200's bandwidth
 // per SM that leaves no room for per-thread copy instructions or for blocks that start and stop:
-//   * one persistent block per SM walks a list of work items (request, chunk of keys, kv head);
+//   * one persistent block per SM; the step's 64-key tiles - all (request, kv head, tile) triples -
+//     are dealt out evenly over the blocks, so every block reads the same number of bytes;
 //   * a producer warp asks the TMA engine for 64-key tiles of K and V - one tensor copy per
 //     64 x 64-element box, written to shared memory in the 128-byte swizzle that makes the later
 //     ldmatrix reads conflict-free - several tiles ahead, across item boundaries, counted on
@@ -20,8 +21,9 @@
 //     trips through L2 off the consumers' path: it counts the item on a counter per (request, kv
 //     head); the block whose count is the last one merges the chunks (the recurrence the reference
 //     sketches in flash_decode_splitk.py:76-87,129-146) and writes the output rows.
-// Which chunks exist, which tiles a chunk has and which warp takes which tile depend on the
-// context length (and window) alone, so the order of every sum is fixed.
+// Where a request is cut between blocks depends on what else is in the step, so the sums of a
+// request are added in an order that varies with the batch: its output varies by rounding, as the
+// bf16 path allows (the 32-bit path has its own kernel, whose order is fixed).
 //
 // No block waits for another block.  Inside a block every wait on an mbarrier is bounded: a wait
 // that runs out raises a flag in shared memory that ends all later waits at once, sets the status
@@ -167,6 +169,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
   uint64_t* efull = qempty + NI;            // the item's partial results are written
   volatile int* abort = reinterpret_cast<volatile int*>(efull + NI);
   float* merge_s = reinterpret_cast<float*>(efull + NI) + 4;   // [gp][max_splits][2]: the epilogue warp's scratch
+  int* prefix_s = reinterpret_cast<int*>(merge_s + a.gp * a.max_splits * 2);   // [n_dec + 1]: tiles before each request
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int G = a.nh / a.nkv;
@@ -187,27 +190,74 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
   __syncthreads();
 
   if (warp == CONSUMERS) {
-    // ------------------------------------------------------------------ producer (one lane)
+    // ------------------------------------------------------------------ producer
+    // The step's tiles - all (request, kv head, 64-key tile) triples in that order - are dealt out
+    // evenly: block c takes the tiles bound(c) .. bound(c + 1), bound(c) = floor(c * total / blocks).
+    // A (request, kv head) that falls into one block is finished there; one that straddles blocks
+    // becomes one item in each, with partial results.  First the warp counts the tiles of every
+    // request into a prefix array, then one lane walks this block's range.
+    {
+      int carry = 0;
+      for (int base = 0; base < a.n_dec; base += 32) {
+        const int e = base + lane;
+        int v = 0;
+        if (e < a.n_dec) {
+          const int p = a.ctx_len[a.decode_items[e]] - 1;
+          const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+          v = (p + 1 - lo / BK * BK + BK - 1) / BK;
+        }
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        if (e < a.n_dec) prefix_s[e] = carry + x - v;
+        carry += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) prefix_s[a.n_dec] = carry;
+      __syncwarp();
+    }
     if (lane != 0) return;
-    const size_t total = (size_t)a.n_dec * a.max_splits * a.nkv;
+    const long long total = (long long)prefix_s[a.n_dec] * a.nkv;
+    // with fewer tiles than blocks only the first `total` blocks work, one tile each
+    const long long nblk = min((long long)gridDim.x, total);
+    const long long t_begin = blockIdx.x < nblk ? (long long)blockIdx.x * total / nblk : total;
+    const long long t_end = blockIdx.x < nblk ? (long long)(blockIdx.x + 1) * total / nblk : total;
     int it = 0, blk = 0;
-    for (size_t t = blockIdx.x; t < total; t += gridDim.x) {
-      const int kvh = (int)(t % a.nkv);
-      const int split = (int)((t / a.nkv) % a.max_splits);
-      const int e = (int)(t / ((size_t)a.nkv * a.max_splits));
+    // the request that holds tile t_begin: the last e with prefix[e] * nkv <= t_begin
+    int e = 0;
+    {
+      int lo_e = 0, hi_e = a.n_dec;          // prefix[lo_e] * nkv <= t_begin < prefix[hi_e] * nkv (when the range is not empty)
+      while (hi_e - lo_e > 1) {
+        const int mid = (lo_e + hi_e) / 2;
+        if ((long long)prefix_s[mid] * a.nkv <= t_begin) lo_e = mid; else hi_e = mid;
+      }
+      e = lo_e;
+    }
+    for (long long t = t_begin; t < t_end;) {
+      while ((long long)prefix_s[e + 1] * a.nkv <= t) ++e;         // skips requests without tiles
+      const int nt = prefix_s[e + 1] - prefix_s[e];
+      const long long first = (long long)prefix_s[e] * a.nkv;      // the request's first tile
+      const int kvh = (int)((t - first) / nt);
+      const int b0 = (int)((t - first) % nt);
+      const int b1 = (int)min((long long)nt, b0 + (t_end - t));
       const int item = a.decode_items[e];
       const int p = a.ctx_len[item] - 1;
       const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-      const int c0 = lo / a.chunk;
-      const int n_splits = p / a.chunk - c0 + 1;
-      if (split >= n_splits) continue;
-      const int chunk_idx = c0 + split;
-      const int k_lo = max(lo, chunk_idx * a.chunk);
-      const int k_end = min(p + 1, (chunk_idx + 1) * a.chunk);
-      const int j0 = k_lo / BK * BK;
-      const int nb = (k_end - j0 + BK - 1) / BK;
+      const int j_first = lo / BK * BK;
+      const int j0 = j_first + b0 * BK;
+      const int nb = b1 - b0;
+      const int k_lo = max(lo, j0);
+      const int k_end = min(p + 1, j_first + b1 * BK);
       const int row = a.q_start[item];
       const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
+      // which blocks share this (request, kv head): those that hold its first and its last tile
+      const long long s_first = first + (long long)kvh * nt, s_last = s_first + nt - 1;
+      const int c_first = (int)(((s_first + 1) * nblk - 1) / total);
+      const int c_last = (int)(((s_last + 1) * nblk - 1) / total);
+      const int n_splits = c_last - c_first + 1;
+      const int split = (int)blockIdx.x - c_first;
 
       const int qp = it % NI;
       mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
@@ -235,6 +285,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         }
       }
       ++it;
+      t += nb;
     }
     // no more items
     const int qp = it % NI;
@@ -517,9 +568,9 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
 }
 
 
-size_t smem_bytes(int stages, int gp, int max_splits) {
+size_t smem_bytes(int stages, int gp, int max_splits, int n_dec) {
   return (size_t)stages * STAGE_BYTES + (size_t)NI * gp * HD * 2 + (size_t)CONSUMERS * gp * (HD + 2) * 4 + NI * sizeof(Item) +
-         (size_t)(2 * MAX_STAGES + 3 * NI) * 8 + 16 + (size_t)gp * max_splits * 2 * 4 + 1024;
+         (size_t)(2 * MAX_STAGES + 3 * NI) * 8 + 16 + (size_t)gp * max_splits * 2 * 4 + (size_t)(n_dec + 1) * 4 + 1024;
 }
 
 }  // namespace
@@ -590,10 +641,10 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
   a.gp = G < 16 ? G : 16;
   a.scale = scale;
   int stages = MAX_STAGES;
-  while (stages > CONSUMERS && smem_bytes(stages, a.gp, max_splits) > 220 * 1024) stages -= CONSUMERS;
-  MI_REQUIRE(smem_bytes(stages, a.gp, max_splits) <= 227 * 1024, "attention_decode_tma: shared memory does not suffice");
+  while (stages > CONSUMERS && smem_bytes(stages, a.gp, max_splits, n_dec) > 220 * 1024) stages -= CONSUMERS;
+  MI_REQUIRE(smem_bytes(stages, a.gp, max_splits, n_dec) <= 227 * 1024, "attention_decode_tma: shared memory does not suffice");
   a.stages = stages;
-  const size_t smem = smem_bytes(stages, a.gp, max_splits);
+  const size_t smem = smem_bytes(stages, a.gp, max_splits, n_dec);
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t err = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -602,8 +653,8 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
   }
   CUtensorMap map;
   memcpy(&map, kv_map, sizeof(map));
-  const size_t total = (size_t)n_dec * max_splits * nkv;
-  const int grid = (int)(total < (size_t)num_sms ? total : (size_t)num_sms);
+  MI_REQUIRE(n_dec <= 4096, "attention_decode_tma: at most 4096 decode entries per launch (got %d)", n_dec);
+  const int grid = num_sms;
   mi::launch(decode_tma_kernel, dim3(grid), dim3(THREADS), smem, stream, map, a);
   MI_LAUNCH_OK("attention_decode_tma");
   return 0;

@@ -261,17 +261,14 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
 DECODE_CHUNKS = (512, 256, 128, 64)
 
 
-def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int, persistent: bool = False) -> int:
-  """Keys per work item of the split-KV decode kernels: the longest chunk that still gives every SM a
-  few items, so that a small batch is spread over the whole GPU."""
+def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
+  """Keys per block of the cp.async split-KV decode kernel: the longest chunk that still gives every
+  SM about two blocks, so that a small batch is spread over the whole GPU."""
   forced = os.environ.get("MINIINFER_B200_DECODE_CHUNK")
   if forced:
     return int(forced)
-  # the persistent kernel balances items over one block per SM: it wants a few items for each;
-  # the other kernel wants about two blocks per SM and holds a chunk's partial sums per block
-  want = 296
-  for c in ((8192, 4096, 2048, 1024) + DECODE_CHUNKS if persistent else DECODE_CHUNKS):
-    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= want:
+  for c in DECODE_CHUNKS:
+    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
       return c
   return DECODE_CHUNKS[-1]
 
@@ -290,8 +287,14 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
     use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 16 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
-    chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd, use_tma)
-    max_splits = -(-span // chunk) + 1
+    if use_tma:
+      # the TMA kernel deals 64-key tiles out evenly; a (request, kv head) is cut into at most as many
+      # pieces as it has tiles, and no more than there are blocks
+      chunk = 64
+      max_splits = min(-(-span // 64) + 2, _num_sms(qkv.device))
+    else:
+      chunk = batch.decode_chunk or decode_chunk(batch.num_decode, nkv, span, hd)
+      max_splits = -(-span // chunk) + 1
     n = batch.num_decode * nh * max_splits * (hd + 2)
     if batch.scratch is not None:
       scratch = batch.scratch.buffer("attention_decode_partials", (n,), torch.float32)
