@@ -192,7 +192,9 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
     engine.step()
   torch.cuda.synchronize()
   dt = time.perf_counter() - t0
-  s1 = engine.stats
+  s1 = dict(engine.stats)
+  host = {k[5:-2]: round(1e6 * (s1[k] - s0[k]) / steps, 1) for k in s1 if k.startswith("host_")}
+  print(f"e2e host microseconds per step by phase: {host}", file=sys.stderr)
   assert s1["decode_tokens"] - s0["decode_tokens"] == batch * steps, "the timed steps were not pure decode steps"
   while engine.has_unfinished():
     engine.step()
@@ -224,12 +226,30 @@ def time_prefill(engine, reps: int = 5) -> dict:
   return {"ms": times[len(times) // 2]}
 
 
-def kernel_table(engine, batch: int, steps: int = 6) -> str:
-  """Device time of every kernel of a decode step, from the CUPTI records of a few graph replays."""
+def kernel_table(engine, batch: int, steps: int = 6, mode: str = "decode") -> str:
+  """Device time of every kernel of a decode step (a few graph replays) or of a prefill step, from CUPTI records."""
   import torch
   from torch.profiler import ProfilerActivity, profile
   from miniinfer_b200.engine import StepItem
   from miniinfer_b200.sampling import Sampler, SamplingParams
+  if mode == "prefill":
+    g = torch.Generator().manual_seed(7)
+    V = engine.model_config.vocab_size
+
+    def whole(i):
+      rid = f"prefill{i}"
+      engine.cache.admit(rid)
+      engine.runner.step([StepItem(rid, torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist(), (PREFILL_TOKENS - 1,))])
+      engine.cache.release_request(rid)
+
+    for i in range(2):
+      whole(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+      for i in range(steps):
+        whole(10 + i)
+      torch.cuda.synchronize()
+    return _table_of(prof, steps, f"prefill step, {PREFILL_TOKENS} tokens")
   rids = fill_context(engine, batch, CONTEXT, seed=batch)
   params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
   tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
@@ -247,6 +267,10 @@ def kernel_table(engine, batch: int, steps: int = 6) -> str:
     torch.cuda.synchronize()
   for r in rids:
     engine.cache.release_request(r)
+  return _table_of(prof, steps, f"decode step, batch {batch}")
+
+
+def _table_of(prof, steps: int, title: str) -> str:
   rows = []
   total = 0.0
   for ev in prof.key_averages():
@@ -256,7 +280,7 @@ def kernel_table(engine, batch: int, steps: int = 6) -> str:
     rows.append((t / steps, ev.count / steps, ev.key))
     total += t / steps
   rows.sort(reverse=True)
-  lines = [f"decode step, batch {batch}: {total:.1f} us of kernels per step"]
+  lines = [f"{title}: {total:.1f} us of kernels per step"]
   for t, c, name in rows[:24]:
     lines.append(f"{t:9.1f} us/step  {c:6.1f} launches/step  {t / max(c, 1e-9):7.2f} us each  {name[:110]}")
   return "\n".join(lines)
@@ -279,7 +303,8 @@ def main() -> int:
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
   ap.add_argument("--skip-points", action="store_true")
-  ap.add_argument("--kernel-table", action="store_true", help="print the device time of each kernel of a decode step and exit")
+  ap.add_argument("--kernel-table", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
+                  help="print the device time of each kernel of a decode step (default) or a prefill step and exit")
   args = ap.parse_args()
   if args.impl == "reference":
     return reference_arm()
@@ -295,7 +320,7 @@ def main() -> int:
     with open(os.path.join(d, "config.json"), "w") as f:
       json.dump(cfg, f)
     if args.kernel_table:
-      print(kernel_table(build_engine(d, args.batch), args.batch))
+      print(kernel_table(build_engine(d, args.batch), args.batch, mode=args.kernel_table))
       return 0
     clocks = ClockSampler()
     engine = build_engine(d, args.batch)

@@ -328,6 +328,11 @@ class KVCacheManager:
     pages = np.asarray(r.pages[group], dtype=np.int64)[pos // g.page_size]
     return (pages * g.page_size + pos % g.page_size).astype(np.int32)
 
+  def slot_at(self, req_id: Hashable, group: int, pos: int) -> int:
+    """``slot_mapping`` for the one token at position ``pos``."""
+    P = self.page_size
+    return self._requests[req_id].pages[group][pos // P] * P + pos % P
+
   def sync(self) -> None:
     for g in self.paged_groups:
       g.sync()

@@ -12,11 +12,17 @@
 //     mbarriers (full / empty per stage);
 //   * three consumer warps take tiles in turn; the number of stages is a multiple of three, so a
 //     stage always goes to the same warp and that warp sees every phase of the stage's barriers
-//     (a parity wait cannot tell phases two apart).  Each warp computes S = Q K^T and O += P V for its whole tile on the tensor cores (mma.m16n8k16, bf16
-//     in, fp32 accumulate; the query heads that share the kv head are the rows of the 16-row tile)
-//     with an online softmax in float32 (base 2, scale folded in);
+//     (a parity wait cannot tell phases two apart).  Each warp computes its whole tile on the
+//     tensor cores (mma.m16n8k16, bf16 in, fp32 accumulate) with the products transposed:
+//     S^T = K Q^T and O^T += V^T P^T, the 16-row operand being keys (or dims of V) and the 8-column
+//     operand the query heads that share the kv head.  A decode step has few heads per kv head and
+//     many keys; this way the padding is to 8 heads, not 16, and the scores, the exponentials and
+//     the accumulators per thread are half of what heads-as-rows needs.  P^T comes from the
+//     scores' fragments by an 8x8 transpose inside the warp (movmatrix).  The softmax is online,
+//     in float32, base 2 with the scale folded in.  More than 8 heads per kv head: further passes;
 //   * at the end of an item the three warps' (max, sum, O) are merged in shared memory in the
-//     order of the tiles they took.  If the item is the request's only chunk, that is the output.  Otherwise it is written
+//     order of the tiles they took.  If the item is the request's only chunk, that is the output.
+//     Otherwise it is written
 //     as the chunk's partial result and handed to an epilogue warp, which does what needs round
 //     trips through L2 off the consumers' path: it counts the item on a counter per (request, kv
 //     head); the block whose count is the last one merges the chunks (the recurrence the reference
@@ -56,7 +62,6 @@ constexpr int BOX_BYTES = BK * 128;          // 64 rows x 128 bytes
 constexpr int TILE_BYTES = NBOX * BOX_BYTES; // K (or V) of one tile
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int KSTEPS = HD / 16;
-constexpr int NT_O = HD / 8;
 constexpr int MAX_STAGES = 12;
 constexpr int WAIT_LIMIT = 1 << 18;          // polls of an mbarrier before giving up
 
@@ -142,6 +147,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Transposes an 8x8 matrix of 16-bit values held in fragment layout (lane 4r + c holds row r, columns 2c, 2c + 1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+  uint32_t r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -153,7 +164,6 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int c) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
-  mi::grid_dependency_sync();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzle pattern is a function of the address: the tiles start on a 1024-byte boundary
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -187,37 +197,39 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // Before this kernel waits for its predecessor it reads only what the host uploaded (lengths, the
+  // list of decode entries): the producer warp counts the tiles of every request into a prefix array.
+  if (warp == CONSUMERS) {
+    int carry = 0;
+    for (int base = 0; base < a.n_dec; base += 32) {
+      const int e = base + lane;
+      int v = 0;
+      if (e < a.n_dec) {
+        const int p = a.ctx_len[a.decode_items[e]] - 1;
+        const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+        v = (p + 1 - lo / BK * BK + BK - 1) / BK;
+      }
+      int x = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (e < a.n_dec) prefix_s[e] = carry + x - v;
+      carry += __shfl_sync(0xffffffffu, x, 31);
+    }
+    if (lane == 0) prefix_s[a.n_dec] = carry;
+    __syncwarp();
+  }
   __syncthreads();
+  mi::grid_dependency_sync();
 
   if (warp == CONSUMERS) {
     // ------------------------------------------------------------------ producer
     // The step's tiles - all (request, kv head, 64-key tile) triples in that order - are dealt out
     // evenly: block c takes the tiles bound(c) .. bound(c + 1), bound(c) = floor(c * total / blocks).
     // A (request, kv head) that falls into one block is finished there; one that straddles blocks
-    // becomes one item in each, with partial results.  First the warp counts the tiles of every
-    // request into a prefix array, then one lane walks this block's range.
-    {
-      int carry = 0;
-      for (int base = 0; base < a.n_dec; base += 32) {
-        const int e = base + lane;
-        int v = 0;
-        if (e < a.n_dec) {
-          const int p = a.ctx_len[a.decode_items[e]] - 1;
-          const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-          v = (p + 1 - lo / BK * BK + BK - 1) / BK;
-        }
-        int x = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const int y = __shfl_up_sync(0xffffffffu, x, o);
-          if (lane >= o) x += y;
-        }
-        if (e < a.n_dec) prefix_s[e] = carry + x - v;
-        carry += __shfl_sync(0xffffffffu, x, 31);
-      }
-      if (lane == 0) prefix_s[a.n_dec] = carry;
-      __syncwarp();
-    }
+    // becomes one item in each, with partial results.  One lane walks this block's range.
     if (lane != 0) return;
     const long long total = (long long)prefix_s[a.n_dec] * a.nkv;
     // with fewer tiles than blocks only the first `total` blocks work, one tile each
@@ -401,27 +413,27 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
       break;
     }
 
-    for (int g0 = 0; g0 < G; g0 += 16) {       // more than 16 heads per kv head: the tiles are walked again
-      const int heads = min(16, G - g0);
-      // query fragments: rows g and g + 8 of the 16-row tile, zero past `heads`
-      uint32_t qf[KSTEPS][4];
+    for (int g0 = 0; g0 < G; g0 += 8) {        // more than 8 heads per kv head: the tiles are walked again
+      const int heads = min(8, G - g0);
+      // The products are taken transposed, keys as the 16-row operand and the (few) heads as the
+      // 8-column one: S^T = K Q^T, O^T = V^T P^T.  Query fragments: head g, dims 16k + 2t.. and + 8.
+      uint32_t qf[KSTEPS][2];
       {
-        const __nv_bfloat16* qrow = q_s + (size_t)qp * gp * HD + (size_t)g0 * HD;
+        const __nv_bfloat16* qrow = q_s + (size_t)qp * gp * HD + (size_t)(g0 + g) * HD;
 #pragma unroll
         for (int k = 0; k < KSTEPS; ++k) {
           const int c0 = k * 16 + 2 * t4;
-          qf[k][0] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + c0) : 0u;
-          qf[k][1] = g + 8 < heads ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + c0) : 0u;
-          qf[k][2] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + g * HD + c0 + 8) : 0u;
-          qf[k][3] = g + 8 < heads ? *reinterpret_cast<const uint32_t*>(qrow + (g + 8) * HD + c0 + 8) : 0u;
+          qf[k][0] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + c0) : 0u;
+          qf[k][1] = g < heads ? *reinterpret_cast<const uint32_t*>(qrow + c0 + 8) : 0u;
         }
       }
-      float o[NT_O][4];
+      // o[db][c]: dim db*16 + g + 8*(c/2), head 2t + (c&1)
+      float o[HD / 16][4];
 #pragma unroll
-      for (int i = 0; i < NT_O; ++i)
+      for (int i = 0; i < HD / 16; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
-      float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+      float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t and 2t + 1
 
       // tile gb of this block's stream goes to warp gb mod 3 (it owns the stages gb mod `stages` can be);
       // `rank` is the warp's place among the item's tiles, which fixes the order of the merge
@@ -433,40 +445,40 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         const uint32_t kt = smem_u32(stage0 + (size_t)s * STAGE_BYTES);
         const uint32_t vt = kt + TILE_BYTES;
 
-        // S = Q K^T: 16 heads x 64 keys
-        float sc[8][4];
+        // S^T = K Q^T: 64 keys x 8 heads; sc[mb][c]: key mb*16 + g + 8*(c/2), head 2t + (c&1)
+        float sc[4][4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int c = 0; c < 4; ++c) sc[i][c] = 0.f;
 #pragma unroll
         for (int k = 0; k < KSTEPS; ++k) {
 #pragma unroll
-          for (int nbk = 0; nbk < 4; ++nbk) {
-            // matrices: (keys nbk*16 + 0..7, d k*16 + 0..7), (same keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
+          for (int mb = 0; mb < 4; ++mb) {
+            // matrices: (keys mb*16 + 0..7, d k*16 + 0..7), (keys + 8, d), (keys, d + 8), (keys + 8, d + 8)
             uint32_t kf[4];
-            ldmatrix_x4(kf, tile_addr(kt, nbk * 16 + (lm >> 1) * 8 + lr, k * 2 + (lm & 1)));
-            mma_bf16(sc[2 * nbk], qf[k], kf[0], kf[1]);
-            mma_bf16(sc[2 * nbk + 1], qf[k], kf[2], kf[3]);
+            ldmatrix_x4(kf, tile_addr(kt, mb * 16 + (lm & 1) * 8 + lr, k * 2 + (lm >> 1)));
+            mma_bf16(sc[mb], kf, qf[k][0], qf[k][1]);
           }
         }
-        // keys outside k_lo .. k_end do not count; softmax update per row (rows g and g + 8)
+        // keys outside k_lo .. k_end do not count; softmax update per head (a column)
         const int jb = d.j0 + b * BK;
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const int j = jb + i * 8 + 2 * t4 + (c & 1);
+            const int j = jb + i * 16 + g + 8 * (c >> 1);
             const float v = (j >= d.k_lo && j < d.k_end) ? sc[i][c] * scale2 : -INFINITY;
             sc[i][c] = v;
-            mx[c >> 1] = fmaxf(mx[c >> 1], v);
+            mx[c & 1] = fmaxf(mx[c & 1], v);
           }
         float alpha[2], m_use[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+          mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
           const float m_new = fmaxf(m_run[h], mx[h]);
           m_use[h] = m_new == -INFINITY ? 0.f : m_new;
           alpha[h] = exp2f(m_run[h] - m_use[h]);
@@ -474,36 +486,33 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
           l_run[h] *= alpha[h];
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const float pe = exp2f(sc[i][c] - m_use[c >> 1]);
+            const float pe = exp2f(sc[i][c] - m_use[c & 1]);
             sc[i][c] = pe;
-            l_run[c >> 1] += pe;
+            l_run[c & 1] += pe;
           }
 #pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-          o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-          o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        for (int i = 0; i < HD / 16; ++i) {
+          o[i][0] *= alpha[0]; o[i][1] *= alpha[1];
+          o[i][2] *= alpha[0]; o[i][3] *= alpha[1];
         }
-        // O += P V
+        // O^T += V^T P^T
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          uint32_t pa[4];
-          pa[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-          pa[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-          pa[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-          pa[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+        for (int kb = 0; kb < 4; ++kb) {
+          // P^T as the 8-column operand: the 8x8 blocks (keys x heads) of the scores, transposed
+          const uint32_t pb0 = movmatrix_trans(pack_bf16(sc[kb][0], sc[kb][1]));
+          const uint32_t pb1 = movmatrix_trans(pack_bf16(sc[kb][2], sc[kb][3]));
 #pragma unroll
-          for (int nb2 = 0; nb2 < HD / 16; ++nb2) {
-            // transposed: (keys kk*16 + 0..7, d nb2*16 + 0..7), (keys + 8, d), (keys, d + 8), (keys + 8, d + 8)
+          for (int db = 0; db < HD / 16; ++db) {
+            // transposed: (keys kb*16 + 0..7, d db*16 + 0..7), (keys, d + 8), (keys + 8, d), (keys + 8, d + 8)
             uint32_t vf[4];
-            ldmatrix_x4_trans(vf, tile_addr(vt, kk * 16 + (lm & 1) * 8 + lr, nb2 * 2 + (lm >> 1)));
-            mma_bf16(o[2 * nb2], pa, vf[0], vf[1]);
-            mma_bf16(o[2 * nb2 + 1], pa, vf[2], vf[3]);
+            ldmatrix_x4_trans(vf, tile_addr(vt, kb * 16 + (lm >> 1) * 8 + lr, db * 2 + (lm & 1)));
+            mma_bf16(o[db], vf, pb0, pb1);
           }
         }
-        if (g0 + 16 >= G) {          // last pass over this tile: hand the stage back
+        if (g0 + 8 >= G) {           // last pass over this tile: hand the stage back
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
         }
@@ -512,25 +521,25 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
       // ---- the four warps' results -> shared memory, merged in warp order
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
       }
       float* red_o = red + (size_t)rank * gp * HD;
       float* red_ml = red + (size_t)CONSUMERS * gp * HD;
 #pragma unroll
-      for (int i = 0; i < NT_O; ++i) {
-        if (g < heads) {
-          red_o[g * HD + i * 8 + 2 * t4] = o[i][0];
-          red_o[g * HD + i * 8 + 2 * t4 + 1] = o[i][1];
+      for (int i = 0; i < HD / 16; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = 2 * t4 + (c & 1);
+          if (h < heads) red_o[h * HD + i * 16 + g + 8 * (c >> 1)] = o[i][c];
         }
-        if (g + 8 < heads) {
-          red_o[(g + 8) * HD + i * 8 + 2 * t4] = o[i][2];
-          red_o[(g + 8) * HD + i * 8 + 2 * t4 + 1] = o[i][3];
+      if (g == 0) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int h = 2 * t4 + c;
+          if (h < heads) { red_ml[(rank * gp + h) * 2] = m_run[c]; red_ml[(rank * gp + h) * 2 + 1] = l_run[c]; }
         }
-      }
-      if (t4 == 0) {
-        if (g < heads) { red_ml[(rank * gp + g) * 2] = m_run[0]; red_ml[(rank * gp + g) * 2 + 1] = l_run[0]; }
-        if (g + 8 < heads) { red_ml[(rank * gp + g + 8) * 2] = m_run[1]; red_ml[(rank * gp + g + 8) * 2 + 1] = l_run[1]; }
       }
       consumer_sync();
       for (int idx = threadIdx.x; idx < heads * HD; idx += CONSUMERS * 32) {

@@ -46,19 +46,20 @@ inline int mi_fail(const char* fmt, ...) {
 
 namespace mi {
 
-// Programmatic dependent launch, off unless MINIINFER_B200_PDL=1: a kernel launched with the
-// attribute may start while its predecessor in the stream is still running.  Every kernel of these
-// libraries begins with grid_dependency_sync(): it first lets its own successor start launching,
-// then waits until the predecessor has completed and its memory operations are visible.  Nothing is
-// read or written before that wait, so the order of the work is what plain stream order gives.
-// Measured on a decode step of 257 short kernels it did not pay (1.73 ms against 1.62 ms without):
-// the successors' blocks sit on the SMs while they wait.  Without the attribute both instructions
-// do nothing.
+// Programmatic dependent launch (on; MINIINFER_B200_PDL=0 turns it off): a kernel launched with
+// the attribute may be placed on the SMs while its predecessor in the stream is still running.
+// Every kernel of these libraries calls grid_dependency_sync() before it reads anything that a
+// kernel writes and before it writes anything at all: it waits until the predecessor has completed
+// and its memory operations are visible, and only then lets its own successor be placed.  So at
+// most one successor waits on the SMs beside a running kernel, and the order of the work is what
+// plain stream order gives.  Before the wait a kernel may only fetch what no kernel writes (weights,
+// the step's description that the host uploaded).  Without the attribute both instructions do nothing.
+// Measured on a decode step of 229 short kernels: 1.31 ms with it, 1.39 ms without.
 inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("MINIINFER_B200_PDL");
-    v = (e && e[0] == '1') ? 1 : 0;
+    v = (e && e[0] == '0') ? 0 : 1;
   }
   return v != 0;
 }
@@ -79,8 +80,8 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 }
 
 __device__ __forceinline__ void grid_dependency_sync() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 __device__ __forceinline__ float to_float(float x) { return x; }

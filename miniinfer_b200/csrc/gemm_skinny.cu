@@ -53,18 +53,28 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 // MT: 16-row tiles of x (M <= 16*MT; HALF: M <= 8, the upper 8 rows of the tile are never loaded).
 // NT: 8-row tiles of w per warp.  KSPLIT: warps that share a group of weight rows and split K between
 // them; a block's 8 warps hold 8 / KSPLIT such groups.  KSPLIT is chosen from N alone.
-template <int MT, int NT, int KSPLIT, bool HALF, typename TOut>
+// SWIGLU (NT == 2): w holds 2N rows, gate rows first; a warp's first tile is 8 gate rows, its second
+// the 8 up rows of the same columns, and the result is silu(gate) * up of the bf16-rounded products,
+// as the product followed by the activation kernel rounds them.
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float swiglu(float gate, float up) {
+  const float g = round_bf16(gate), u = round_bf16(up);
+  return g / (1.f + expf(-g)) * u;
+}
+
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
-  mi::grid_dependency_sync();
   extern __shared__ float red[];  // [WARPS][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
   constexpr int GROUPS = WARPS / KSPLIT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int group = warp / KSPLIT, kpart = warp % KSPLIT;
-  const int n0 = (blockIdx.x * GROUPS + group) * (NT * 8);
+  static_assert(!SWIGLU || NT == 2, "the fused activation pairs one gate tile with one up tile");
+  constexpr int COLS = SWIGLU ? 8 : NT * 8;   // output columns of a group of warps
+  const int n0 = (blockIdx.x * GROUPS + group) * COLS;
 
   const int nkb = (K + 31) / 32;
   const int per = (nkb + KSPLIT - 1) / KSPLIT;
@@ -81,7 +91,9 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 
   const __nv_bfloat16* wrow[NT];
 #pragma unroll
-  for (int j = 0; j < NT; ++j) wrow[j] = w + (size_t)min(n0 + j * 8 + g, N - 1) * K;
+  for (int j = 0; j < NT; ++j)
+    wrow[j] = SWIGLU ? w + ((size_t)min(n0 + g, N - 1) + (size_t)j * N) * K
+                     : w + (size_t)min(n0 + j * 8 + g, N - 1) * K;
 
   // k-blocks are taken U at a time; the loads of the next group are issued before the products of
   // this one, so a warp always has a whole group of 16-byte loads in flight.
@@ -91,13 +103,20 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   uint4 wv[U][NT], xa[U][MT], xb[U][HALF ? 1 : MT];
   uint4 wn[U][NT], xan[U][MT], xbn[U][HALF ? 1 : MT];
 
-  auto load_group = [&](int kb0, uint4 (&w_)[U][NT], uint4 (&a_)[U][MT], uint4 (&b_)[U][HALF ? 1 : MT]) {
+  auto load_w = [&](int kb0, uint4 (&w_)[U][NT]) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (kb0 + u) * 32 + 8 * t;
       const bool in = (kb0 + u) < kb_end && k < K;
 #pragma unroll
       for (int j = 0; j < NT; ++j) w_[u][j] = in ? ld_stream(wrow[j] + k) : zero;
+    }
+  };
+  auto load_x = [&](int kb0, uint4 (&a_)[U][MT], uint4 (&b_)[U][HALF ? 1 : MT]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (kb0 + u) * 32 + 8 * t;
+      const bool in = (kb0 + u) < kb_end && k < K;
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         const int ma = i * 16 + g, mb = ma + 8;
@@ -107,10 +126,17 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     }
   };
 
-  if (kb_begin < kb_end) load_group(kb_begin, wv, xa, xb);
+  // The first group of weights is on its way before this kernel waits for its predecessor: the
+  // weights are written by no kernel, the activations are.
+  if (kb_begin < kb_end) load_w(kb_begin, wv);
+  mi::grid_dependency_sync();
+  if (kb_begin < kb_end) load_x(kb_begin, xa, xb);
   for (int kb = kb_begin; kb < kb_end; kb += U) {
     const bool more = kb + U < kb_end;
-    if (more) load_group(kb + U, wn, xan, xbn);
+    if (more) {
+      load_w(kb + U, wn);
+      load_x(kb + U, xan, xbn);
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -138,6 +164,16 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   const int rows = min(M, MT * 16);
   if (KSPLIT == 1) {
     // no partner: straight from the fragments; element c of (i, j): row i*16 + g + 8*(c/2), col j*8 + 2t + (c&1)
+    if constexpr (SWIGLU) {
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int m = i * 16 + g + 8 * (c >> 1), n = n0 + 2 * t + (c & 1);
+          if (m < rows && n < N) store_out<TOut>(out + (size_t)m * ldo + n, swiglu(acc[i][0][c], acc[i][NT - 1][c]));
+        }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -161,48 +197,53 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   __syncthreads();
   constexpr int PER_GROUP = KSPLIT * 32;           // threads of a group
   const int tid_in_group = kpart * 32 + lane;
-  for (int idx = tid_in_group; idx < rows * (NT * 8); idx += PER_GROUP) {
-    const int m = idx / (NT * 8), c = idx % (NT * 8);
+  for (int idx = tid_in_group; idx < rows * COLS; idx += PER_GROUP) {
+    const int m = idx / COLS, c = idx % COLS;
     const int n = n0 + c;
     if (n >= N) continue;
-    float s = 0.f;
+    float s = 0.f, s_up = 0.f;
 #pragma unroll
-    for (int ww = 0; ww < KSPLIT; ++ww) s += red[((size_t)(group * KSPLIT + ww) * (MT * 16) + m) * RS + c];
-    store_out<TOut>(out + (size_t)m * ldo + n, s);
+    for (int ww = 0; ww < KSPLIT; ++ww) {
+      const float* tile = red + ((size_t)(group * KSPLIT + ww) * (MT * 16) + m) * RS;
+      s += tile[c];
+      if (SWIGLU) s_up += tile[8 + c];
+    }
+    store_out<TOut>(out + (size_t)m * ldo + n, SWIGLU ? swiglu(s, s_up) : s);
   }
 }
 
-template <int MT, int NT, int KSPLIT, bool HALF, typename TOut>
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU>
 int launch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
            cudaStream_t stream) {
   const size_t smem = KSPLIT == 1 ? 0 : (size_t)WARPS * (MT * 16) * (NT * 8 + 1) * sizeof(float);
-  auto kernel = gemm_skinny_kernel<MT, NT, KSPLIT, HALF, TOut>;
+  auto kernel = gemm_skinny_kernel<MT, NT, KSPLIT, HALF, TOut, SWIGLU>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return mi_fail("gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
-  const int rows_per_block = (WARPS / KSPLIT) * NT * 8;
-  const int blocks = (N + rows_per_block - 1) / rows_per_block;
+  const int cols_per_block = (WARPS / KSPLIT) * (SWIGLU ? 8 : NT * 8);
+  const int blocks = (N + cols_per_block - 1) / cols_per_block;
   mi::launch(kernel, dim3(blocks), dim3(WARPS * 32), smem, stream, out, x, w, M, N, K, ldo);
   MI_LAUNCH_OK("gemm_skinny");
   return 0;
 }
 
-template <int MT, int NT, bool HALF, typename TOut>
+template <int MT, int NT, bool HALF, typename TOut, bool SWIGLU = false>
 int pick_ksplit(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
                 cudaStream_t stream) {
   // As few warps per group of rows as still gives every SM about two blocks: long-lived warps that
   // stream many rows keep more bytes in flight than many short-lived blocks.  A function of N only,
   // so that the order of the additions behind an output does not depend on the batch.
   const int target = 296;
+  const int cols = SWIGLU ? 8 : NT * 8;
   int ks = 1;
-  while (ks < 8 && (N + (WARPS / ks) * NT * 8 - 1) / ((WARPS / ks) * NT * 8) < target) ks *= 2;
+  while (ks < 8 && (N + (WARPS / ks) * cols - 1) / ((WARPS / ks) * cols) < target) ks *= 2;
   if (K < 64 * ks) ks = 1;   // nothing to split
   switch (ks) {
-    case 1: return launch<MT, NT, 1, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
-    case 2: return launch<MT, NT, 2, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
-    case 4: return launch<MT, NT, 4, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
-    default: return launch<MT, NT, 8, HALF, TOut>(out, x, w, M, N, K, ldo, stream);
+    case 1: return launch<MT, NT, 1, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);
+    case 2: return launch<MT, NT, 2, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);
+    case 4: return launch<MT, NT, 4, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);
+    default: return launch<MT, NT, 8, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);
   }
 }
 
@@ -219,7 +260,29 @@ int dispatch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, i
               : pick_ksplit<4, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
 }
 
+// out[M, I] = silu(x * w[0:I]^T) * (x * w[I:2I]^T), bf16
+int dispatch_swiglu(__nv_bfloat16* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int I, int K, int ldo,
+                    cudaStream_t stream) {
+  if (M <= 8) return pick_ksplit<1, 2, true, __nv_bfloat16, true>(out, x, w, M, I, K, ldo, stream);
+  if (M <= 16) return pick_ksplit<1, 2, false, __nv_bfloat16, true>(out, x, w, M, I, K, ldo, stream);
+  if (M <= 32) return pick_ksplit<2, 2, false, __nv_bfloat16, true>(out, x, w, M, I, K, ldo, stream);
+  return pick_ksplit<4, 2, false, __nv_bfloat16, true>(out, x, w, M, I, K, ldo, stream);
+}
+
 }  // namespace
+
+// The gate-and-up product of a SwiGLU feed-forward with the activation in its epilogue:
+// out[M, I] = silu(x w_gate^T) * (x w_up^T), w = [w_gate; w_up] of 2I rows.  Both products are
+// rounded to bf16 before the activation, as mi_gemm_skinny_bf16 followed by mi_silu_mul rounds them.
+MI_API int mi_gemm_skinny_swiglu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo,
+                                      cudaStream_t stream) {
+  MI_REQUIRE(M >= 0 && M <= 64, "gemm_skinny_swiglu: M=%d is not in 0..64", M);
+  MI_REQUIRE(I > 0 && K > 0 && ldo >= I, "gemm_skinny_swiglu: bad sizes I=%d K=%d ldo=%d", I, K, ldo);
+  MI_REQUIRE(K % 8 == 0, "gemm_skinny_swiglu: K=%d must be a multiple of 8 (16-byte loads of bf16 rows)", K);
+  MI_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_skinny_swiglu: operands must be 16-byte aligned");
+  if (M == 0) return 0;
+  return dispatch_swiglu((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, I, K, ldo, stream);
+}
 
 MI_API int mi_gemm_skinny_bf16(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K,
                                int ldo, cudaStream_t stream) {

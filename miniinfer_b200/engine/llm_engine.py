@@ -79,7 +79,8 @@ class LLMEngine:
     self._next_id = 0
     self._tokens_host: Optional[torch.Tensor] = None
     self._tokens_dev: Optional[torch.Tensor] = None
-    self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0}
+    self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0,
+                  "host_schedule_s": 0.0, "host_launch_s": 0.0, "host_wait_s": 0.0, "host_update_s": 0.0}
 
   # ------------------------------------------------------------------ life cycle (API parity)
 
@@ -151,9 +152,11 @@ class LLMEngine:
   @torch.no_grad()
   def step(self) -> List[Dict[str, Any]]:
     """Schedules, runs and samples one step; returns the outputs of the requests that finished."""
+    t0 = time.perf_counter()
     out = self.scheduler.schedule()
     if not out.items:
       return []
+    t1 = time.perf_counter()
     items, sampling_reqs = [], []
     for it in out.items:
       n = len(it.tokens)
@@ -166,6 +169,7 @@ class LLMEngine:
     R = len(sampling_reqs)
     dev, host = self._token_buffers(max(R, 1))
     toks_dev = self.runner.step_and_sample(items, extras, Sampler.sample, dev, use_graphs=not self.config.enforce_eager)
+    t2 = time.perf_counter()
     self.stats["h2d_bytes"] += self.runner.last_h2d_bytes
     self.stats["launches"] += self.runner.last_launches
     if R:
@@ -175,11 +179,19 @@ class LLMEngine:
       toks = host[:R].tolist()
       sampled = {r.req_id: t for r, t in zip(sampling_reqs, toks)}
       self.stats["d2h_bytes"] += 4 * R
+    t3 = time.perf_counter()
     self.stats["steps"] += 1
     self.stats["prefill_tokens"] += out.num_prefill_tokens
     self.stats["decode_tokens"] += out.num_decode_tokens
     done = self.scheduler.update(out, sampled)
-    return [self._output_of(r) for r in done]
+    outs = [self._output_of(r) for r in done]
+    t4 = time.perf_counter()
+    # Host seconds by phase: deciding the step, describing and launching it, waiting for the tokens, book-keeping.
+    self.stats["host_schedule_s"] += t1 - t0
+    self.stats["host_launch_s"] += t2 - t1
+    self.stats["host_wait_s"] += t3 - t2
+    self.stats["host_update_s"] += t4 - t3
+    return outs
 
   def _output_of(self, req: Request) -> Dict[str, Any]:
     return {"text": self._decode(req.output_ids), "token_ids": list(req.output_ids), "request_id": req.req_id,

@@ -65,26 +65,44 @@ class _MetaBuffers:
       self.host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
       self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
 
-  def upload(self, arrays: "OrderedDict[str, np.ndarray]", fixed_capacity: bool = False) -> Dict[str, Tuple[int, int]]:
+  def begin(self) -> np.ndarray:
+    """The staging array, once the copy that last read it has finished."""
+    if self.copy_done is not None:
+      self.copy_done.synchronize()
+    return self.host.numpy()
+
+  def send(self, total: int) -> None:
+    """One host-to-device copy of the first ``total`` words."""
+    self.dev[:total].copy_(self.host[:total], non_blocking=True)
+    if self.device.type == "cuda":
+      if self.copy_done is None:
+        self.copy_done = torch.cuda.Event()
+      self.copy_done.record()
+    self.bytes_copied = 4 * total
+
+  @staticmethod
+  def layout(arrays: "OrderedDict[str, np.ndarray]") -> Tuple[Dict[str, Tuple[int, int]], int]:
     offsets: Dict[str, Tuple[int, int]] = {}
     total = 0
     for name, arr in arrays.items():
       offsets[name] = (total, len(arr))
       total += _pad4(len(arr))
+    return offsets, total
+
+  def upload(self, arrays: "OrderedDict[str, np.ndarray]", fixed_capacity: bool = False) -> Dict[str, Tuple[int, int]]:
+    offsets, total = self.layout(arrays)
     if fixed_capacity and total > self.host.numel():
       raise RuntimeError("step description is larger than the captured buffers")
-    self._ensure(total)
-    if self.copy_done is not None:
-      self.copy_done.synchronize()     # the staging array may still be feeding the previous copy
-    h = self.host.numpy()
+    if total > self.host.numel():
+      if self.copy_done is not None:
+        self.copy_done.synchronize()
+      self.copy_done = None
+      self._ensure(total)
+    h = self.begin()
     for name, arr in arrays.items():
       o, n = offsets[name]
       h[o:o + n] = arr
-    self.dev[:total].copy_(self.host[:total], non_blocking=True)
-    if self.device.type == "cuda":
-      self.copy_done = torch.cuda.Event()
-      self.copy_done.record()
-    self.bytes_copied = 4 * total
+    self.send(total)
     return offsets
 
 
@@ -101,6 +119,10 @@ class _DecodeGraph:
     self.tokens: Optional[torch.Tensor] = None
     self.launches = 0
     self.max_ctx_len = 0
+    # the description of a step with no live entry (all padding) and where each array lies in it
+    self.template: Optional[np.ndarray] = None
+    self.offsets: Dict[str, Tuple[int, int]] = {}
+    self.total = 0
 
 
 class ModelRunner:
@@ -324,19 +346,22 @@ class ModelRunner:
     starts = self._check_and_reserve(items)
     B = len(items)
     try:
-      arrays = self._padded(self._describe(items, starts, sampling), bucket)
       # the split-KV grid is part of the capture: one graph per (bucket, context class)
-      longest = int(arrays["ctx_len"].max())
+      longest = max(starts) + 1
       ctx_class = min(self.cache.max_model_len, -(-longest // GRAPH_CONTEXT_STEP) * GRAPH_CONTEXT_STEP)
       g = self._graphs.get((bucket, ctx_class))
       if g is None:
         g = self._graphs[(bucket, ctx_class)] = _DecodeGraph(bucket, self.device)
         g.max_ctx_len = ctx_class
-      offsets = g.meta.upload(arrays, fixed_capacity=g.graph is not None)
-      self.last_h2d_bytes = g.meta.bytes_copied
-      self.cache.sync()
       if g.graph is None:
-        self._capture(g, arrays, offsets, sample_fn)
+        arrays = self._decode_layout(g, self._describe(items, starts, sampling))
+        g.meta.upload(arrays)
+        self.cache.sync()
+        self._capture(g, arrays, g.offsets, sample_fn)
+      else:
+        self._fill_decode(g, items, starts, sampling)
+        self.cache.sync()
+      self.last_h2d_bytes = g.meta.bytes_copied
       g.graph.replay()
       self.last_launches = g.launches
     except BaseException:
@@ -344,6 +369,44 @@ class ModelRunner:
       raise
     self._finish(items, True)
     return g.tokens[:B]
+
+  def _decode_layout(self, g: _DecodeGraph, described: "OrderedDict[str, np.ndarray]") -> "OrderedDict[str, np.ndarray]":
+    """Fixes where each array of a decode-only step lies in the graph's buffers and keeps the
+    description of a step without live entries; returns ``described`` padded to the bucket."""
+    arrays = self._padded(described, g.bucket)
+    empty = self._padded(OrderedDict((k, v[:0]) for k, v in described.items()), g.bucket)
+    g.offsets, g.total = g.meta.layout(arrays)
+    g.template = np.zeros(g.total, dtype=np.int32)
+    for k, v in empty.items():
+      o, n = g.offsets[k]
+      g.template[o:o + n] = v
+    return arrays
+
+  def _fill_decode(self, g: _DecodeGraph, items, starts, sampling) -> None:
+    """A decode-only step written straight into the graph's staging array: the entries that differ
+    from step to step (token, position, cache slot, length, request slot, sampling options) over the
+    all-padding description.  Gives the same words as ``_padded(_describe(...))``."""
+    cache = self.cache
+    B = len(items)
+    h = g.meta.begin()
+    h[:g.total] = g.template
+    off = g.offsets
+
+    def put(name, values):
+      o, n = off[name]
+      if len(values) > n:
+        raise RuntimeError("step description is larger than the captured buffers")
+      h[o:o + len(values)] = values
+
+    put("ids", [it.tokens[0] for it in items])
+    put("positions", starts)
+    put("ctx_len", [s + 1 for s in starts])
+    put("seq_slot", [cache.slot_of(it.req_id) for it in items])
+    for gi in range(len(cache.paged_groups)):
+      put(f"slot_mapping{gi}", [cache.slot_at(it.req_id, gi, s) for it, s in zip(items, starts)])
+    for k, v in sampling.items():
+      put(f"extra:{k}", v if v.dtype == np.int32 else v.view(np.int32))
+    g.meta.send(g.total)
 
   def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn) -> None:
     # every length of the context class must be served by the captured launch: size the split-KV grid for it

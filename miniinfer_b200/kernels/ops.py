@@ -184,6 +184,25 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
     _ptr(kv_layer), T, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(eps), _stream()))
 
 
+def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace) -> None:
+  """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
+  bfloat16 with M <= 64: one kernel, the activation in the product's epilogue.  Otherwise the product
+  into a buffer of ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
+  M, K = x.shape
+  I = out.shape[1]
+  if w.shape != (2 * I, K) or out.shape[0] != M or out.dtype != x.dtype:
+    raise KernelError(f"linear_swiglu: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if M == 0:
+    return
+  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_M:
+    lib = common_lib()
+    _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
+    return
+  gu = workspace.buffer("gate_up", (M, 2 * I), x.dtype)
+  linear(gu, x, w)
+  silu_mul(out, gu)
+
+
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
   lib = common_lib()
   T, I = out.shape

@@ -30,10 +30,8 @@ class SwiGLUFeedForward(FeedForward):
 
   def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
     T = x.shape[0]
-    gu = ctx.ws.buffer("gate_up", (T, 2 * self.intermediate_size), ctx.dtype)
-    ops.linear(gu, x, self.gate_up)
     act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)
-    ops.silu_mul(act, gu)
+    ops.linear_swiglu(act, x, self.gate_up, ctx.ws)
     out = ctx.ws.buffer("ffn_out", (T, self.hidden_size), ctx.dtype)
     ops.linear(out, act, self.down)
     return out

@@ -129,3 +129,37 @@ def test_step_refuses_bad_input(cpu_kernels, model_dirs):
     r.runner.step([StepItem("a", list(range(40)), []), StepItem("b", list(range(40)), [])])
   assert r.cache.length_of("a") == 0 and r.cache.free_pages() == [4]
   r.cache.check_invariants()
+
+
+def test_decode_description_written_in_place_equals_the_general_one(cpu_kernels, model_dirs):
+  """The decode-only steps of a captured graph write their description straight into the staging
+  array; word for word it must be what the general description, padded, gives."""
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.engine.runner import _DecodeGraph
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  r = make_runner(model_dirs("A"), 16, 256)
+  run = r.runner
+  lengths = {"a": 5, "b": 33, "c": 16}
+  for rid, n in lengths.items():
+    r.cache.admit(rid)
+    run.step([StepItem(rid, list(range(1, n + 1)), [])])
+  g = _DecodeGraph(4, torch.device("cpu"))
+  params = [SamplingParams(temperature=0.7, top_k=5, top_p=0.9), SamplingParams(), SamplingParams(temperature=1.3)]
+  for step, rids in enumerate((["a", "b", "c"], ["c", "a"], ["b"], ["b", "c", "a"])):
+    items = [StepItem(rid, [7 + step + i], (0,)) for i, rid in enumerate(rids)]
+    packed = Sampler.pack(params[:len(rids)], [11, 2 ** 40 + 5, 3][:len(rids)], [step] * len(rids))
+    starts = run._check_and_reserve(items)
+    general = run._padded(run._describe(items, starts, packed), 4)
+    if g.template is None:
+      run._decode_layout(g, run._describe(items, starts, packed))
+    want = np.zeros(g.total, dtype=np.int32)
+    for k, v in general.items():
+      o, n = g.offsets[k]
+      assert n == len(v)
+      want[o:o + n] = v
+    run._fill_decode(g, items, starts, packed)
+    assert np.array_equal(g.meta.host.numpy()[:g.total], want), (step, rids)
+    run._finish(items, True)
+  for rid in lengths:
+    r.cache.release_request(rid)
+  r.cache.check_invariants()

@@ -150,6 +150,9 @@ CASES = [
   ([(333, 333), (100, 1)], 3, 1, 80, 8, 50),
   ([(150, 1), (150, 150)], 2, 2, 256, 64, None),
   ([(260, 1), (150, 150)], 8, 1, 16, 32, None),
+  # exactly 8 and 16 query heads per kv head in the TMA decode kernel (one full pass, two full passes)
+  ([(500, 1), (70, 1), (64, 1)], 16, 2, 128, 64, None),
+  ([(300, 1), (129, 1)], 16, 1, 64, 64, 100),
 ]
 
 
@@ -198,6 +201,39 @@ def test_silu_mul(ops, dtype, T, I):
   ops.silu_mul(out, gu)
   ref.silu_mul(want, gu)
   assert torch.allclose(out.float(), want.float(), atol=1e-6 if dtype == torch.float32 else 2e-2, rtol=1e-2 if dtype == torch.bfloat16 else 1e-5)
+
+
+class _Scratch:
+  def buffer(self, name, shape, dtype):
+    return torch.empty(shape, dtype=dtype, device=DEV)
+
+
+@pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (7, 8), (333, 2048)])
+def test_linear_swiglu(ops, I, K):
+  """The fused gate-and-up product against product + activation (which it must match up to the
+  order of its K-sums), and a row's value must not depend on the other rows."""
+  w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.08)
+  xs = rnd(100, K, dtype=torch.bfloat16, seed=1)
+  full = None
+  for M in (64, 1, 3, 8, 9, 16, 17, 33, 100):       # 100 rows: the unfused path
+    x = xs[:M].contiguous()
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    want = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ref.linear(gu, x, w)
+    ref.silu_mul(want, gu)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(out, x, w, _Scratch())
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
+    if M == 64:
+      full = out
+    elif M < 64:
+      assert torch.equal(out, full[:M]), "a row's value must not depend on the other rows"
+  x32, w32 = xs[:5].float(), w.float()
+  out32 = torch.empty(5, I, device=DEV)
+  ops.linear_swiglu(out32, x32, w32, _Scratch())
+  g = x32 @ w32.t()
+  assert torch.allclose(out32, torch.nn.functional.silu(g[:, :I]) * g[:, I:], atol=1e-4, rtol=1e-4)
 
 
 def _sample(ops, logits, temp, k, p, seed, counter):

@@ -100,6 +100,12 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
   out.copy_(res.reshape(T, nh * hd).to(out.dtype))
 
 
+def linear_swiglu(out, x, w, workspace):
+  gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype)
+  linear(gu, x, w)
+  silu_mul(out, gu)
+
+
 def silu_mul(out, gate_up):
   I = out.shape[1]
   g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
@@ -153,5 +159,5 @@ def install(monkeypatch) -> None:
   """Puts the statements above in place of the CUDA kernels (CPU tests of the host-side logic)."""
   from miniinfer_b200.kernels import ops
 
-  for name in ("embedding", "add_rmsnorm", "linear", "qk_norm_rope_store", "attention", "silu_mul", "sample"):
+  for name in ("embedding", "add_rmsnorm", "linear", "linear_swiglu", "qk_norm_rope_store", "attention", "silu_mul", "sample"):
     monkeypatch.setattr(ops, name, globals()[name])
