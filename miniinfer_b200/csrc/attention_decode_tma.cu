@@ -222,15 +222,18 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
     __syncwarp();
   }
   __syncthreads();
-  mi::grid_dependency_sync();
 
   if (warp == CONSUMERS) {
     // ------------------------------------------------------------------ producer
     // The step's tiles - all (request, kv head, 64-key tile) triples in that order - are dealt out
     // evenly: block c takes the tiles bound(c) .. bound(c + 1), bound(c) = floor(c * total / blocks).
     // A (request, kv head) that falls into one block is finished there; one that straddles blocks
-    // becomes one item in each, with partial results.  One lane walks this block's range.
-    if (lane != 0) return;
+    // becomes one item in each, with partial results.  The whole warp walks this block's range in
+    // step (so that its lanes can fetch a run of page numbers at once); lane 0 alone talks to the
+    // barriers and the copy engines.  What describes an item comes from arrays the host uploaded,
+    // so the warp works out its first item before it waits for the preceding kernel, whose output
+    // (the queries, this step's keys and values) only the copies read.
+    bool waited = false;
     const long long total = (long long)prefix_s[a.n_dec] * a.nkv;
     // with fewer tiles than blocks only the first `total` blocks work, one tile each
     const long long nblk = min((long long)gridDim.x, total);
@@ -272,40 +275,56 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
       const int split = (int)blockIdx.x - c_first;
 
       const int qp = it % NI;
-      mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
-      Item d;
-      d.nb = nb; d.e = e; d.kvh = kvh; d.split = split; d.n_splits = n_splits;
-      d.j0 = j0; d.k_lo = k_lo; d.k_end = k_end; d.row = row;
-      items[qp] = d;
-      // the query heads of this kv head are neighbours in the row: one copy
-      mbar_expect_tx(&qfull[qp], (uint32_t)(G * HD * 2));
-      bulk_load_1d(q_s + (size_t)qp * a.gp * HD, a.q_base + (size_t)row * a.q_stride + (size_t)kvh * G * HD, (uint32_t)(G * HD * 2), &qfull[qp]);
-
-      for (int b = 0; b < nb; ++b, ++blk) {
-        const int s = blk % a.stages;
-        mbar_wait(&empty[s], ((blk / a.stages) & 1) ^ 1, abort, a.status);
-        const int jb = j0 + b * BK;
-        const int page = bt[jb / a.page_size];
-        const int y_k = ((page * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
-        const int y_v = y_k + a.nkv * a.page_size;
-        unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
+      int page = nb > 0 ? bt[(j0 + min(lane, nb - 1) * BK) / a.page_size] : 0;   // the pages of the first 32 tiles
+      if (!waited) {
+        mi::grid_dependency_sync();
+        waited = true;
+      }
+      if (lane == 0) {
+        mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
+        Item d;
+        d.nb = nb; d.e = e; d.kvh = kvh; d.split = split; d.n_splits = n_splits;
+        d.j0 = j0; d.k_lo = k_lo; d.k_end = k_end; d.row = row;
+        items[qp] = d;
+        // the query heads of this kv head are neighbours in the row: one copy
+        mbar_expect_tx(&qfull[qp], (uint32_t)(G * HD * 2));
+        bulk_load_1d(q_s + (size_t)qp * a.gp * HD, a.q_base + (size_t)row * a.q_stride + (size_t)kvh * G * HD, (uint32_t)(G * HD * 2), &qfull[qp]);
+      }
+      for (int c0 = 0; c0 < nb; c0 += 32) {
+        if (c0 > 0) page = bt[(j0 + min(c0 + lane, nb - 1) * BK) / a.page_size];
+        const int run = min(32, nb - c0);
+        for (int u = 0; u < run; ++u, ++blk) {
+          const int pg = __shfl_sync(0xffffffffu, page, u);
+          if (lane == 0) {
+            const int s = blk % a.stages;
+            mbar_wait(&empty[s], ((blk / a.stages) & 1) ^ 1, abort, a.status);
+            const int jb = j0 + (c0 + u) * BK;
+            const int y_k = ((pg * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
+            const int y_v = y_k + a.nkv * a.page_size;
+            unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
+            mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
 #pragma unroll
-        for (int x = 0; x < NBOX; ++x) {
-          tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
-          tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+            for (int x = 0; x < NBOX; ++x) {
+              tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
+              tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+            }
+          }
         }
       }
       ++it;
       t += nb;
     }
+    if (!waited) mi::grid_dependency_sync();
     // no more items
-    const int qp = it % NI;
-    mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
-    items[qp].nb = -1;
-    mbar_arrive(&qfull[qp]);
+    if (lane == 0) {
+      const int qp = it % NI;
+      mbar_wait(&qempty[qp], ((it / NI) & 1) ^ 1, abort, a.status);
+      items[qp].nb = -1;
+      mbar_arrive(&qfull[qp]);
+    }
     return;
   }
+  mi::grid_dependency_sync();   // consumers and the epilogue warp: before anything a kernel wrote is read, or anything is written
 
   if (warp == CONSUMERS + 1) {
     // ------------------------------------------------------------------ epilogue warp

@@ -1,0 +1,517 @@
+// Prefill attention over the paged cache in bf16 on the fifth-generation tensor cores (tcgen05):
+// the kernel for head sizes 64 and 128 and page sizes that are multiples of 64.  The other sizes
+// take the mma.sync kernel of attention_prefill.cu, which computes the same thing.
+//
+// A block owns 128 query rows that share one kv head - 128 tokens of one query head, or, when the
+// number of query heads per kv head is even, 64 tokens of two neighbouring heads (so K and V are
+// read once for both) - and walks the keys the mask allows in tiles of 128:
+//   * a producer warp asks the TMA engine for the Q rows once and for K and V tile by tile (boxes
+//     of 64 rows x 64 elements, one page and one half of the head size each, written in the
+//     128-byte swizzle), two stages ahead, counted on mbarriers;
+//   * one thread of the MMA warp issues S = Q K^T (tcgen05.mma, M = 128, N = 128, K = 16 per
+//     instruction, operands described in shared memory, K-major) into one of two 128-column
+//     accumulators in tensor memory, and, once the softmax warps have written P, O_tile = P V
+//     (V is MN-major: dims contiguous, as the cache stores it) into a third; tcgen05.commit tells
+//     the mbarriers when the products are done.  S of the next tile is issued before P V of this
+//     one, so the tensor cores work while the softmax warps do;
+//   * eight softmax warps - two threads per query row (tensor-memory lane = row), each with half of
+//     the row's columns - read S with tcgen05.ld (first for the row maximum, again for the
+//     exponentials), keep the running maximum and sum and their half of the output row in
+//     registers in float32, base 2 with the scale folded in, fold the finished O_tile of the
+//     previous tile into the output row, and write P in bf16 to shared memory in the layout the
+//     second product reads.
+// Causal and window masks go by absolute position; tiles that the mask does not touch skip the
+// comparisons.  Rows past the end of the item's tokens are computed on whatever the Q copy brought
+// and never stored.
+//
+// Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
+// ends all later waits at once and sets the status word, and the block runs to its end, where the
+// tensor memory is given back.
+//
+// Stands where the reference calls flash_attn_varlen_func / FlashInfer's prefill wrapper
+// (miniinfer/layers/attention_backend/flashattention_backend.py:441-452,
+// flashinfer_backend.py:352-374).
+//
+// Compiled once per head size: -DMI_HEAD_DIM=<head size>.
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+
+#ifndef MI_HEAD_DIM
+#error "compile with -DMI_HEAD_DIM=<head size>"
+#endif
+
+#if MI_HEAD_DIM == 64 || MI_HEAD_DIM == 128
+
+namespace {
+
+constexpr int HD = MI_HEAD_DIM;
+constexpr int BM = 128;                       // query rows of a block
+constexpr int BN = 128;                       // keys of a tile
+constexpr int STAGES = 2;
+constexpr int NHALF = HD / 64;                // 64-element (128-byte) halves of a row
+constexpr int HALF_BYTES = 128 * 128;         // 128 rows x 128 bytes
+constexpr int Q_BYTES = NHALF * HALF_BYTES;
+constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
+constexpr int STAGE_BYTES = 2 * K_BYTES;
+constexpr int P_BYTES = 2 * HALF_BYTES;       // 128 rows x 128 keys
+constexpr int SOFTMAX_WARPS = 8;                // two threads per query row, half of the columns each
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+constexpr int THREADS = 10 * 32;
+constexpr int TMEM_COLS = 512;
+constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+constexpr int WAIT_LIMIT = 1 << 22;
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + 256 + 2 * 2 * BM * sizeof(float);
+
+struct Args {
+  __nv_bfloat16* out;            // [T, nh * HD]
+  const int* block_table;
+  int bt_stride;
+  const int* tiles;              // [n_tiles, 2]: item, first row of the tile within the item's new tokens (multiples of 64)
+  const int* q_start;
+  const int* q_len;
+  const int* ctx_len;
+  const int* seq_slot;
+  int* status;
+  int n_tiles, nh, nkv, page_size, window;
+  int hpt;                       // query heads of a block: 1 (128 tokens) or 2 (64 tokens each)
+  float scale_log2;              // scale * log2(e)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait.  `abort` is a flag in shared memory: once any wait has run out, all waits return.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return;
+    if ((i & 63) == 63 && *abort) return;
+  }
+  *abort = 1;
+  atomicExch(status, 2);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// ---- tensor memory and tcgen05
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_in_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16 in, float32 out; one thread issues it for the block.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane of the warp).
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor, 128-byte swizzle: start address, leading and stride byte offsets
+// in 16-byte units, descriptor version 1 (bits 46..47), layout type 2 = 128-byte swizzle (bits 61..63).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: float32 accumulator (bits 4..5 = 1), bf16 A and B (bits 7..9
+// and 10..12 = 1), B K-major or MN-major (bit 16), N / 8 at bits 17..22, M / 16 at bits 24..28.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
+  mi::grid_dependency_sync();
+  // ---- which rows and which keys (uniform over the block)
+  const int tile = a.n_tiles - 1 - (int)blockIdx.x;       // later tiles see more keys: they start first
+  const int item = a.tiles[2 * tile], o = a.tiles[2 * tile + 1];
+  if (a.hpt == 1 && (o & 64)) return;                     // the block of the tile before covers these 64 tokens too
+  const int G = a.nh / a.nkv;
+  const int head0 = (int)blockIdx.y * a.hpt;
+  const int kvh = head0 / G;
+  const int qlen = a.q_len[item], ctx = a.ctx_len[item];
+  const int start = ctx - qlen;                           // position of the item's first new token
+  const int tok_per_block = BM / a.hpt;
+  const int rows_tok = min(tok_per_block, qlen - o);      // tokens of this block that exist
+  const int p_first = start + o, p_last = start + o + rows_tok - 1;
+  const int lo_first = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+  const int lo_last = a.window > 0 ? max(0, p_last - a.window + 1) : 0;
+  const int t_begin = lo_first / BN;
+  const int n = p_last / BN - t_begin + 1;                // key tiles to walk
+  const int row0 = a.q_start[item] + o;                   // the block's first row in the step
+  const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* kv_s = q_s + Q_BYTES;                    // [stage][K, V]
+  unsigned char* p_s = kv_s + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + STAGES;
+  uint64_t* s_full = kv_empty + STAGES;                   // [2]
+  uint64_t* s_empty = s_full + 2;                         // [2]
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* o_full = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(bars + 32);       // [2][2][BM]: what the two threads of a row tell each other
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&s_empty[b], SOFTMAX_WARPS * 32);
+    }
+    mbar_init(p_full, SOFTMAX_WARPS * 32);
+    mbar_init(o_full, 1);
+    *abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == PRODUCER_WARP) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
+#pragma unroll
+      for (int rb = 0; rb < 2; ++rb) {
+        const int head = head0 + (a.hpt == 2 ? rb : 0);
+        const int y = row0 + (a.hpt == 2 ? 0 : 64 * rb);
+#pragma unroll
+        for (int h = 0; h < NHALF; ++h)
+          tma_load_2d(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
+      }
+      for (int i = 0; i < n; ++i) {
+        const int s = i % STAGES;
+        mbar_wait(&kv_empty[s], ((i / STAGES) & 1) ^ 1, abort, a.status);
+        if (*abort) break;
+        unsigned char* k_dst = kv_s + (size_t)s * STAGE_BYTES;
+        unsigned char* v_dst = k_dst + K_BYTES;
+        mbar_expect_tx(&kv_full[s], (uint32_t)STAGE_BYTES);
+        const int key0 = (t_begin + i) * BN;
+#pragma unroll
+        for (int pg = 0; pg < 2; ++pg) {
+          const int key = key0 + 64 * pg;
+          const int page = bt[min(key / a.page_size, a.bt_stride - 1)];   // past the context: the dummy page, masked below
+          const int y_k = ((page * 2) * a.nkv + kvh) * a.page_size + key % a.page_size;
+          const int y_v = y_k + a.nkv * a.page_size;
+#pragma unroll
+          for (int h = 0; h < NHALF; ++h) {
+            tma_load_2d(k_dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y_k, &kv_full[s]);
+            tma_load_2d(v_dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y_v, &kv_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
+      constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto issue_s = [&](int i) {
+        const int s = i % STAGES, b = i & 1;
+        mbar_wait(&kv_full[s], (i / STAGES) & 1, abort, a.status);
+        mbar_wait(&s_empty[b], ((i / 2) & 1) ^ 1, abort, a.status);
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
+        const uint32_t d = tmem_base + (b ? S_COL1 : S_COL0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
+          tc_mma(d, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[b]);
+      };
+      mbar_wait(q_full, 0, abort, a.status);
+      if (!*abort) issue_s(0);
+      for (int j = 0; j < n && !*abort; ++j) {
+        if (j + 1 < n) issue_s(j + 1);
+        mbar_wait(p_full, j & 1, abort, a.status);
+        if (*abort) break;
+        tc_fence_after();
+        const int s = j % STAGES;
+        const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          const uint32_t p_off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
+          tc_mma(tmem_base + O_COL, smem_desc(p_addr + p_off, 16, 1024),
+                 smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024), IDESC_PV, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(o_full);
+        tc_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: two threads per row
+    // Warps q and q + 4 read the tensor-memory lanes 32q .. 32q + 31 (a warp reaches the lanes of
+    // its number mod 4); the first takes the columns 0..63 of a row of S and the lower half of the
+    // output row, the second the rest.  They tell each other their half's maximum (and at the end
+    // its sum) through shared memory, with a barrier of their 64 threads.
+    const int q = warp & 3, ch = warp >> 2;
+    const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
+    const int tok = a.hpt == 2 ? (r & 63) : r;
+    const int head = head0 + (a.hpt == 2 ? (r >> 6) : 0);
+    const bool row_valid = tok < rows_tok;
+    const int pos = row_valid ? start + o + tok : p_last;
+    const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+    constexpr int OD = HD / 2;                             // output columns of this thread
+    float o_reg[OD];
+#pragma unroll
+    for (int d = 0; d < OD; ++d) o_reg[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float sc = a.scale_log2;
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };
+
+    auto fold = [&]() {                                    // the finished P V of a tile joins the output row
+#pragma unroll
+      for (int c = 0; c < OD / 32; ++c) {
+        float v[32];
+        tmem_ld32(v, t_lane + O_COL + ch * OD + c * 32);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_reg[c * 32 + i] += v[i];
+      }
+    };
+
+    for (int j = 0; j < n; ++j) {
+      const int b = j & 1;
+      const int key0 = (t_begin + j) * BN + ch * 64;       // first key of this thread's columns
+      const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
+      // (after a wait has run out the loop goes on without waiting, so that the two warps of a
+      // row still meet at every pair barrier; what it computes then is never stored)
+      mbar_wait(&s_full[b], (j / 2) & 1, abort, a.status);
+      tc_fence_after();
+      const uint32_t s_addr = t_lane + (b ? S_COL1 : S_COL0) + ch * 64;
+      // pass 1: the row's maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(v, s_addr + c * 32);
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            if (key >= lo_r && key <= pos) mx = fmaxf(mx, v[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+        }
+      }
+      xch[(b * 2 + ch) * BM + r] = mx;
+      pair_sync();
+      mx = fmaxf(mx, xch[(b * 2 + (ch ^ 1)) * BM + r]);
+      const float m_new = fmaxf(m_run, mx * sc);           // the scale is positive
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      m_run = m_new;
+      if (j > 0) {
+        mbar_wait(o_full, (j - 1) & 1, abort, a.status);   // P V of the tile before is done: P and the O tile are free
+        tc_fence_after();
+        fold();
+      }
+      if (alpha != 1.f) {
+        l_run *= alpha;
+#pragma unroll
+        for (int d = 0; d < OD; ++d) o_reg[d] *= alpha;
+      }
+      // pass 2: exponentials, their sum, P in bf16 to shared memory (K-major, 128-byte swizzle);
+      // this thread's 64 keys are one 128-byte row of the key half `ch`
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(v, s_addr + c * 32);
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + c * 32 + i;
+          float x = fmaf(v[i], sc, -m_use);
+          if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
+          float pe;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
+          v[i] = pe;
+          part[i & 3] += pe;
+        }
+        l_run += (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {                   // 8 keys = 16 bytes at a time
+          const int c8 = c * 4 + q4;                       // 16-byte chunk of this thread's 128 bytes
+          const uint32_t dst = smem_u32(p_s) + (uint32_t)(ch * HALF_BYTES + r * 128 + ((c8 ^ (r & 7)) << 4));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(v[q4 * 8], v[q4 * 8 + 1])),
+                       "r"(pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3])), "r"(pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5])),
+                       "r"(pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7])) : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&s_empty[b]);                            // S of this tile is read: the accumulator may be written again
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is visible to the tensor cores
+      mbar_arrive(p_full);
+    }
+    mbar_wait(o_full, (n - 1) & 1, abort, a.status);
+    tc_fence_after();
+    fold();
+    // the row's sum: both halves
+    xch[((n & 1) * 2 + ch) * BM + r] = l_run;
+    pair_sync();
+    l_run += xch[((n & 1) * 2 + (ch ^ 1)) * BM + r];
+    if (row_valid && !*abort) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = a.out + (size_t)(row0 + tok) * a.nh * HD + (size_t)head * HD + ch * OD;
+#pragma unroll
+      for (int d = 0; d < OD; d += 8) {
+        uint4 w;
+        w.x = pack_bf16(o_reg[d] * inv, o_reg[d + 1] * inv);
+        w.y = pack_bf16(o_reg[d + 2] * inv, o_reg[d + 3] * inv);
+        w.z = pack_bf16(o_reg[d + 4] * inv, o_reg[d + 5] * inv);
+        w.w = pack_bf16(o_reg[d + 6] * inv, o_reg[d + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + d) = w;
+      }
+    }
+  }
+  // ---- teardown: every tensor-memory access is done, then the columns go back
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+MI_API int mi_attention_prefill_tc_supported() { return 1; }
+
+// Describes the step's fused QKV rows - [rows, width] bf16, row-major - to the TMA engine: boxes of
+// 64 rows x 64 elements, 128-byte swizzle, zeros past the last row.  `out_map` receives 128 bytes.
+MI_API int mi_qkv_tensor_map(void* out_map, const void* qkv, long long rows, long long width) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return mi_fail("qkv_tensor_map: the driver does not offer cuTensorMapEncodeTiled");
+    encode = (EncodeFn)fn;
+  }
+  MI_REQUIRE(((uintptr_t)qkv % 16) == 0 && rows > 0 && width >= 64 && width % 8 == 0,
+             "qkv_tensor_map: rows=%lld, width=%lld (a multiple of 8, at least 64) or the address do not fit", rows, width);
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  const cuuint32_t box[2] = {64, 64};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mi_fail("qkv_tensor_map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  memcpy(out_map, &map, sizeof(map));
+  return 0;
+}
+
+// q_map: mi_qkv_tensor_map of the step's QKV rows; kv_map: mi_kv_tensor_map of the layer's cache.
+// status: one word, set to 2 if a bounded wait ran out.
+MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_map, const int* block_table, int bt_stride,
+                                   const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
+                                   const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
+                                   cudaStream_t stream) {
+  MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
+  MI_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page_size=%d must be a multiple of 64", page_size);
+  MI_REQUIRE(scale > 0.f, "attention_prefill_tc: the scale must be positive");
+  MI_REQUIRE(nh <= 65535, "attention_prefill_tc: too many heads for one launch");
+  if (n_tiles == 0) return 0;
+  Args a;
+  a.out = (__nv_bfloat16*)out;
+  a.block_table = block_table;
+  a.bt_stride = bt_stride;
+  a.tiles = tiles;
+  a.q_start = q_start;
+  a.q_len = q_len;
+  a.ctx_len = ctx_len;
+  a.seq_slot = seq_slot;
+  a.status = status;
+  a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
+  a.hpt = ((nh / nkv) % 2 == 0) ? 2 : 1;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (err != cudaSuccess) return mi_fail("attention_prefill_tc: cannot get %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(err));
+    configured = true;
+  }
+  CUtensorMap qm, km;
+  memcpy(&qm, q_map, sizeof(qm));
+  memcpy(&km, kv_map, sizeof(km));
+  mi::launch(attention_prefill_tc_kernel, dim3(n_tiles, nh / a.hpt), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
+  MI_LAUNCH_OK("attention_prefill_tc");
+  return 0;
+}
+
+#else  // other head sizes have no tcgen05 kernel
+
+MI_API int mi_attention_prefill_tc_supported() { return 0; }
+MI_API int mi_qkv_tensor_map(void*, const void*, long long, long long) { return mi_fail("qkv_tensor_map: head size %d has no tcgen05 kernel", MI_HEAD_DIM); }
+MI_API int mi_attention_prefill_tc(void*, const void*, const void*, const int*, int, const int*, int, const int*, const int*, const int*,
+                                   const int*, int*, int, int, int, float, int, cudaStream_t) {
+  return mi_fail("attention_prefill_tc: head size %d has no tcgen05 kernel", MI_HEAD_DIM);
+}
+
+#endif

@@ -181,6 +181,8 @@ class LLMEngine:
       self.stats["d2h_bytes"] += 4 * R
     t3 = time.perf_counter()
     self.stats["steps"] += 1
+    if self.stats["steps"] % 256 == 0:
+      self.runner.check_status()
     self.stats["prefill_tokens"] += out.num_prefill_tokens
     self.stats["decode_tokens"] += out.num_decode_tokens
     done = self.scheduler.update(out, sampled)
@@ -224,6 +226,7 @@ class LLMEngine:
           bar.update(1)
     if bar is not None:
       bar.close()
+    self.runner.check_status()
     for rid in ids:
       self._requests.pop(rid, None)
     return [results[rid] for rid in ids]

@@ -66,6 +66,7 @@ class TraceRunner:
         logits = out.float().cpu().numpy().astype("<f4", copy=False)
       elif self.device.type == "cuda":
         torch.cuda.synchronize()
+      self.runner.check_status()
     for rid in record.get("end", []):
       if self.cache.has_request(rid):
         self.cache.release_request(rid)

@@ -427,5 +427,13 @@ class ModelRunner:
     g.launches = ops.launch_count() - before
     g.graph = graph
 
+  def check_status(self) -> None:
+    """Raises if a bounded wait inside a kernel ran out since the buffers were made (the step's
+    results are then not to be trusted).  Reads a few words from the device."""
+    for ws in [self.ws] + [g.ws for g in self._graphs.values()]:
+      code = ops.device_status(ws)
+      if code:
+        raise ops.KernelError(f"a bounded wait inside an attention kernel ran out (status {code})")
+
   def num_graphs(self) -> int:
     return sum(1 for g in self._graphs.values() if g.graph is not None)

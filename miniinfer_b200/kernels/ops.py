@@ -21,7 +21,9 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
-SKINNY_MAX_M = 64
+SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
+SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
+_MM_F32_OUT: Optional[bool] = None   # whether torch.mm writes float32 from bf16 operands into a given tensor
 
 
 class KernelError(RuntimeError):
@@ -127,10 +129,25 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Te
                                  ctypes.c_float(eps), int(bool(write_back)), _stream()))
 
 
-def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+def _mm_f32_out_works(device) -> bool:
+  """Tried once: bf16 x bf16 -> float32 through cuBLAS, written into a tensor the caller owns."""
+  global _MM_F32_OUT
+  if _MM_F32_OUT is None:
+    try:
+      a = torch.ones(32, 16, dtype=torch.bfloat16, device=device)
+      o = torch.empty(32, 32, dtype=torch.float32, device=device)
+      torch.mm(a, a.t(), out_dtype=torch.float32, out=o)
+      _MM_F32_OUT = bool((o == 16).all().item())
+    except (TypeError, RuntimeError, NotImplementedError):
+      _MM_F32_OUT = False
+  return _MM_F32_OUT
+
+
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bool = False) -> None:
   """out[M, N] = x[M, K] @ w[N, K]^T.  float32 operands: this package's fp32 FMA kernel (out float32).
-  bfloat16 operands: its skinny tensor-core kernel for M <= 64 (out bf16 or fp32), cuBLAS above
-  (out bf16; an fp32 out is produced in slices of 64 rows by the skinny kernel)."""
+  bfloat16 operands: its skinny tensor-core kernel for M <= 16 (out bf16 or fp32; a row's value does
+  not depend on the other rows), cuBLAS above (where the reference uses it for every product).
+  ``force_skinny``: the skinny kernel for any M (in slices of 64 rows)."""
   M, K = x.shape
   N = w.shape[0]
   if w.shape[1] != K or out.shape != (M, N):
@@ -143,17 +160,24 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
     return
   if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
     raise KernelError(f"linear: operands must both be float32 or both bfloat16, got {x.dtype} and {w.dtype}")
-  if M <= SKINNY_MAX_M:
+  if M <= SKINNY_BEST_M or (force_skinny and M <= SKINNY_MAX_M):
     _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, N, _stream()))
-  elif out.dtype == torch.bfloat16:
-    if not (out.is_cuda and out.is_contiguous()):
-      raise KernelError("linear: out must be a contiguous CUDA tensor")
-    torch.matmul(x, w.t(), out=out)
-  else:
-    for m0 in range(0, M, SKINNY_MAX_M):
-      m1 = min(M, m0 + SKINNY_MAX_M)
-      _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out[m0:m1]), _dt(out), _ptr(x[m0:m1]), _ptr(w), m1 - m0, N, K, N,
-                                          _stream()))
+    return
+  if not force_skinny:
+    if not (out.is_cuda and out.is_contiguous() and x.is_contiguous() and w.is_contiguous()):
+      raise KernelError("linear: operands and out must be contiguous CUDA tensors")
+    if K % 8 != 0:
+      raise KernelError(f"linear: K={K} must be a multiple of 8 (16-byte loads of bf16 rows)")
+    if out.dtype == torch.bfloat16:
+      torch.matmul(x, w.t(), out=out)
+      return
+    if out.dtype == torch.float32 and _mm_f32_out_works(out.device):
+      torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+      return
+  for m0 in range(0, M, SKINNY_MAX_M):
+    m1 = min(M, m0 + SKINNY_MAX_M)
+    _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out[m0:m1]), _dt(out), _ptr(x[m0:m1]), _ptr(w), m1 - m0, N, K, N,
+                                        _stream()))
 
 
 def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
@@ -184,9 +208,9 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
     _ptr(kv_layer), T, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(eps), _stream()))
 
 
-def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace) -> None:
+def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
-  bfloat16 with M <= 64: one kernel, the activation in the product's epilogue.  Otherwise the product
+  bfloat16 with M <= 16: one kernel, the activation in the product's epilogue.  Otherwise the product
   into a buffer of ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
   M, K = x.shape
   I = out.shape[1]
@@ -194,7 +218,7 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     raise KernelError(f"linear_swiglu: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
   if M == 0:
     return
-  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_M:
+  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (M <= SKINNY_BEST_M or (force_skinny and M <= SKINNY_MAX_M)):
     lib = common_lib()
     _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
     return
@@ -297,11 +321,26 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   the two write disjoint rows of ``out``."""
   lib = attention_lib(hd)
   if batch.num_prefill_tiles:
-    _check(lib, lib.mi_attention_prefill_bf16(
-      _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
-      _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
-      _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
-      nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
+    use_tc = (page_size % 64 == 0 and lib.mi_attention_prefill_tc_supported() == 1
+              and os.environ.get("MINIINFER_B200_PREFILL_TC", "1") != "0")
+    if use_tc:
+      if batch.scratch is not None:
+        status = batch.scratch.zeros("attention_prefill_status", 1, torch.int32)
+      else:
+        status = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+      _check(lib, lib.mi_attention_prefill_tc(
+        _ptr(out), _qkv_tensor_map(lib, qkv), _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
+        _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
+        _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
+      if batch.scratch is None and int(status[0]) != 0:
+        raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
+    else:
+      _check(lib, lib.mi_attention_prefill_bf16(
+        _ptr(out), _ptr(qkv), qkv.shape[1], _ptr(kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
+        _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
+        nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
@@ -362,7 +401,29 @@ def _kv_tensor_map(lib, kv_layer: torch.Tensor):
   return m
 
 
+def _qkv_tensor_map(lib, qkv: torch.Tensor):
+  """The TMA descriptor of a step's fused QKV rows (kept per address and shape: the workspace hands
+  out the same buffer step after step)."""
+  key = ("qkv", qkv.data_ptr(), tuple(qkv.shape))
+  m = _tensor_maps.get(key)
+  if m is None:
+    if not qkv.is_contiguous():
+      raise KernelError("attention: the QKV rows must be contiguous")
+    if len(_tensor_maps) > 4096:
+      _tensor_maps.clear()
+    m = ctypes.create_string_buffer(128)
+    code = lib.mi_qkv_tensor_map(m, _ptr(qkv), ctypes.c_longlong(qkv.shape[0]), ctypes.c_longlong(qkv.shape[1]))
+    if code != 0:
+      raise KernelError(lib.mi_last_error().decode())
+    _tensor_maps[key] = m
+  return m
+
+
 def device_status(ws) -> int:
-  """The status word that kernels with bounded waits set when a wait ran out (0: all well)."""
-  buf = ws._bufs.get(("attention_decode_counters", torch.int32))
-  return int(buf[0]) if buf is not None else 0
+  """The status words that kernels with bounded waits set when a wait ran out (0: all well)."""
+  code = 0
+  for name in ("attention_decode_counters", "attention_prefill_status"):
+    buf = ws._bufs.get((name, torch.int32))
+    if buf is not None:
+      code |= int(buf[0])
+  return code

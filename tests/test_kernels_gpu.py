@@ -81,7 +81,7 @@ def test_linear_bf16_few_rows(ops, out_dtype, N, K):
   for M in (64, 1, 3, 8, 9, 16, 17, 33):
     x = xs[:M].contiguous()
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    ops.linear(out, x, w)
+    ops.linear(out, x, w, force_skinny=True)
     exact = x.float() @ w.float().t()
     err = (out.float() - exact).abs().max().item()
     bound = (1e-4 if out_dtype == torch.float32 else 1e-2) * max(1.0, exact.abs().max().item())
@@ -90,6 +90,12 @@ def test_linear_bf16_few_rows(ops, out_dtype, N, K):
       full = out
     else:
       assert torch.equal(out, full[:M]), "a row's value must not depend on the other rows"
+    routed = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.linear(routed, x, w)                      # above 16 rows: the library product
+    if M <= 16:
+      assert torch.equal(routed, out)
+    else:
+      assert (routed.float() - exact).abs().max().item() <= bound, M
 
 
 def test_linear_bf16_many_rows_and_float32_logits(ops):
@@ -102,8 +108,9 @@ def test_linear_bf16_many_rows_and_float32_logits(ops):
   out32 = torch.empty(200, 1000, dtype=torch.float32, device=DEV)
   ops.linear(out32, x, w)
   assert (out32 - exact).abs().max() < 1e-4 * max(1.0, exact.abs().max().item())
-  with pytest.raises(ops.KernelError, match="multiple of 8"):
-    ops.linear(torch.empty(2, 5, dtype=torch.bfloat16, device=DEV), rnd(2, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16))
+  for M in (2, 20):
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+      ops.linear(torch.empty(M, 5, dtype=torch.bfloat16, device=DEV), rnd(M, 12, dtype=torch.bfloat16), rnd(5, 12, dtype=torch.bfloat16))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -222,13 +229,19 @@ def test_linear_swiglu(ops, I, K):
     ref.linear(gu, x, w)
     ref.silu_mul(want, gu)
     out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.linear_swiglu(out, x, w, _Scratch())
+    ops.linear_swiglu(out, x, w, _Scratch(), force_skinny=True)
     err = (out.float() - want.float()).abs().max().item()
     assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
     if M == 64:
       full = out
     elif M < 64:
       assert torch.equal(out, full[:M]), "a row's value must not depend on the other rows"
+    routed = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(routed, x, w, _Scratch())    # above 16 rows: library product, then the activation kernel
+    if M <= 16:
+      assert torch.equal(routed, out)
+    else:
+      assert (routed.float() - want.float()).abs().max().item() <= 2e-2 * max(1.0, want.float().abs().max().item()), M
   x32, w32 = xs[:5].float(), w.float()
   out32 = torch.empty(5, I, device=DEV)
   ops.linear_swiglu(out32, x32, w32, _Scratch())

@@ -35,7 +35,7 @@ def add_rmsnorm(out, resid, delta, weight, eps, rows=None, write_back=True):
   out.copy_((weight * (x * torch.rsqrt(var + eps))).to(out.dtype))
 
 
-def linear(out, x, w):
+def linear(out, x, w, force_skinny=False):
   out.copy_((x.float() @ w.float().t()).to(out.dtype))
 
 
@@ -100,7 +100,7 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
   out.copy_(res.reshape(T, nh * hd).to(out.dtype))
 
 
-def linear_swiglu(out, x, w, workspace):
+def linear_swiglu(out, x, w, workspace, force_skinny=False):
   gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype)
   linear(gu, x, w)
   silu_mul(out, gu)
