@@ -7,19 +7,21 @@
 // read once for both) - and walks the keys the mask allows in tiles of 128:
 //   * a producer warp asks the TMA engine for the Q rows once and for K and V tile by tile (boxes
 //     of 64 rows x 64 elements, one page and one half of the head size each, written in the
-//     128-byte swizzle), two stages ahead, counted on mbarriers;
+//     128-byte swizzle), two stages each, counted on mbarriers; K and V are counted apart, since
+//     K is free again as soon as S is computed;
 //   * one thread of the MMA warp issues S = Q K^T (tcgen05.mma, M = 128, N = 128, K = 16 per
 //     instruction, operands described in shared memory, K-major) into one of two 128-column
 //     accumulators in tensor memory, and, once the softmax warps have written P, O_tile = P V
-//     (V is MN-major: dims contiguous, as the cache stores it) into a third; tcgen05.commit tells
+//     (P from tensor memory; V from shared memory, MN-major: dims contiguous, as the cache stores
+//     it) into a third; tcgen05.commit tells
 //     the mbarriers when the products are done.  S of the next tile is issued before P V of this
 //     one, so the tensor cores work while the softmax warps do;
 //   * eight softmax warps - two threads per query row (tensor-memory lane = row), each with half of
 //     the row's columns - read S with tcgen05.ld (first for the row maximum, again for the
 //     exponentials), keep the running maximum and sum and their half of the output row in
 //     registers in float32, base 2 with the scale folded in, fold the finished O_tile of the
-//     previous tile into the output row, and write P in bf16 to shared memory in the layout the
-//     second product reads.
+//     previous tile into the output row, and write P in bf16 into tensor memory (two buffers),
+//     from where the second product takes its A operand.
 // Causal and window masks go by absolute position; tiles that the mask does not touch skip the
 // comparisons.  Rows past the end of the item's tokens are computed on whatever the Q copy brought
 // and never stored.
@@ -55,14 +57,14 @@ constexpr int HALF_BYTES = 128 * 128;         // 128 rows x 128 bytes
 constexpr int Q_BYTES = NHALF * HALF_BYTES;
 constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
 constexpr int STAGE_BYTES = 2 * K_BYTES;
-constexpr int P_BYTES = 2 * HALF_BYTES;       // 128 rows x 128 keys
 constexpr int SOFTMAX_WARPS = 8;                // two threads per query row, half of the columns each
 constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
 constexpr int THREADS = 10 * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;   // two S accumulators, the P V accumulator (float32 columns)
+constexpr int P_COL0 = 384, P_COL1 = 448;              // two P operands: 128 keys in bf16, two to a column
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + 256 + 2 * 2 * BM * sizeof(float);
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + 2 * 2 * BM * sizeof(float);
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
@@ -129,6 +131,20 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with A in tensor memory: lane = row, two bf16 of consecutive k to a column.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive columns of this thread's lane, written.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
 // 32 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane of the warp).
 __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
   uint32_t r[32];
@@ -165,11 +181,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
   mi::grid_dependency_sync();
   // ---- which rows and which keys (uniform over the block)
-  const int tile = a.n_tiles - 1 - (int)blockIdx.x;       // later tiles see more keys: they start first
+  // Blocks start in the order of x, then y: all heads of the last tile first, then the tile before.
+  // Later tiles of a request see more keys, so the long blocks start first and the short ones fill up.
+  const int tile = a.n_tiles - 1 - (int)blockIdx.y;
   const int item = a.tiles[2 * tile], o = a.tiles[2 * tile + 1];
   if (a.hpt == 1 && (o & 64)) return;                     // the block of the tile before covers these 64 tokens too
   const int G = a.nh / a.nkv;
-  const int head0 = (int)blockIdx.y * a.hpt;
+  const int head0 = (int)blockIdx.x * a.hpt;
   const int kvh = head0 / G;
   const int qlen = a.q_len[item], ctx = a.ctx_len[item];
   const int start = ctx - qlen;                           // position of the item's first new token
@@ -187,12 +205,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + Q_BYTES;                    // [stage][K, V]
-  unsigned char* p_s = kv_s + STAGES * STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + STAGES * STAGE_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = kv_full + STAGES;
-  uint64_t* s_full = kv_empty + STAGES;                   // [2]
+  uint64_t* k_full = bars + 1;                            // K and V of a tile are counted apart: K is free again
+  uint64_t* k_empty = k_full + STAGES;                    // once S is computed, long before P V is
+  uint64_t* v_full = k_empty + STAGES;
+  uint64_t* v_empty = v_full + STAGES;
+  uint64_t* s_full = v_empty + STAGES;                    // [2]
   uint64_t* s_empty = s_full + 2;                         // [2]
   uint64_t* p_full = s_empty + 2;
   uint64_t* o_full = p_full + 1;
@@ -204,8 +223,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
@@ -234,26 +255,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         for (int h = 0; h < NHALF; ++h)
           tma_load_2d(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
       }
-      for (int i = 0; i < n; ++i) {
+      // K of tile i goes first, then V of tile i - 1: S of the next tile never waits for a V copy
+      auto load = [&](int i, bool values) {
         const int s = i % STAGES;
-        mbar_wait(&kv_empty[s], ((i / STAGES) & 1) ^ 1, abort, a.status);
-        if (*abort) break;
-        unsigned char* k_dst = kv_s + (size_t)s * STAGE_BYTES;
-        unsigned char* v_dst = k_dst + K_BYTES;
-        mbar_expect_tx(&kv_full[s], (uint32_t)STAGE_BYTES);
+        uint64_t* full = values ? &v_full[s] : &k_full[s];
+        mbar_wait(values ? &v_empty[s] : &k_empty[s], ((i / STAGES) & 1) ^ 1, abort, a.status);
+        unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (values ? K_BYTES : 0);
+        mbar_expect_tx(full, (uint32_t)K_BYTES);
         const int key0 = (t_begin + i) * BN;
 #pragma unroll
         for (int pg = 0; pg < 2; ++pg) {
           const int key = key0 + 64 * pg;
           const int page = bt[min(key / a.page_size, a.bt_stride - 1)];   // past the context: the dummy page, masked below
-          const int y_k = ((page * 2) * a.nkv + kvh) * a.page_size + key % a.page_size;
-          const int y_v = y_k + a.nkv * a.page_size;
+          const int y = ((page * 2 + (values ? 1 : 0)) * a.nkv + kvh) * a.page_size + key % a.page_size;
 #pragma unroll
-          for (int h = 0; h < NHALF; ++h) {
-            tma_load_2d(k_dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y_k, &kv_full[s]);
-            tma_load_2d(v_dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y_v, &kv_full[s]);
-          }
+          for (int h = 0; h < NHALF; ++h) tma_load_2d(dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y, full);
         }
+      };
+      for (int step = 0; step <= n && !*abort; ++step) {
+        if (step < n) load(step, false);
+        if (step >= 1) load(step - 1, true);
       }
     }
   } else if (warp == MMA_WARP) {
@@ -261,10 +282,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     if (lane == 0) {
       constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
       constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s);
       auto issue_s = [&](int i) {
         const int s = i % STAGES, b = i & 1;
-        mbar_wait(&kv_full[s], (i / STAGES) & 1, abort, a.status);
+        mbar_wait(&k_full[s], (i / STAGES) & 1, abort, a.status);
         mbar_wait(&s_empty[b], ((i / 2) & 1) ^ 1, abort, a.status);
         tc_fence_after();
         const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
@@ -275,24 +296,25 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           tc_mma(d, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
         }
         tc_commit(&s_full[b]);
+        tc_commit(&k_empty[s]);
       };
       mbar_wait(q_full, 0, abort, a.status);
       if (!*abort) issue_s(0);
       for (int j = 0; j < n && !*abort; ++j) {
         if (j + 1 < n) issue_s(j + 1);
+        const int s = j % STAGES;
         mbar_wait(p_full, j & 1, abort, a.status);
+        mbar_wait(&v_full[s], (j / STAGES) & 1, abort, a.status);
         if (*abort) break;
         tc_fence_after();
-        const int s = j % STAGES;
         const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES);
+        const uint32_t p_tmem = tmem_base + ((j & 1) ? P_COL1 : P_COL0);
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          const uint32_t p_off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
-          tc_mma(tmem_base + O_COL, smem_desc(p_addr + p_off, 16, 1024),
-                 smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024), IDESC_PV, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < BN / 16; ++ks)
+          tc_mma_ts(tmem_base + O_COL, p_tmem + (uint32_t)ks * 8u, smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024),
+                    IDESC_PV, ks > 0 ? 1u : 0u);
         tc_commit(o_full);
-        tc_commit(&kv_empty[s]);
+        tc_commit(&v_empty[s]);
       }
     }
   } else {
@@ -360,23 +382,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = exp2f(m_run - m_use);
       m_run = m_new;
-      if (j > 0) {
-        mbar_wait(o_full, (j - 1) & 1, abort, a.status);   // P V of the tile before is done: P and the O tile are free
-        tc_fence_after();
-        fold();
-      }
-      if (alpha != 1.f) {
-        l_run *= alpha;
-#pragma unroll
-        for (int d = 0; d < OD; ++d) o_reg[d] *= alpha;
-      }
-      // pass 2: exponentials, their sum, P in bf16 to shared memory (K-major, 128-byte swizzle);
-      // this thread's 64 keys are one 128-byte row of the key half `ch`
+      l_run *= alpha;
+      // pass 2: exponentials, their sum, and P in bf16 into tensor memory, where the second product
+      // reads its A operand (lane = row, two keys to a column); this thread's 64 keys are 32 columns
+      const uint32_t p_addr = t_lane + (b ? P_COL1 : P_COL0) + ch * 32;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_ld32(v, s_addr + c * 32);
         float part[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int key = key0 + c * 32 + i;
@@ -389,17 +404,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         }
         l_run += (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {                   // 8 keys = 16 bytes at a time
-          const int c8 = c * 4 + q4;                       // 16-byte chunk of this thread's 128 bytes
-          const uint32_t dst = smem_u32(p_s) + (uint32_t)(ch * HALF_BYTES + r * 128 + ((c8 ^ (r & 7)) << 4));
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16(v[q4 * 8], v[q4 * 8 + 1])),
-                       "r"(pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3])), "r"(pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5])),
-                       "r"(pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7])) : "memory");
-        }
+        for (int i = 0; i < 16; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        tmem_st16(p_addr + c * 16, packed);
       }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       tc_fence_before();
       mbar_arrive(&s_empty[b]);                            // S of this tile is read: the accumulator may be written again
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is visible to the tensor cores
+      // the P V of the tile before joins the output row (it was computed against the old maximum),
+      // then the row moves to the new maximum; only then may the next P V overwrite the O tile
+      if (j > 0) {
+        mbar_wait(o_full, (j - 1) & 1, abort, a.status);
+        tc_fence_after();
+        fold();
+        tc_fence_before();
+      }
+      if (alpha != 1.f) {
+#pragma unroll
+        for (int d = 0; d < OD; ++d) o_reg[d] *= alpha;
+      }
       mbar_arrive(p_full);
     }
     mbar_wait(o_full, (n - 1) & 1, abort, a.status);
@@ -476,7 +498,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page_size=%d must be a multiple of 64", page_size);
   MI_REQUIRE(scale > 0.f, "attention_prefill_tc: the scale must be positive");
-  MI_REQUIRE(nh <= 65535, "attention_prefill_tc: too many heads for one launch");
+  MI_REQUIRE(n_tiles <= 65535, "attention_prefill_tc: more than 65535 tiles in one launch (%d)", n_tiles);
   if (n_tiles == 0) return 0;
   Args a;
   a.out = (__nv_bfloat16*)out;
@@ -500,7 +522,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   CUtensorMap qm, km;
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));
-  mi::launch(attention_prefill_tc_kernel, dim3(n_tiles, nh / a.hpt), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
+  mi::launch(attention_prefill_tc_kernel, dim3(nh / a.hpt, n_tiles), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
   MI_LAUNCH_OK("attention_prefill_tc");
   return 0;
 }
