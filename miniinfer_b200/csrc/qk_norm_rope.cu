@@ -81,86 +81,116 @@ qk_norm_rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ q_w, co
 }
 
 // The common case in one pass over registers: bf16, the whole head rotated, head_dim a multiple of
-// 128 (so that a lane's partner elements d and d + head_dim/2 are its own).  A lane holds pairs of
-// neighbouring elements (32-bit loads and stores).
+// 128 (so that a lane's partner elements d and d + head_dim/2 are its own).  A block takes one token,
+// a warp every eighth head of it, four heads at a time: all their loads are issued before anything
+// is computed, and the token's cosines and sines and the norm weights are loaded once per lane and
+// used for every head.  A lane holds pairs of neighbouring elements (32-bit loads and stores).
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(256)
 qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
                                const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ kv_layer, int nh, int nkv,
                                int page_size, float eps) {
-  mi::grid_dependency_sync();
   constexpr int HALF = HD / 2;
   constexpr int NP = HALF / 64;                 // bf16 pairs per lane in each half
+  constexpr int HEADS_AT_ONCE = 4;
   const int tkn = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nh + 2 * nkv;
-  const int h = blockIdx.y * WARPS + warp;
-  if (h >= heads) return;
-  __nv_bfloat16* x = qkv + ((size_t)tkn * heads + h) * HD;
-  const bool is_q = h < nh;
-  const bool is_k = !is_q && h < nh + nkv;
-  const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
-  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
-  __nv_bfloat16* dst = nullptr;
-  if (!is_q && slot >= 0) {
-    const int page = slot / page_size, off = slot % page_size;
-    dst = kv_layer + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD;
-  }
-  uint32_t raw[2][NP];
+  // what no kernel writes is fetched before the wait for the preceding kernel: weights, the table
+  float2 wq[2][NP], wk[2][NP], cs_c[NP], cs_s[NP];
 #pragma unroll
   for (int i = 0; i < NP; ++i) {
-    raw[0][i] = *reinterpret_cast<const uint32_t*>(x + 64 * i + 2 * lane);
-    raw[1][i] = *reinterpret_cast<const uint32_t*>(x + HALF + 64 * i + 2 * lane);
+    const int j = 64 * i + 2 * lane;
+    wq[0][i] = q_w ? *reinterpret_cast<const float2*>(q_w + j) : make_float2(1.f, 1.f);
+    wq[1][i] = q_w ? *reinterpret_cast<const float2*>(q_w + HALF + j) : make_float2(1.f, 1.f);
+    wk[0][i] = k_w ? *reinterpret_cast<const float2*>(k_w + j) : make_float2(1.f, 1.f);
+    wk[1][i] = k_w ? *reinterpret_cast<const float2*>(k_w + HALF + j) : make_float2(1.f, 1.f);
   }
-  if (!is_q && !is_k) {
-    if (dst) {
+  const float* cs = cos_sin ? cos_sin + (size_t)positions[tkn] * HD : nullptr;
 #pragma unroll
-      for (int i = 0; i < NP; ++i) {
-        *reinterpret_cast<uint32_t*>(dst + 64 * i + 2 * lane) = raw[0][i];
-        *reinterpret_cast<uint32_t*>(dst + HALF + 64 * i + 2 * lane) = raw[1][i];
+  for (int i = 0; i < NP; ++i) {
+    const int j = 64 * i + 2 * lane;
+    cs_c[i] = cs ? *reinterpret_cast<const float2*>(cs + j) : make_float2(1.f, 1.f);
+    cs_s[i] = cs ? *reinterpret_cast<const float2*>(cs + HALF + j) : make_float2(0.f, 0.f);
+  }
+  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
+  mi::grid_dependency_sync();
+  __nv_bfloat16* row = qkv + (size_t)tkn * heads * HD;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+
+  for (int h0 = warp; h0 < heads; h0 += 8 * HEADS_AT_ONCE) {
+    uint32_t raw[HEADS_AT_ONCE][2][NP];
+#pragma unroll
+    for (int u = 0; u < HEADS_AT_ONCE; ++u) {
+      const int h = h0 + 8 * u;
+      if (h < heads) {
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          raw[u][0][i] = *reinterpret_cast<const uint32_t*>(row + (size_t)h * HD + 64 * i + 2 * lane);
+          raw[u][1][i] = *reinterpret_cast<const uint32_t*>(row + (size_t)h * HD + HALF + 64 * i + 2 * lane);
+        }
       }
     }
-    return;
-  }
-  const float* w = is_q ? q_w : k_w;
-  const float* cs = cos_sin ? cos_sin + (size_t)positions[tkn] * HD : nullptr;
-  float2 v[2][NP];
-  float ss = 0.f;
 #pragma unroll
-  for (int hf = 0; hf < 2; ++hf)
+    for (int u = 0; u < HEADS_AT_ONCE; ++u) {
+      const int h = h0 + 8 * u;
+      if (h >= heads) break;                          // uniform over the warp
+      __nv_bfloat16* x = row + (size_t)h * HD;
+      const bool is_q = h < nh;
+      const bool is_k = !is_q && h < nh + nkv;
+      const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+      __nv_bfloat16* dst = (!is_q && slot >= 0)
+          ? kv_layer + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD : nullptr;
+      if (!is_q && !is_k) {                           // values: stored as they are
+        if (dst) {
 #pragma unroll
-    for (int i = 0; i < NP; ++i) {
-      v[hf][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[hf][i]));
-      ss += v[hf][i].x * v[hf][i].x + v[hf][i].y * v[hf][i].y;
-    }
-  float rstd = 1.f;
-  if (w) {
-    ss = mi::warp_sum(ss);
-    rstd = rsqrtf(ss / (float)HD + eps);
-  }
+          for (int i = 0; i < NP; ++i) {
+            *reinterpret_cast<uint32_t*>(dst + 64 * i + 2 * lane) = raw[u][0][i];
+            *reinterpret_cast<uint32_t*>(dst + HALF + 64 * i + 2 * lane) = raw[u][1][i];
+          }
+        }
+        continue;
+      }
+      const bool normed = is_q ? q_w != nullptr : k_w != nullptr;
+      float2 v[2][NP];
+      float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < NP; ++i) {
-    const int j = 64 * i + 2 * lane;                  // index in the first half
-    float2 a = v[0][i], b = v[1][i];
-    if (w) {
-      const float2 wa = *reinterpret_cast<const float2*>(w + j), wb = *reinterpret_cast<const float2*>(w + HALF + j);
-      a.x *= rstd * wa.x; a.y *= rstd * wa.y;
-      b.x *= rstd * wb.x; b.y *= rstd * wb.y;
-    }
-    if (cs) {
-      const float2 c = *reinterpret_cast<const float2*>(cs + j), s = *reinterpret_cast<const float2*>(cs + HALF + j);
-      const float2 ra = make_float2(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
-      const float2 rb = make_float2(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
-      a = ra; b = rb;
-    }
-    const __nv_bfloat162 oa = __floats2bfloat162_rn(a.x, a.y), ob = __floats2bfloat162_rn(b.x, b.y);
-    const uint32_t ua = *reinterpret_cast<const uint32_t*>(&oa), ub = *reinterpret_cast<const uint32_t*>(&ob);
-    *reinterpret_cast<uint32_t*>(x + j) = ua;
-    *reinterpret_cast<uint32_t*>(x + HALF + j) = ub;
-    if (dst) {
-      *reinterpret_cast<uint32_t*>(dst + j) = ua;
-      *reinterpret_cast<uint32_t*>(dst + HALF + j) = ub;
+      for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          v[hf][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u][hf][i]));
+          ss += v[hf][i].x * v[hf][i].x + v[hf][i].y * v[hf][i].y;
+        }
+      float rstd = 1.f;
+      if (normed) {
+        ss = mi::warp_sum(ss);
+        rstd = rsqrtf(ss / (float)HD + eps);
+      }
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {
+        const int j = 64 * i + 2 * lane;              // index in the first half
+        float2 a = v[0][i], b = v[1][i];
+        if (normed) {
+          const float2 wa = is_q ? wq[0][i] : wk[0][i], wb = is_q ? wq[1][i] : wk[1][i];
+          a.x *= rstd * wa.x; a.y *= rstd * wa.y;
+          b.x *= rstd * wb.x; b.y *= rstd * wb.y;
+        }
+        if (cs) {
+          const float2 c = cs_c[i], sn = cs_s[i];
+          const float2 ra = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+          const float2 rb = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+          a = ra; b = rb;
+        }
+        const __nv_bfloat162 oa = __floats2bfloat162_rn(a.x, a.y), ob = __floats2bfloat162_rn(b.x, b.y);
+        const uint32_t ua = *reinterpret_cast<const uint32_t*>(&oa), ub = *reinterpret_cast<const uint32_t*>(&ob);
+        *reinterpret_cast<uint32_t*>(x + j) = ua;
+        *reinterpret_cast<uint32_t*>(x + HALF + j) = ub;
+        if (dst) {
+          *reinterpret_cast<uint32_t*>(dst + j) = ua;
+          *reinterpret_cast<uint32_t*>(dst + HALF + j) = ub;
+        }
+      }
     }
   }
 }
@@ -181,10 +211,10 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
   const bool whole = !cos_sin || rotary_dim == hd;
   if (dtype == MI_BF16 && whole && (hd == 128 || hd == 256)) {
     if (hd == 128)
-      mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(grid), dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     else
-      mi::launch(qk_norm_rope_store_fast_kernel<256>, dim3(grid), dim3(WARPS * 32), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<256>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     MI_LAUNCH_OK("qk_norm_rope_store");
     return 0;

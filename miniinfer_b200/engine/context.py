@@ -19,9 +19,14 @@ class Workspace:
   def __init__(self, device):
     self.device = device
     self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+    self._views: Dict[tuple, torch.Tensor] = {}     # (name, dtype, shape) -> view of the buffer as it is now
     self.frozen = False
 
   def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+    vkey = (name, dtype, tuple(shape))
+    view = self._views.get(vkey)
+    if view is not None:
+      return view
     n = 1
     for s in shape:
       n *= int(s)
@@ -32,7 +37,13 @@ class Workspace:
         raise RuntimeError(f"workspace buffer {name!r} would have to grow to {n} elements while frozen")
       buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
       self._bufs[key] = buf
-    return buf[:n].view(*shape)
+      for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+        del self._views[k]                          # views of the buffer this one replaces
+    if len(self._views) > 1024:
+      self._views.clear()
+    view = buf[:n].view(*shape)
+    self._views[vkey] = view
+    return view
 
   def zeros(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
     """A buffer that starts at zero and is left to its users afterwards (counters that kernels reset

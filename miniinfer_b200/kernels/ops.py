@@ -95,7 +95,13 @@ def _ptr(t: Optional[torch.Tensor], dtype: Optional[torch.dtype] = None) -> ctyp
   return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+  """The current CUDA stream of the current device (also the capture stream while a graph is recorded)."""
+  if _raw_stream is not None:
+    return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
   return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -127,6 +133,21 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Te
                                  _dt(delta) if delta is not None else F32, _ptr(weight, torch.float32),
                                  _ptr(rows, torch.int32) if rows is not None else _ptr(None), R, H,
                                  ctypes.c_float(eps), int(bool(write_back)), _stream()))
+
+
+_transposed_views: Dict[int, tuple] = {}
+
+
+def _transposed(w: torch.Tensor) -> torch.Tensor:
+  """``w.t()``, kept per weight tensor: making the view costs more host time than a small product."""
+  hit = _transposed_views.get(id(w))
+  if hit is not None and hit[0] is w:
+    return hit[1]
+  if len(_transposed_views) > 4096:
+    _transposed_views.clear()
+  v = w.t()
+  _transposed_views[id(w)] = (w, v)
+  return v
 
 
 def _mm_f32_out_works(device) -> bool:
@@ -169,10 +190,10 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
     if K % 8 != 0:
       raise KernelError(f"linear: K={K} must be a multiple of 8 (16-byte loads of bf16 rows)")
     if out.dtype == torch.bfloat16:
-      torch.matmul(x, w.t(), out=out)
+      torch.mm(x, _transposed(w), out=out)
       return
     if out.dtype == torch.float32 and _mm_f32_out_works(out.device):
-      torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+      torch.mm(x, _transposed(w), out_dtype=torch.float32, out=out)
       return
   for m0 in range(0, M, SKINNY_MAX_M):
     m1 = min(M, m0 + SKINNY_MAX_M)
@@ -246,7 +267,7 @@ def sample(out: torch.Tensor, logits: torch.Tensor, temperature: torch.Tensor, t
       raise KernelError("sample: per-row arguments differ in length")
   if R == 0:
     return
-  slices = max(1, min(64, 296 // R, -(-V // 1024)))
+  slices = max(1, min(64, 640 // R, -(-V // 1024)))   # about four blocks of the pick kernel per SM
   words = R + 2 * R * slices
   if workspace is not None:
     scratch = workspace.buffer("sample_partials", (words,), torch.int32)
