@@ -11,17 +11,19 @@
 //     K is free again as soon as S is computed;
 //   * one thread of the MMA warp issues S = Q K^T (tcgen05.mma, M = 128, N = 128, K = 16 per
 //     instruction, operands described in shared memory, K-major) into one of two 128-column
-//     accumulators in tensor memory, and, once the softmax warps have written P, O_tile = P V
+//     accumulators in tensor memory, and, once the softmax warps have written P, O += P V
 //     (P from tensor memory; V from shared memory, MN-major: dims contiguous, as the cache stores
 //     it) into a third; tcgen05.commit tells
 //     the mbarriers when the products are done.  S of the next tile is issued before P V of this
 //     one, so the tensor cores work while the softmax warps do;
-//   * eight softmax warps - two threads per query row (tensor-memory lane = row), each with half of
-//     the row's columns - read S with tcgen05.ld (first for the row maximum, again for the
-//     exponentials), keep the running maximum and sum and their half of the output row in
-//     registers in float32, base 2 with the scale folded in, fold the finished O_tile of the
-//     previous tile into the output row, and write P in bf16 into tensor memory (two buffers),
-//     from where the second product takes its A operand.
+//   * sixteen softmax warps - four threads per query row (tensor-memory lane = row), each with 32
+//     of the row's 128 columns - read S with tcgen05.ld, keep the running maximum and sum in
+//     float32, base 2 with the scale folded in, and write P in bf16 into tensor memory (two
+//     buffers), from where the second product takes its A operand.  The output row stays in
+//     tensor memory, where the second product adds to it tile after tile; it is rescaled there
+//     only when a row's maximum moves up by more than 2^8 (until then sums and P are taken
+//     against the older maximum, which costs no accuracy in float32 and bf16), and read once at
+//     the end.
 // Causal and window masks go by absolute position; tiles that the mask does not touch skip the
 // comparisons.  Rows past the end of the item's tokens are computed on whatever the Q copy brought
 // and never stored.
@@ -57,14 +59,17 @@ constexpr int HALF_BYTES = 128 * 128;         // 128 rows x 128 bytes
 constexpr int Q_BYTES = NHALF * HALF_BYTES;
 constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
 constexpr int STAGE_BYTES = 2 * K_BYTES;
-constexpr int SOFTMAX_WARPS = 8;                // two threads per query row, half of the columns each
-constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
-constexpr int THREADS = 10 * 32;
+constexpr int TPR = 4;                          // softmax threads per query row, a run of columns each
+constexpr int COLS = BN / TPR;                  // columns of S per softmax thread
+constexpr int SOFTMAX_WARPS = 4 * TPR;
+constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+static_assert(COLS == 32, "a softmax thread reads its run of S with one 32-column load");
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;   // two S accumulators, the P V accumulator (float32 columns)
 constexpr int P_COL0 = 384, P_COL1 = 448;              // two P operands: 128 keys in bf16, two to a column
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + 2 * 2 * BM * sizeof(float);
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + 2 * TPR * BM * sizeof(float);
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
@@ -145,6 +150,28 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+// 16 consecutive columns of this thread's lane, read.
+__device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 consecutive columns of this thread's lane, written.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31]) : "memory");
+}
 // 32 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane of the warp).
 __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
   uint32_t r[32];
@@ -160,6 +187,12 @@ __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+
+// by the length of the array
+__device__ __forceinline__ void tmem_ld(float (&v)[32], uint32_t taddr) { tmem_ld32(v, taddr); }
+__device__ __forceinline__ void tmem_ld(float (&v)[16], uint32_t taddr) { tmem_ld16(v, taddr); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 
 // Shared-memory operand descriptor, 128-byte swizzle: start address, leading and stride byte offsets
 // in 16-byte units, descriptor version 1 (bits 46..47), layout type 2 = 128-byte swizzle (bits 61..63).
@@ -217,7 +250,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   uint64_t* o_full = p_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(bars + 32);       // [2][2][BM]: what the two threads of a row tell each other
+  float* xch = reinterpret_cast<float*>(bars + 32);       // [2][TPR][BM]: what the threads of a row tell each other
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
@@ -312,17 +345,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
           tc_mma_ts(tmem_base + O_COL, p_tmem + (uint32_t)ks * 8u, smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024),
-                    IDESC_PV, ks > 0 ? 1u : 0u);
+                    IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);     // O is summed over the tiles in tensor memory
         tc_commit(o_full);
         tc_commit(&v_empty[s]);
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: two threads per row
-    // Warps q and q + 4 read the tensor-memory lanes 32q .. 32q + 31 (a warp reaches the lanes of
-    // its number mod 4); the first takes the columns 0..63 of a row of S and the lower half of the
-    // output row, the second the rest.  They tell each other their half's maximum (and at the end
-    // its sum) through shared memory, with a barrier of their 64 threads.
+    // ------------------------------------------------------------------ softmax: TPR threads per row
+    // The warps q, q + 4, q + 8, ... read the tensor-memory lanes 32q .. 32q + 31 (a warp reaches
+    // the lanes of its number mod 4); warp q + 4 ch takes the columns 32 ch .. 32 ch + 31 of a row
+    // of S and the ch-th part of the output row.  The threads of a row tell each other their
+    // part's maximum (and at the end its sum) through shared memory, with a barrier of the
+    // 32 * TPR threads that share the rows.
     const int q = warp & 3, ch = warp >> 2;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
     const int tok = a.hpt == 2 ? (r & 63) : r;
@@ -331,116 +365,116 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int pos = row_valid ? start + o + tok : p_last;
     const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    constexpr int OD = HD / 2;                             // output columns of this thread
-    float o_reg[OD];
-#pragma unroll
-    for (int d = 0; d < OD; ++d) o_reg[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    constexpr int OD = HD / TPR;                           // output columns of this thread: 32 or 16
+    float m_run = -INFINITY, l_run = 0.f;                  // m_run: the maximum the row's sums are taken against
     const float sc = a.scale_log2;
-    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory"); };
-
-    auto fold = [&]() {                                    // the finished P V of a tile joins the output row
-#pragma unroll
-      for (int c = 0; c < OD / 32; ++c) {
-        float v[32];
-        tmem_ld32(v, t_lane + O_COL + ch * OD + c * 32);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_reg[c * 32 + i] += v[i];
+    auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(32 * TPR) : "memory"); };
+    // o_full completes once per tile; every thread takes the phases in order, each at most one
+    // tile late, and remembers how many it has seen
+    int o_seen = 0;
+    auto wait_o = [&](int tile_done) {
+      while (o_seen <= tile_done) {
+        mbar_wait(o_full, o_seen & 1, abort, a.status);
+        ++o_seen;
       }
+      tc_fence_after();
     };
+    const uint32_t o_addr = t_lane + O_COL + ch * OD;
+    float o_part[OD];                                      // this thread's part of the output row, when it is read or rescaled
+    auto load_o = [&]() { tmem_ld(o_part, o_addr); };
 
     for (int j = 0; j < n; ++j) {
       const int b = j & 1;
-      const int key0 = (t_begin + j) * BN + ch * 64;       // first key of this thread's columns
+      const int key0 = (t_begin + j) * BN + ch * COLS;     // first key of this thread's columns
       const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
-      // (after a wait has run out the loop goes on without waiting, so that the two warps of a
-      // row still meet at every pair barrier; what it computes then is never stored)
+      // (after a wait has run out the loop goes on without waiting, so that the warps of a row
+      // still meet at every row barrier; what it computes then is never stored)
       mbar_wait(&s_full[b], (j / 2) & 1, abort, a.status);
       tc_fence_after();
-      const uint32_t s_addr = t_lane + (b ? S_COL1 : S_COL0) + ch * 64;
-      // pass 1: the row's maximum
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_ld32(v, s_addr + c * 32);
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            if (key >= lo_r && key <= pos) mx = fmaxf(mx, v[i]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
-        }
-      }
-      xch[(b * 2 + ch) * BM + r] = mx;
-      pair_sync();
-      mx = fmaxf(mx, xch[(b * 2 + (ch ^ 1)) * BM + r]);
-      const float m_new = fmaxf(m_run, mx * sc);           // the scale is positive
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      l_run *= alpha;
-      // pass 2: exponentials, their sum, and P in bf16 into tensor memory, where the second product
-      // reads its A operand (lane = row, two keys to a column); this thread's 64 keys are 32 columns
-      const uint32_t p_addr = t_lane + (b ? P_COL1 : P_COL0) + ch * 32;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_ld32(v, s_addr + c * 32);
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + c * 32 + i;
-          float x = fmaf(v[i], sc, -m_use);
-          if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
-          float pe;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
-          v[i] = pe;
-          part[i & 3] += pe;
-        }
-        l_run += (part[0] + part[1]) + (part[2] + part[3]);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-        tmem_st16(p_addr + c * 16, packed);
-      }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      // this thread's 32 scores, read once
+      float v[COLS];
+      tmem_ld32(v, t_lane + (b ? S_COL1 : S_COL0) + ch * COLS);
       tc_fence_before();
       mbar_arrive(&s_empty[b]);                            // S of this tile is read: the accumulator may be written again
-      // the P V of the tile before joins the output row (it was computed against the old maximum),
-      // then the row moves to the new maximum; only then may the next P V overwrite the O tile
-      if (j > 0) {
-        mbar_wait(o_full, (j - 1) & 1, abort, a.status);
-        tc_fence_after();
-        fold();
-        tc_fence_before();
-      }
-      if (alpha != 1.f) {
+      float mx = -INFINITY;
 #pragma unroll
-        for (int d = 0; d < OD; ++d) o_reg[d] *= alpha;
+      for (int i = 0; i < COLS; ++i) {
+        if (masked) {
+          const int key = key0 + i;
+          v[i] = (key >= lo_r && key <= pos) ? v[i] : -INFINITY;
+        }
+        mx = fmaxf(mx, v[i]);
       }
+      xch[(b * TPR + ch) * BM + r] = mx;
+      row_sync();
+#pragma unroll
+      for (int c = 0; c < TPR; ++c) mx = fmaxf(mx, xch[(b * TPR + c) * BM + r]);
+      // The sums stay relative to the old maximum while the new one is at most 2^8 above it (the
+      // exponentials then stay below 2^8, which float32 sums and bf16 P hold easily); only a larger
+      // move - the first tile, mostly - rescales the sum and the output row in tensor memory.  The
+      // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; all
+      // threads of a row see the same maxima and decide alike.
+      const float m_new = fmaxf(m_run, mx * sc);           // the scale is positive
+      const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
+      if (__any_sync(0xffffffffu, move)) {
+        const float m_next = move ? m_new : m_run;
+        const float m_to = m_next == -INFINITY ? 0.f : m_next;
+        const float alpha = move ? exp2f(m_run - m_to) : 1.f;   // 0 for a row that had no key yet
+        if (j > 0) {
+          wait_o(j - 1);                                   // the products so far are in the output row
+          load_o();
+          uint32_t w[OD];
+#pragma unroll
+          for (int i = 0; i < OD; ++i) w[i] = __float_as_uint(o_part[i] * alpha);
+          tmem_st(o_addr, w);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        l_run *= alpha;
+        m_run = m_next;
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      // exponentials, their sum, and P in bf16 into tensor memory, where the second product reads
+      // its A operand (lane = row, two keys to a column); this thread's 32 keys are 16 columns
+      float part[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[COLS / 2];
+#pragma unroll
+      for (int i = 0; i < COLS; ++i) {
+        const float x = fmaf(v[i], sc, -m_use);
+        float pe;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
+        v[i] = pe;
+        part[i & 3] += pe;
+      }
+      l_run += (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+      for (int i = 0; i < COLS / 2; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+      tmem_st16(t_lane + (b ? P_COL1 : P_COL0) + ch * (COLS / 2), packed);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      // Every phase of o_full is taken no later than one tile after it completes (a waiter two
+      // phases behind would read the parity of the wrong phase).  The product waited for here was
+      // issued a whole tile ago; the product that read this tile's P buffer is older still.
+      if (j > 0) wait_o(j - 1);
+      tc_fence_before();
       mbar_arrive(p_full);
     }
-    mbar_wait(o_full, (n - 1) & 1, abort, a.status);
-    tc_fence_after();
-    fold();
-    // the row's sum: both halves
-    xch[((n & 1) * 2 + ch) * BM + r] = l_run;
-    pair_sync();
-    l_run += xch[((n & 1) * 2 + (ch ^ 1)) * BM + r];
+    wait_o(n - 1);
+    load_o();
+    // the row's sum: all parts
+    xch[((n & 1) * TPR + ch) * BM + r] = l_run;
+    row_sync();
+    l_run = 0.f;
+#pragma unroll
+    for (int c = 0; c < TPR; ++c) l_run += xch[((n & 1) * TPR + c) * BM + r];
     if (row_valid && !*abort) {
       const float inv = 1.f / l_run;
       __nv_bfloat16* dst = a.out + (size_t)(row0 + tok) * a.nh * HD + (size_t)head * HD + ch * OD;
 #pragma unroll
       for (int d = 0; d < OD; d += 8) {
         uint4 w;
-        w.x = pack_bf16(o_reg[d] * inv, o_reg[d + 1] * inv);
-        w.y = pack_bf16(o_reg[d + 2] * inv, o_reg[d + 3] * inv);
-        w.z = pack_bf16(o_reg[d + 4] * inv, o_reg[d + 5] * inv);
-        w.w = pack_bf16(o_reg[d + 6] * inv, o_reg[d + 7] * inv);
+        w.x = pack_bf16(o_part[d] * inv, o_part[d + 1] * inv);
+        w.y = pack_bf16(o_part[d + 2] * inv, o_part[d + 3] * inv);
+        w.z = pack_bf16(o_part[d + 4] * inv, o_part[d + 5] * inv);
+        w.w = pack_bf16(o_part[d + 6] * inv, o_part[d + 7] * inv);
         *reinterpret_cast<uint4*>(dst + d) = w;
       }
     }
