@@ -9,18 +9,21 @@
 //     of 64 rows x 64 elements, one page and one half of the head size each, written in the
 //     128-byte swizzle), two stages each, counted on mbarriers; K and V are counted apart, since
 //     K is free again as soon as S is computed;
+//   * the key tiles are dealt to two streams, the even and the odd ones.  A stream has an S
+//     accumulator (128 columns of tensor memory), an output accumulator (head size columns), and
+//     a running maximum and sum per row of its own, as if it were a request with half the keys;
+//     the two are merged at the end.  Inside a stream everything follows in order - S, softmax,
+//     P V, S of its next tile - and the two streams take turns on the tensor cores, which so have
+//     the products of one stream to do while the softmax warps of the other work;
 //   * one thread of the MMA warp issues S = Q K^T (tcgen05.mma, M = 128, N = 128, K = 16 per
-//     instruction, operands described in shared memory, K-major) into one of two 128-column
-//     accumulators in tensor memory, and, once the softmax warps have written P, O += P V
-//     (P from tensor memory; V from shared memory, MN-major: dims contiguous, as the cache stores
-//     it) into a third; tcgen05.commit tells
-//     the mbarriers when the products are done.  S of the next tile is issued before P V of this
-//     one, so the tensor cores work while the softmax warps do;
-//   * sixteen softmax warps - four threads per query row (tensor-memory lane = row), each with 32
-//     of the row's 128 columns - read S with tcgen05.ld, keep the running maximum and sum in
-//     float32, base 2 with the scale folded in, and write P in bf16 into tensor memory (two
-//     buffers), from where the second product takes its A operand.  The output row stays in
-//     tensor memory, where the second product adds to it tile after tile; it is rescaled there
+//     instruction, operands described in shared memory, K-major) and, once the stream's softmax
+//     warps have written P, O += P V (P from tensor memory, where it overwrites the columns of S
+//     it came from; V from shared memory, MN-major: dims contiguous, as the cache stores it);
+//     tcgen05.commit tells the mbarriers when the products are done;
+//   * eight softmax warps per stream - two threads per query row (tensor-memory lane = row), 64
+//     columns each - read S with tcgen05.ld (once for the maximum, again for the exponentials),
+//     keep the maximum and the sum in float32, base 2 with the scale folded in, and write P in
+//     bf16 back into tensor memory.  The output row stays in tensor memory; it is rescaled there
 //     only when a row's maximum moves up by more than 2^8 (until then sums and P are taken
 //     against the older maximum, which costs no accuracy in float32 and bf16), and read once at
 //     the end.
@@ -59,17 +62,18 @@ constexpr int HALF_BYTES = 128 * 128;         // 128 rows x 128 bytes
 constexpr int Q_BYTES = NHALF * HALF_BYTES;
 constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
 constexpr int STAGE_BYTES = 2 * K_BYTES;
-constexpr int TPR = 4;                          // softmax threads per query row, a run of columns each
+constexpr int STREAMS = 2;                      // the key tiles are dealt to two streams (even, odd) with sums of their own
+constexpr int TPR = 2;                          // softmax threads per query row and stream, half of the columns each
 constexpr int COLS = BN / TPR;                  // columns of S per softmax thread
-constexpr int SOFTMAX_WARPS = 4 * TPR;
+constexpr int SOFTMAX_WARPS = 4 * TPR * STREAMS;
 constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
 constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
-static_assert(COLS == 32, "a softmax thread reads its run of S with one 32-column load");
 constexpr int TMEM_COLS = 512;
-constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;   // two S accumulators, the P V accumulator (float32 columns)
-constexpr int P_COL0 = 384, P_COL1 = 448;              // two P operands: 128 keys in bf16, two to a column
+// Tensor memory: per stream an S accumulator (128 float32 columns; P overwrites part of it) and an
+// output accumulator (head size columns).
+constexpr int S_COL = 0, O_COL = 256;                  // stream s: S at S_COL + 128 s, O at O_COL + 128 s
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + 2 * TPR * BM * sizeof(float);
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + STREAMS * (TPR + 1)) * BM * sizeof(float);
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
@@ -244,13 +248,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   uint64_t* k_empty = k_full + STAGES;                    // once S is computed, long before P V is
   uint64_t* v_full = k_empty + STAGES;
   uint64_t* v_empty = v_full + STAGES;
-  uint64_t* s_full = v_empty + STAGES;                    // [2]
-  uint64_t* s_empty = s_full + 2;                         // [2]
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* s_full = v_empty + STAGES;                    // [stream]: S of the stream's tile is computed
+  uint64_t* p_full = s_full + STREAMS;                    // [stream]: its P is written
+  uint64_t* o_full = p_full + STREAMS;                    // [stream]: its P V is added to the output row
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + STREAMS);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(bars + 32);       // [2][TPR][BM]: what the threads of a row tell each other
+  float* xch = reinterpret_cast<float*>(bars + 32);       // [stream][2][TPR][BM]: the maxima the threads of a row tell each other
+  float* fin_l = xch + 2 * STREAMS * TPR * BM;            // [stream][TPR][BM]: at the end, each thread's sum
+  float* fin_m = fin_l + STREAMS * TPR * BM;              // [stream][BM]: and each stream's maximum
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
@@ -261,12 +266,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < STREAMS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], SOFTMAX_WARPS * 32);
+      mbar_init(&p_full[b], 4 * TPR * 32);
+      mbar_init(&o_full[b], 1);
     }
-    mbar_init(p_full, SOFTMAX_WARPS * 32);
-    mbar_init(o_full, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -316,13 +320,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
       constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
       const uint32_t q_addr = smem_u32(q_s);
+      // Tile j belongs to stream j & 1.  The products of a stream follow each other - S, (softmax,)
+      // P V, S of its next tile, ... - and the two streams take turns, so the tensor cores have the
+      // products of one stream to do while the softmax warps of the other work.  The tensor cores
+      // run the products in the order they are issued: P V of a tile (which reads P from the
+      // columns of S) is issued before S of the stream's next tile overwrites them.
       auto issue_s = [&](int i) {
         const int s = i % STAGES, b = i & 1;
         mbar_wait(&k_full[s], (i / STAGES) & 1, abort, a.status);
-        mbar_wait(&s_empty[b], ((i / 2) & 1) ^ 1, abort, a.status);
         tc_fence_after();
         const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
-        const uint32_t d = tmem_base + (b ? S_COL1 : S_COL0);
+        const uint32_t d = tmem_base + S_COL + 128 * b;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
@@ -333,31 +341,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       };
       mbar_wait(q_full, 0, abort, a.status);
       if (!*abort) issue_s(0);
+      if (!*abort && n > 1) issue_s(1);
       for (int j = 0; j < n && !*abort; ++j) {
-        if (j + 1 < n) issue_s(j + 1);
-        const int s = j % STAGES;
-        mbar_wait(p_full, j & 1, abort, a.status);
+        const int s = j % STAGES, b = j & 1;
+        mbar_wait(&p_full[b], (j / 2) & 1, abort, a.status);
         mbar_wait(&v_full[s], (j / STAGES) & 1, abort, a.status);
         if (*abort) break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES);
-        const uint32_t p_tmem = tmem_base + ((j & 1) ? P_COL1 : P_COL0);
+        const uint32_t p_tmem = tmem_base + S_COL + 128 * b;   // thread `ch` of a row leaves its 64 keys in its first 32 columns
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks)
-          tc_mma_ts(tmem_base + O_COL, p_tmem + (uint32_t)ks * 8u, smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024),
-                    IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);     // O is summed over the tiles in tensor memory
-        tc_commit(o_full);
+          tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(64 * (ks >> 2) + 8 * (ks & 3)),
+                    smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024), IDESC_PV,
+                    (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over its tiles in tensor memory
+        tc_commit(&o_full[b]);
         tc_commit(&v_empty[s]);
+        if (j + 2 < n) issue_s(j + 2);
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: TPR threads per row
-    // The warps q, q + 4, q + 8, ... read the tensor-memory lanes 32q .. 32q + 31 (a warp reaches
-    // the lanes of its number mod 4); warp q + 4 ch takes the columns 32 ch .. 32 ch + 31 of a row
-    // of S and the ch-th part of the output row.  The threads of a row tell each other their
-    // part's maximum (and at the end its sum) through shared memory, with a barrier of the
-    // 32 * TPR threads that share the rows.
-    const int q = warp & 3, ch = warp >> 2;
+    // ------------------------------------------------------------------ softmax
+    // Warp w: tensor-memory lanes 32 (w & 3) .. + 31 (a warp reaches the lanes of its number mod
+    // 4), half ch = (w >> 2) & 1 of the columns, stream st = w >> 3.  A stream keeps a maximum, a sum
+    // and an output row of its own over its tiles (the even or the odd ones); the two are merged at
+    // the end.  The two threads of a row and stream tell each other their half's maximum through
+    // shared memory, with a barrier of the 64 threads that share the rows.
+    const int q = warp & 3, ch = (warp >> 2) & 1, st = warp >> 3;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
     const int tok = a.hpt == 2 ? (r & 63) : r;
     const int head = head0 + (a.hpt == 2 ? (r >> 6) : 0);
@@ -365,54 +375,52 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int pos = row_valid ? start + o + tok : p_last;
     const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    constexpr int OD = HD / TPR;                           // output columns of this thread: 32 or 16
-    float m_run = -INFINITY, l_run = 0.f;                  // m_run: the maximum the row's sums are taken against
+    float m_run = -INFINITY, l_run = 0.f;                  // m_run: the maximum the stream's sums are taken against
     const float sc = a.scale_log2;
-    auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + q), "n"(32 * TPR) : "memory"); };
-    // o_full completes once per tile; every thread takes the phases in order, each at most one
-    // tile late, and remembers how many it has seen
+    auto row_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + st * 4 + q) : "memory"); };
+    // o_full of the stream completes once per tile of the stream; every thread takes the phases in
+    // order, each at most one tile late, and remembers how many it has seen
     int o_seen = 0;
-    auto wait_o = [&](int tile_done) {
-      while (o_seen <= tile_done) {
-        mbar_wait(o_full, o_seen & 1, abort, a.status);
+    auto wait_o = [&](int upto) {
+      while (o_seen <= upto) {
+        mbar_wait(&o_full[st], o_seen & 1, abort, a.status);
         ++o_seen;
       }
       tc_fence_after();
     };
-    const uint32_t o_addr = t_lane + O_COL + ch * OD;
-    float o_part[OD];                                      // this thread's part of the output row, when it is read or rescaled
-    auto load_o = [&]() { tmem_ld(o_part, o_addr); };
+    const uint32_t s_addr = t_lane + S_COL + 128 * st + ch * COLS;
+    const uint32_t o_addr = t_lane + O_COL + 128 * st + ch * (HD / 2);   // for rescaling: this thread's half of the stream's output row
+    const int n_mine = (n - st + 1) / 2;                   // tiles of this stream
 
-    for (int j = 0; j < n; ++j) {
-      const int b = j & 1;
+    for (int k = 0; k < n_mine; ++k) {
+      const int j = 2 * k + st;
       const int key0 = (t_begin + j) * BN + ch * COLS;     // first key of this thread's columns
       const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
       // (after a wait has run out the loop goes on without waiting, so that the warps of a row
       // still meet at every row barrier; what it computes then is never stored)
-      mbar_wait(&s_full[b], (j / 2) & 1, abort, a.status);
+      mbar_wait(&s_full[st], k & 1, abort, a.status);
       tc_fence_after();
-      // this thread's 32 scores, read once
-      float v[COLS];
-      tmem_ld32(v, t_lane + (b ? S_COL1 : S_COL0) + ch * COLS);
-      tc_fence_before();
-      mbar_arrive(&s_empty[b]);                            // S of this tile is read: the accumulator may be written again
-      float mx = -INFINITY;
+      // first pass over this thread's 64 scores: their maximum
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64 links
 #pragma unroll
-      for (int i = 0; i < COLS; ++i) {
-        if (masked) {
-          const int key = key0 + i;
-          v[i] = (key >= lo_r && key <= pos) ? v[i] : -INFINITY;
+      for (int c = 0; c < COLS / 32; ++c) {
+        float v[32];
+        tmem_ld32(v, s_addr + 32 * c);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + 32 * c + i;
+          if (!masked || (key >= lo_r && key <= pos)) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
         }
-        mx = fmaxf(mx, v[i]);
       }
-      xch[(b * TPR + ch) * BM + r] = mx;
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* my_xch = xch + ((st * 2 + (k & 1)) * TPR) * BM;
+      my_xch[ch * BM + r] = mx;
       row_sync();
-#pragma unroll
-      for (int c = 0; c < TPR; ++c) mx = fmaxf(mx, xch[(b * TPR + c) * BM + r]);
+      mx = fmaxf(mx, my_xch[(ch ^ 1) * BM + r]);
       // The sums stay relative to the old maximum while the new one is at most 2^8 above it (the
       // exponentials then stay below 2^8, which float32 sums and bf16 P hold easily); only a larger
       // move - the first tile, mostly - rescales the sum and the output row in tensor memory.  The
-      // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; all
+      // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; both
       // threads of a row see the same maxima and decide alike.
       const float m_new = fmaxf(m_run, mx * sc);           // the scale is positive
       const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
@@ -420,13 +428,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const float m_next = move ? m_new : m_run;
         const float m_to = m_next == -INFINITY ? 0.f : m_next;
         const float alpha = move ? exp2f(m_run - m_to) : 1.f;   // 0 for a row that had no key yet
-        if (j > 0) {
-          wait_o(j - 1);                                   // the products so far are in the output row
-          load_o();
-          uint32_t w[OD];
+        if (k > 0) {
+          wait_o(k - 1);                                   // the stream's products so far are in its output row
 #pragma unroll
-          for (int i = 0; i < OD; ++i) w[i] = __float_as_uint(o_part[i] * alpha);
-          tmem_st(o_addr, w);
+          for (int c = 0; c < HD / 2 / 32; ++c) {
+            float op[32];
+            tmem_ld32(op, o_addr + c * 32);
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(op[i] * alpha);
+            tmem_st32(o_addr + c * 32, w);
+          }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         l_run *= alpha;
@@ -434,47 +446,73 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       }
       const float m_use = m_run == -INFINITY ? 0.f : m_run;
       // exponentials, their sum, and P in bf16 into tensor memory, where the second product reads
-      // its A operand (lane = row, two keys to a column); this thread's 32 keys are 16 columns
+      // its A operand (lane = row, two keys to a column): this thread's 64 keys go to the first 32
+      // of its own 64 columns of S, which it has read
+      // (32 scores at a time: the first 32 are read before P overwrites the first 16 columns, and
+      // the P of the second 32 goes to the columns 16..31, read by then)
       float part[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[COLS / 2];
 #pragma unroll
-      for (int i = 0; i < COLS; ++i) {
-        const float x = fmaf(v[i], sc, -m_use);
-        float pe;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
-        v[i] = pe;
-        part[i & 3] += pe;
+      for (int c = 0; c < COLS / 32; ++c) {
+        float v[32];
+        tmem_ld32(v, s_addr + 32 * c);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + 32 * c + i;
+          float x = fmaf(v[i], sc, -m_use);
+          if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
+          float pe;
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
+          v[i] = pe;
+          part[i & 3] += pe;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        tmem_st16(s_addr + 16 * c, packed);
       }
       l_run += (part[0] + part[1]) + (part[2] + part[3]);
-#pragma unroll
-      for (int i = 0; i < COLS / 2; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-      tmem_st16(t_lane + (b ? P_COL1 : P_COL0) + ch * (COLS / 2), packed);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       // Every phase of o_full is taken no later than one tile after it completes (a waiter two
       // phases behind would read the parity of the wrong phase).  The product waited for here was
-      // issued a whole tile ago; the product that read this tile's P buffer is older still.
-      if (j > 0) wait_o(j - 1);
+      // issued a whole tile of the stream ago.
+      if (k > 0) wait_o(k - 1);
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[st]);
     }
-    wait_o(n - 1);
-    load_o();
-    // the row's sum: all parts
-    xch[((n & 1) * TPR + ch) * BM + r] = l_run;
-    row_sync();
-    l_run = 0.f;
+    if (n_mine > 0) wait_o(n_mine - 1);
+    // ---- the two streams' sums are merged: every thread leaves its sum (and the stream's maximum)
+    // in shared memory, all softmax warps meet, and each thread finishes a quarter of the output row
+    fin_l[(st * TPR + ch) * BM + r] = l_run;
+    if (ch == 0) fin_m[st * BM + r] = m_run;
+    tc_fence_before();
+    asm volatile("bar.sync 9, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+    tc_fence_after();
+    const float m0 = fin_m[r], m1 = fin_m[BM + r];
+    const float m_all = fmaxf(m0, m1);
+    const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);     // a stream without tiles, or without a visible key, counts nothing
+    const float w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m_all);
+    const float l_all = (fin_l[r] + fin_l[BM + r]) * w0 + (fin_l[2 * BM + r] + fin_l[3 * BM + r]) * w1;
+    constexpr int OD = HD / 4;                             // output columns of this thread: 32 or 16
+    const int part_no = st * 2 + ch;
+    float o0[OD], o1[OD];
+    const bool has1 = n > 1;                               // the second stream has an output row only if it had a tile
+    tmem_ld(o0, t_lane + O_COL + part_no * OD);
+    if (has1) {
+      tmem_ld(o1, t_lane + O_COL + 128 + part_no * OD);
+    } else {
 #pragma unroll
-    for (int c = 0; c < TPR; ++c) l_run += xch[((n & 1) * TPR + c) * BM + r];
+      for (int i = 0; i < OD; ++i) o1[i] = 0.f;
+    }
     if (row_valid && !*abort) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = a.out + (size_t)(row0 + tok) * a.nh * HD + (size_t)head * HD + ch * OD;
+      const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(row0 + tok) * a.nh * HD + (size_t)head * HD + part_no * OD;
 #pragma unroll
       for (int d = 0; d < OD; d += 8) {
         uint4 w;
-        w.x = pack_bf16(o_part[d] * inv, o_part[d + 1] * inv);
-        w.y = pack_bf16(o_part[d + 2] * inv, o_part[d + 3] * inv);
-        w.z = pack_bf16(o_part[d + 4] * inv, o_part[d + 5] * inv);
-        w.w = pack_bf16(o_part[d + 6] * inv, o_part[d + 7] * inv);
+        w.x = pack_bf16(o0[d] * f0 + o1[d] * f1, o0[d + 1] * f0 + o1[d + 1] * f1);
+        w.y = pack_bf16(o0[d + 2] * f0 + o1[d + 2] * f1, o0[d + 3] * f0 + o1[d + 3] * f1);
+        w.z = pack_bf16(o0[d + 4] * f0 + o1[d + 4] * f1, o0[d + 5] * f0 + o1[d + 5] * f1);
+        w.w = pack_bf16(o0[d + 6] * f0 + o1[d + 6] * f1, o0[d + 7] * f0 + o1[d + 7] * f1);
         *reinterpret_cast<uint4*>(dst + d) = w;
       }
     }

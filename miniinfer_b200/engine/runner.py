@@ -422,7 +422,7 @@ class ModelRunner:
     g.ws.frozen = True
     before = ops.launch_count()
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with ops.recording_graph(), torch.cuda.graph(graph):
       run()
     g.launches = ops.launch_count() - before
     g.graph = graph

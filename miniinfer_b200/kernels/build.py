@@ -30,7 +30,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
               "-Xptxas", "-v"]
 
 COMMON_SOURCES = ["common.cu", "embedding.cu", "norm.cu", "gemm_f32.cu", "gemm_skinny.cu",
-                  "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu"]
+                  "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu", "gemm_cublas.cu"]
+COMMON_LIBS = ["cublas"]
 ATTENTION_SOURCES = ["attention_prefill.cu", "attention_decode.cu", "attention_decode_tma.cu", "attention_prefill_tc.cu"]
 
 _lock = threading.Lock()
@@ -129,7 +130,7 @@ def build_library(name: str, sources: Sequence[str], defines: Optional[Dict[str,
 
 
 def build_common() -> str:
-  return build_library("common", COMMON_SOURCES)
+  return build_library("common", COMMON_SOURCES, libs=COMMON_LIBS)
 
 
 def build_attention(head_dim: int) -> str:

@@ -136,6 +136,24 @@ def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Te
 
 
 _transposed_views: Dict[int, tuple] = {}
+_capturing = False
+
+
+class recording_graph:
+  """``with ops.recording_graph():`` around a stream capture: library products then go through
+  PyTorch, whose cuBLAS handle has a workspace that is safe to use while a graph is recorded."""
+
+  def __enter__(self):
+    global _capturing
+    self._before = _capturing
+    _capturing = True
+    return self
+
+  def __exit__(self, *exc):
+    global _capturing
+    _capturing = self._before
+    return False
+
 
 
 def _transposed(w: torch.Tensor) -> torch.Tensor:
@@ -189,6 +207,10 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
       raise KernelError("linear: operands and out must be contiguous CUDA tensors")
     if K % 8 != 0:
       raise KernelError(f"linear: K={K} must be a multiple of 8 (16-byte loads of bf16 rows)")
+    if M > SKINNY_MAX_M and not _capturing and out.dtype in (torch.bfloat16, torch.float32):
+      # prefill-sized: straight to cuBLAS (a third of the host time of torch.mm); not while a graph is recorded
+      _check(lib, lib.mi_gemm_cublas_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, _stream()), kernels=0)
+      return
     if out.dtype == torch.bfloat16:
       torch.mm(x, _transposed(w), out=out)
       return

@@ -160,6 +160,11 @@ CASES = [
   # exactly 8 and 16 query heads per kv head in the TMA decode kernel (one full pass, two full passes)
   ([(500, 1), (70, 1), (64, 1)], 16, 2, 128, 64, None),
   ([(300, 1), (129, 1)], 16, 1, 64, 64, 100),
+  # the tcgen05 prefill kernel: one head per kv head (128 tokens of one head per block), head size 128;
+  # a long portion that starts inside the prompt, with a window that cuts its first key tiles; one key tile only
+  ([(700, 300), (130, 129), (2, 2)], 3, 3, 128, 64, None),
+  ([(2500, 1100), (200, 1)], 4, 2, 128, 128, 700),
+  ([(100, 100)], 6, 1, 64, 64, None),
 ]
 
 
