@@ -56,6 +56,15 @@ class Request:
   def all_ids(self) -> List[int]:
     return self.prompt_ids + self.output_ids
 
+  def ids(self, start: int, stop: int) -> List[int]:
+    """Tokens ``start .. stop`` of prompt followed by output, without joining the two lists."""
+    n = len(self.prompt_ids)
+    if stop <= n:
+      return self.prompt_ids[start:stop]
+    if start >= n:
+      return self.output_ids[start - n:stop - n]
+    return self.prompt_ids[start:] + self.output_ids[:stop - n]
+
   @property
   def total_len(self) -> int:
     return len(self.prompt_ids) + len(self.output_ids)
@@ -177,7 +186,7 @@ class Scheduler:
       self._preempt(self.running[-1], out)
     for req in decoders:
       self._take(req.req_id, 1, pending)
-      items.append(ScheduledItem(req, [req.all_ids()[-1]], True))
+      items.append(ScheduledItem(req, req.ids(req.total_len - 1, req.total_len), True))
       scheduled.add(req.req_id)
       budget -= 1
       out.num_decode_tokens += 1
@@ -193,7 +202,7 @@ class Scheduler:
       if n < 1:
         continue
       self._take(req.req_id, n, pending)
-      ids = req.all_ids()[req.num_computed:req.num_computed + n]
+      ids = req.ids(req.num_computed, req.num_computed + n)
       items.append(ScheduledItem(req, ids, n == remaining))
       scheduled.add(req.req_id)
       budget -= n
@@ -212,7 +221,7 @@ class Scheduler:
       req.status = RUNNING
       self.running.append(req)
       self._take(req.req_id, n, pending)
-      items.append(ScheduledItem(req, req.all_ids()[:n], n == remaining))
+      items.append(ScheduledItem(req, req.ids(0, n), n == remaining))
       scheduled.add(req.req_id)
       budget -= n
       out.num_prefill_tokens += n
