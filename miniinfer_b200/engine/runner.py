@@ -144,6 +144,8 @@ class ModelRunner:
       else:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
     self.meta = _MetaBuffers(self.device)
+    # a part that reads the step on the host would have its decisions frozen into a recorded graph
+    self.graphs_allowed = not any(p.reads_step_on_host for p in spec.all_parts())
     self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
     self.last_h2d_bytes = 0
     self.last_launches = 0
@@ -302,7 +304,7 @@ class ModelRunner:
     R = sum(len(it.want) for it in items)
     decode_only = all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items)
     bucket = next((b for b in GRAPH_BUCKETS if b >= len(items)), None)
-    if use_graphs and decode_only and bucket is not None and self.device.type == "cuda":
+    if use_graphs and self.graphs_allowed and decode_only and bucket is not None and self.device.type == "cuda":
       return self._graph_step(items, sampling, sample_fn, tokens_out, bucket)
     logits, ctx = self.step(items, sampling, return_ctx=True)
     if R:

@@ -57,7 +57,14 @@ def whole(file_name: str, shape: Sequence[int]) -> List[Piece]:
 
 
 class Part:
-  """Base of all parts.  ``name`` is the prefix of the part's tensors in a weights file."""
+  """Base of all parts.  ``name`` is the prefix of the part's tensors in a weights file.
+
+  ``reads_step_on_host``: set it to True in a part whose forward method reads the step's description
+  on the host (``ctx.host``: lengths, slots, ...) or decides anything else in Python from the
+  step's contents.  Decode steps of a model with such a part are not replayed from CUDA graphs,
+  since a graph replays the kernels of the step it was recorded from."""
+
+  reads_step_on_host = False
 
   def __init__(self, name: str):
     self.name = name

@@ -26,6 +26,8 @@ def define_toy():
     class DecayMixer(Mixer):
       """out_t = W (s_t), s_t = decay * s_{t-1} + x_t: a running sum per request, kept in a state slot."""
 
+      reads_step_on_host = True      # forward walks the items of the step in Python
+
       def __init__(self, name, hidden_size, decay):
         super().__init__(name)
         self.hidden_size, self.decay = hidden_size, decay
@@ -104,6 +106,7 @@ def test_toy_mixer_with_state_runs_through_the_engine(tmp_path):
   reqs = rc.make_requests(97, (40, 23, 9), seed=1)
   ref = {rid: plain_toy(weights, cfg, ids) for rid, ids in reqs.items()}
   runner = TraceRunner(d, "float32", 256, device=DEV)
+  assert not runner.runner.graphs_allowed        # its mixer reads the step on the host: no CUDA graphs for it
   assert runner.cache.paged_groups == [] and len(runner.cache.state_groups) == 1
   assert runner.cache.state_groups[0].state.shape == (2, 9, 32)
   for trace in (rc.whole(reqs), rc.portions(reqs), rc.mixed(reqs, 256, seed=2)):
