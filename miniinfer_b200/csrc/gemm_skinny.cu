@@ -21,7 +21,7 @@
 
 namespace {
 
-constexpr int WARPS = 8;
+constexpr int WARPS = 8;        // warps of a block; 16 for matrices with so few rows that 8 would leave SMs without a block
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
@@ -62,13 +62,13 @@ __device__ __forceinline__ float swiglu(float gate, float up) {
   return g / (1.f + expf(-g)) * u;
 }
 
-template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false, int W = WARPS>
+__global__ void __launch_bounds__(W * 32)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
-  extern __shared__ float red[];  // [WARPS][MT*16][NT*8 + 1]
+  extern __shared__ float red[];  // [W][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
-  constexpr int GROUPS = WARPS / KSPLIT;
+  constexpr int GROUPS = W / KSPLIT;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int group = warp / KSPLIT, kpart = warp % KSPLIT;
@@ -212,18 +212,18 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
   }
 }
 
-template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU>
+template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU, int W = WARPS>
 int launch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
            cudaStream_t stream) {
-  const size_t smem = KSPLIT == 1 ? 0 : (size_t)WARPS * (MT * 16) * (NT * 8 + 1) * sizeof(float);
-  auto kernel = gemm_skinny_kernel<MT, NT, KSPLIT, HALF, TOut, SWIGLU>;
+  const size_t smem = KSPLIT == 1 ? 0 : (size_t)W * (MT * 16) * (NT * 8 + 1) * sizeof(float);
+  auto kernel = gemm_skinny_kernel<MT, NT, KSPLIT, HALF, TOut, SWIGLU, W>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return mi_fail("gemm_skinny: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   }
-  const int cols_per_block = (WARPS / KSPLIT) * (SWIGLU ? 8 : NT * 8);
+  const int cols_per_block = (W / KSPLIT) * (SWIGLU ? 8 : NT * 8);
   const int blocks = (N + cols_per_block - 1) / cols_per_block;
-  mi::launch(kernel, dim3(blocks), dim3(WARPS * 32), smem, stream, out, x, w, M, N, K, ldo);
+  mi::launch(kernel, dim3(blocks), dim3(W * 32), smem, stream, out, x, w, M, N, K, ldo);
   MI_LAUNCH_OK("gemm_skinny");
   return 0;
 }
@@ -239,6 +239,13 @@ int pick_ksplit(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M
   int ks = 1;
   while (ks < 8 && (N + (WARPS / ks) * cols - 1) / ((WARPS / ks) * cols) < target) ks *= 2;
   if (K < 64 * ks) ks = 1;   // nothing to split
+  // Few rows (a hidden-size output): even one group of rows per block leaves SMs without a block, and
+  // each warp would walk a long stretch of K.  Sixteen warps per block halve the stretch and double
+  // the bytes in flight.  Few activation rows only: the wide tiles need the registers.
+  if constexpr (MT == 1) {
+    if (ks == 8 && (N + cols - 1) / cols < 148 && K >= 64 * 16)
+      return launch<MT, NT, 16, HALF, TOut, SWIGLU, 16>(out, x, w, M, N, K, ldo, stream);
+  }
   switch (ks) {
     case 1: return launch<MT, NT, 1, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);
     case 2: return launch<MT, NT, 2, HALF, TOut, SWIGLU>(out, x, w, M, N, K, ldo, stream);

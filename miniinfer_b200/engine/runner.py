@@ -145,7 +145,8 @@ class ModelRunner:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
     self.meta = _MetaBuffers(self.device)
     # a part that reads the step on the host would have its decisions frozen into a recorded graph
-    self.graphs_allowed = not any(p.reads_step_on_host for p in spec.all_parts())
+    parts = spec.all_parts() if hasattr(spec, "all_parts") else []
+    self.graphs_allowed = not any(getattr(p, "reads_step_on_host", False) for p in parts)
     self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
     self.last_h2d_bytes = 0
     self.last_launches = 0
