@@ -63,7 +63,7 @@ __device__ __forceinline__ float swiglu(float gate, float up) {
 }
 
 template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false, int W = WARPS>
-__global__ void __launch_bounds__(W * 32)
+__global__ void __launch_bounds__(W * 32, (MT == 1 && W == 8) ? 2 : 1)   // few activation rows: two blocks of 8 warps per SM
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int M, int N, int K, int ldo) {
   extern __shared__ float red[];  // [W][MT*16][NT*8 + 1]
@@ -258,9 +258,12 @@ template <typename TOut>
 int dispatch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, int N, int K, int ldo,
              cudaStream_t stream) {
   // Wider warp tiles re-use the activation fragments; narrower ones make more blocks.
-  if (M <= 8) return pick_ksplit<1, 1, true, TOut>(out, x, w, M, N, K, ldo, stream);
-  if (M <= 16) return pick_ksplit<1, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
   const bool wide = N >= 2048;
+  // (16 weight rows per warp where there are many rows: half as many blocks, all of them on the SMs at once)
+  if (M <= 8) return wide ? pick_ksplit<1, 2, true, TOut>(out, x, w, M, N, K, ldo, stream)
+                          : pick_ksplit<1, 1, true, TOut>(out, x, w, M, N, K, ldo, stream);
+  if (M <= 16) return wide ? pick_ksplit<1, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)
+                           : pick_ksplit<1, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
   if (M <= 32) return wide ? pick_ksplit<2, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)
                            : pick_ksplit<2, 1, false, TOut>(out, x, w, M, N, K, ldo, stream);
   return wide ? pick_ksplit<4, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)
