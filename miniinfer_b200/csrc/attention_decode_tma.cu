@@ -275,8 +275,34 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
       const int split = (int)blockIdx.x - c_first;
 
       const int qp = it % NI;
-      int page = nb > 0 ? bt[(j0 + min(lane, nb - 1) * BK) / a.page_size] : 0;   // the pages of the first 32 tiles
+      // asks for the tiles from .. to of this item, 32 page numbers at a time
+      auto issue_tiles = [&](int from, int to) {
+        for (int c0 = from; c0 < to; c0 += 32) {
+          const int page = bt[(j0 + min(c0 + lane, nb - 1) * BK) / a.page_size];
+          const int run = min(32, to - c0);
+          for (int u = 0; u < run; ++u, ++blk) {
+            const int pg = __shfl_sync(0xffffffffu, page, u);
+            if (lane == 0) {
+              const int s = blk % a.stages;
+              mbar_wait(&empty[s], ((blk / a.stages) & 1) ^ 1, abort, a.status);
+              const int jb = j0 + (c0 + u) * BK;
+              const int y_k = ((pg * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
+              const int y_v = y_k + a.nkv * a.page_size;
+              unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
+              mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
+#pragma unroll
+              for (int x = 0; x < NBOX; ++x) {
+                tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
+                tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+              }
+            }
+          }
+        }
+      };
       if (!waited) {
+        // (Asking for the block's first tiles before the wait - they hold only what earlier steps
+        // wrote - was tried and made the step slower: the early copies compete with the kernel that
+        // is still running.)
         mi::grid_dependency_sync();
         waited = true;
       }
@@ -290,27 +316,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         mbar_expect_tx(&qfull[qp], (uint32_t)(G * HD * 2));
         bulk_load_1d(q_s + (size_t)qp * a.gp * HD, a.q_base + (size_t)row * a.q_stride + (size_t)kvh * G * HD, (uint32_t)(G * HD * 2), &qfull[qp]);
       }
-      for (int c0 = 0; c0 < nb; c0 += 32) {
-        if (c0 > 0) page = bt[(j0 + min(c0 + lane, nb - 1) * BK) / a.page_size];
-        const int run = min(32, nb - c0);
-        for (int u = 0; u < run; ++u, ++blk) {
-          const int pg = __shfl_sync(0xffffffffu, page, u);
-          if (lane == 0) {
-            const int s = blk % a.stages;
-            mbar_wait(&empty[s], ((blk / a.stages) & 1) ^ 1, abort, a.status);
-            const int jb = j0 + (c0 + u) * BK;
-            const int y_k = ((pg * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
-            const int y_v = y_k + a.nkv * a.page_size;
-            unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
-            mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
-#pragma unroll
-            for (int x = 0; x < NBOX; ++x) {
-              tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
-              tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
-            }
-          }
-        }
-      }
+      issue_tiles(0, nb);
       ++it;
       t += nb;
     }
