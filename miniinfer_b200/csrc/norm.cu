@@ -46,13 +46,21 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ resid,
                             const __nv_bfloat16* __restrict__ delta, const float* __restrict__ w,
                             const int* __restrict__ rows, int H, float eps, int write_back) {
-  mi::grid_dependency_sync();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
+  const int H4 = H / 4;
+  // the norm weights and the row list are written by no kernel: fetched before the wait for the preceding kernel
   const int row = rows ? rows[r] : r;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 ww[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int h = threadIdx.x + i * 256;
+    if (h < H4) ww[i] = w4[h];
+  }
+  mi::grid_dependency_sync();
   float4* x = reinterpret_cast<float4*>(resid + (size_t)row * H);
   const uint2* d = delta ? reinterpret_cast<const uint2*>(delta + (size_t)row * H) : nullptr;
-  const int H4 = H / 4;
   float4 v[VPT];
   float ss = 0.f;
 #pragma unroll
@@ -73,14 +81,12 @@ add_rmsnorm_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__
   const float total = mi::block_sum(ss, scratch);
   const float rstd = rsqrtf(total / (float)H + eps);
   uint2* o = reinterpret_cast<uint2*>(out + (size_t)r * H);
-  const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int h = threadIdx.x + i * 256;
     if (h < H4) {
-      const float4 ww = w4[h];
-      const __nv_bfloat162 lo = __floats2bfloat162_rn(ww.x * (v[i].x * rstd), ww.y * (v[i].y * rstd));
-      const __nv_bfloat162 hi = __floats2bfloat162_rn(ww.z * (v[i].z * rstd), ww.w * (v[i].w * rstd));
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(ww[i].x * (v[i].x * rstd), ww[i].y * (v[i].y * rstd));
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(ww[i].z * (v[i].z * rstd), ww[i].w * (v[i].w * rstd));
       uint2 packed;
       packed.x = *reinterpret_cast<const uint32_t*>(&lo);
       packed.y = *reinterpret_cast<const uint32_t*>(&hi);

@@ -119,11 +119,13 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
   __nv_bfloat16* row = qkv + (size_t)tkn * heads * HD;
   const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
 
-  for (int h0 = warp; h0 < heads; h0 += 8 * HEADS_AT_ONCE) {
+  // gridDim.y blocks share a token (few tokens: more blocks, a head per warp; many: one block, four heads per warp)
+  const int stride = 8 * (int)gridDim.y;
+  for (int h0 = (int)blockIdx.y * 8 + warp; h0 < heads; h0 += stride * HEADS_AT_ONCE) {
     uint32_t raw[HEADS_AT_ONCE][2][NP];
 #pragma unroll
     for (int u = 0; u < HEADS_AT_ONCE; ++u) {
-      const int h = h0 + 8 * u;
+      const int h = h0 + stride * u;
       if (h < heads) {
 #pragma unroll
         for (int i = 0; i < NP; ++i) {
@@ -134,7 +136,7 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
     }
 #pragma unroll
     for (int u = 0; u < HEADS_AT_ONCE; ++u) {
-      const int h = h0 + 8 * u;
+      const int h = h0 + stride * u;
       if (h >= heads) break;                          // uniform over the warp
       __nv_bfloat16* x = row + (size_t)h * HD;
       const bool is_q = h < nh;
@@ -210,11 +212,12 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
   MI_REQUIRE(grid.y <= 65535, "qk_norm_rope: too many heads for one launch");
   const bool whole = !cos_sin || rotary_dim == hd;
   if (dtype == MI_BF16 && whole && (hd == 128 || hd == 256)) {
+    const dim3 fast_grid(T, T <= 64 ? (nh + 2 * nkv + 7) / 8 : 1);
     if (hd == 128)
-      mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(fast_grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     else
-      mi::launch(qk_norm_rope_store_fast_kernel<256>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
+      mi::launch(qk_norm_rope_store_fast_kernel<256>, dim3(fast_grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     MI_LAUNCH_OK("qk_norm_rope_store");
     return 0;
