@@ -31,6 +31,11 @@
 // request are added in an order that varies with the batch: its output varies by rounding, as the
 // bf16 path allows (the 32-bit path has its own kernel, whose order is fixed).
 //
+// (Dealing only three quarters of the tiles out evenly and handing the rest out in runs of two
+// tiles from a counter, so that blocks whose copies come in slowly end up with fewer tiles, was
+// tried: every further item costs a merge of the three warps and a partial result, which outweighed
+// the balance gained - a batch-8 decode step took 1.46 ms against 1.15 ms.)
+//
 // No block waits for another block.  Inside a block every wait on an mbarrier is bounded: a wait
 // that runs out raises a flag in shared memory that ends all later waits at once, sets the status
 // word in global memory, and the block runs to its end (its results are then garbage and the host
