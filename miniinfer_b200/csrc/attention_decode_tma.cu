@@ -356,19 +356,32 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         if (last && lane == 0) a.counters[d.e * a.nkv + d.kvh] = 0;     // ready for the next launch
         if (last) {
           __threadfence();
-          // All heads of this kv head at once, in two round trips through L2: (1) every chunk's max
-          // and sum into shared memory, from which the weights follow; (2) every chunk's partial
-          // output, many loads in flight per lane.
+          // All heads of this kv head at once: every chunk's max and sum go to shared memory, from
+          // which the weights follow; the chunks' partial outputs are asked for at the same time.
           constexpr int DS = (HD + 31) / 32;
           const int ns = d.n_splits;
           const float* ml0 = a.part_ml + ((size_t)d.e * a.nh + (size_t)d.kvh * G) * a.max_splits * 2;
           const float* po0 = a.part_o + ((size_t)d.e * a.nh + (size_t)d.kvh * G) * a.max_splits * HD;
+          // four chunks of one head's partial output at a time, many loads in flight per lane
+          auto load_batch = [&](float (&v)[4][DS], int gh, int sp0) {
+            const float* po = po0 + (size_t)gh * a.max_splits * HD;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int i = 0; i < DS; ++i) {
+                const int dd = i * 32 + lane;
+                v[u][i] = (sp0 + u < ns && dd < HD) ? __ldcg(po + (size_t)(sp0 + u) * HD + dd) : 0.f;
+              }
+          };
+          float cur[4][DS], nxt[4][DS];
+          // one round trip through L2 for every chunk's max and sum and for the first batch of outputs
           for (int idx = lane; idx < G * ns; idx += 32) {
             const int gh = idx / ns, sp = idx % ns;
             const float2 v = __ldcg(reinterpret_cast<const float2*>(ml0 + ((size_t)gh * a.max_splits + sp) * 2));
             merge_s[2 * idx] = v.x;
             merge_s[2 * idx + 1] = v.y;
           }
+          load_batch(cur, 0, 0);
           __syncwarp();
           for (int gh = 0; gh < G; ++gh) {
             float m = -INFINITY;
@@ -382,42 +395,34 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
             for (int sp = lane; sp < ns; sp += 32) merge_s[2 * (gh * ns + sp)] = exp2f(merge_s[2 * (gh * ns + sp)] - m) * inv;   // the chunk's weight
           }
           __syncwarp();
-          for (int gh = 0; gh < G; ++gh) {
-            float acc[DS];
+          // the batches in order (head by head); the next one is on its way while this one is added up
+          const int per_head = (ns + 3) / 4;
+          float acc[DS];
+          for (int bi = 0; bi < G * per_head; ++bi) {
+            const int gh = bi / per_head, sp0 = (bi % per_head) * 4;
+            if (bi + 1 < G * per_head) load_batch(nxt, (bi + 1) / per_head, ((bi + 1) % per_head) * 4);
+            if (sp0 == 0) {
 #pragma unroll
-            for (int i = 0; i < DS; ++i) acc[i] = 0.f;
-            const float* po = po0 + (size_t)gh * a.max_splits * HD;
-            int sp = 0;
-            for (; sp + 4 <= ns; sp += 4) {          // 4 * DS independent loads per lane
-              float v[4][DS];
-#pragma unroll
-              for (int u = 0; u < 4; ++u)
-#pragma unroll
-                for (int i = 0; i < DS; ++i) {
-                  const int dd = i * 32 + lane;
-                  v[u][i] = dd < HD ? __ldcg(po + (size_t)(sp + u) * HD + dd) : 0.f;
-                }
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float f = merge_s[2 * (gh * ns + sp + u)];
-#pragma unroll
-                for (int i = 0; i < DS; ++i) acc[i] = fmaf(v[u][i], f, acc[i]);
-              }
+              for (int i = 0; i < DS; ++i) acc[i] = 0.f;
             }
-            for (; sp < ns; ++sp) {
-              const float f = merge_s[2 * (gh * ns + sp)];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float f = sp0 + u < ns ? merge_s[2 * (gh * ns + sp0 + u)] : 0.f;
+#pragma unroll
+              for (int i = 0; i < DS; ++i) acc[i] = fmaf(cur[u][i], f, acc[i]);
+            }
+            if (sp0 + 4 >= ns) {
+              const int head = d.kvh * G + gh;
 #pragma unroll
               for (int i = 0; i < DS; ++i) {
                 const int dd = i * 32 + lane;
-                if (dd < HD) acc[i] = fmaf(__ldcg(po + (size_t)sp * HD + dd), f, acc[i]);
+                if (dd < HD) a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(acc[i]);
               }
             }
-            const int head = d.kvh * G + gh;
 #pragma unroll
-            for (int i = 0; i < DS; ++i) {
-              const int dd = i * 32 + lane;
-              if (dd < HD) a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(acc[i]);
-            }
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int i = 0; i < DS; ++i) cur[u][i] = nxt[u][i];
           }
         }
       }
