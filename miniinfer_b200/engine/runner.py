@@ -33,6 +33,8 @@ from .context import StepContext, Workspace
 PREFILL_TILE = 64   # query rows of one prefill-attention tile
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 GRAPH_CONTEXT_STEP = 1024   # a captured decode step serves contexts up to a multiple of this
+STEP_GRAPHS_KEPT = 8        # graphs of steps other than decode-only ones (prompt portions, mixed steps) that are kept
+STEP_GRAPH_AFTER = 2        # a step of a shape is recorded once that shape has been seen this many times
 
 
 @dataclass
@@ -148,6 +150,9 @@ class ModelRunner:
     parts = spec.all_parts() if hasattr(spec, "all_parts") else []
     self.graphs_allowed = not any(getattr(p, "reads_step_on_host", False) for p in parts)
     self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+    # steps of any other kind, by shape (see _shape_key): how often seen, and the graphs of the repeated ones
+    self._shape_seen: Dict[tuple, int] = {}
+    self._step_graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
     self.last_h2d_bytes = 0
     self.last_launches = 0
 
@@ -250,7 +255,18 @@ class ModelRunner:
   def prepare(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
     """Reserves cache room for the items' tokens and builds the step's device-side description
     with one host-to-device copy."""
-    starts = self._check_and_reserve(items)
+    self._reserved_starts = self._check_and_reserve(items)
+    return self._prepare_reserved(items, extras)
+
+  def _prepare_reserved(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
+    starts = self._reserved_starts
+    try:
+      return self._prepare_described(items, starts, extras)
+    except BaseException:
+      self._finish(items, False)
+      raise
+
+  def _prepare_described(self, items, starts, extras) -> StepContext:
     arrays = self._describe(items, starts, extras)
     offsets = self.meta.upload(arrays)
     self.last_h2d_bytes = self.meta.bytes_copied
@@ -280,9 +296,85 @@ class ModelRunner:
       else:
         self.cache.cancel(it.req_id, len(it.tokens))
 
+  # ------------------------------------------------------------------ steps of a repeated shape, from CUDA graphs
+
+  def _shape_key(self, items: Sequence[StepItem], starts: Sequence[int], sampled: bool) -> tuple:
+    """What the launches of a step depend on: the counts of tokens, items, prefill tiles, decode
+    items and wanted rows, the context class of the decode items (their split-KV grid), and whether
+    the sampler runs.  Everything else about the step is in the description on the device."""
+    T = B = tiles = n_dec = R = 0
+    longest = 0
+    for it, st in zip(items, starts):
+      n = len(it.tokens)
+      T += n
+      B += 1
+      R += len(it.want)
+      if n == 1:
+        n_dec += 1
+        longest = max(longest, st + 1)
+      else:
+        tiles += -(-n // PREFILL_TILE)
+    ctx_class = min(self.cache.max_model_len, -(-longest // GRAPH_CONTEXT_STEP) * GRAPH_CONTEXT_STEP) if n_dec else 0
+    return (T, B, tiles, n_dec, R, ctx_class, sampled)
+
+  def _shape_step(self, items: Sequence[StepItem], extras: Optional[dict], sample_fn) -> Optional[_DecodeGraph]:
+    """Runs the step from a CUDA graph if a step of its shape has been recorded, records it if the
+    shape has been seen often enough; returns the graph (logits and tokens in its buffers), or None
+    if the step is to run kernel by kernel.  The items' cache room is reserved on return either way;
+    a returned graph means the step has run and is committed."""
+    starts = self._check_and_reserve(items)
+    self._reserved_starts = starts
+    if not (self.graphs_allowed and self.device.type == "cuda"):
+      return None
+    key = self._shape_key(items, starts, sample_fn is not None)
+    g = self._step_graphs.get(key)
+    if g is None:
+      seen = self._shape_seen.get(key, 0) + 1
+      if len(self._shape_seen) > 4096:
+        self._shape_seen.clear()
+      self._shape_seen[key] = seen
+      if seen < STEP_GRAPH_AFTER:
+        return None
+    try:
+      arrays = self._describe(items, starts, extras)
+      if g is None:
+        g = _DecodeGraph(len(items), self.device)
+        g.max_ctx_len = key[5]
+        g.offsets, g.total = g.meta.layout(arrays)
+        g.meta.upload(arrays)
+        self.cache.sync()
+        self._capture(g, arrays, g.offsets, sample_fn, rows=key[4])
+        self._step_graphs[key] = g
+        while len(self._step_graphs) > STEP_GRAPHS_KEPT:
+          self._step_graphs.popitem(last=False)
+      else:
+        self._step_graphs.move_to_end(key)
+        offsets = g.meta.upload(arrays, fixed_capacity=True)
+        if offsets != g.offsets:
+          raise RuntimeError("a step's description does not have the layout its shape was recorded with")
+        self.cache.sync()
+      self.last_h2d_bytes = g.meta.bytes_copied
+      g.graph.replay()
+      self.last_launches = g.launches
+    except BaseException:
+      self._finish(items, False)
+      raise
+    self._finish(items, True)
+    return g
+
   @torch.no_grad()
-  def step(self, items: Sequence[StepItem], extras: Optional[dict] = None, return_ctx: bool = False):
-    ctx = self.prepare(items, extras)
+  def step(self, items: Sequence[StepItem], extras: Optional[dict] = None, return_ctx: bool = False,
+           use_graphs: bool = True):
+    """Runs one step; returns the float32 logits of the wanted rows.  A step whose shape repeats is
+    replayed from a CUDA graph; its logits then live in a buffer that the next step of the same
+    shape overwrites."""
+    if use_graphs and not return_ctx:
+      g = self._shape_step(items, extras, None)
+      if g is not None:
+        return g.logits
+      ctx = self._prepare_reserved(items, extras)
+    else:
+      ctx = self.prepare(items, extras)
     before = ops.launch_count()
     try:
       logits = self.forward(ctx)
@@ -307,11 +399,23 @@ class ModelRunner:
     bucket = next((b for b in GRAPH_BUCKETS if b >= len(items)), None)
     if use_graphs and self.graphs_allowed and decode_only and bucket is not None and self.device.type == "cuda":
       return self._graph_step(items, sampling, sample_fn, tokens_out, bucket)
-    logits, ctx = self.step(items, sampling, return_ctx=True)
-    if R:
-      before = ops.launch_count()
-      sample_fn(logits, ctx.extra, tokens_out[:R], self.ws)
-      self.last_launches += ops.launch_count() - before
+    if use_graphs and R:
+      g = self._shape_step(items, sampling, sample_fn)      # a step of a repeated shape: forward pass and sampler from one graph
+      if g is not None:
+        return g.tokens[:R]
+      ctx = self._prepare_reserved(items, sampling)
+    else:
+      ctx = self.prepare(items, sampling)
+    before = ops.launch_count()
+    try:
+      logits = self.forward(ctx)
+      if R:
+        sample_fn(logits, ctx.extra, tokens_out[:R], self.ws)
+    except BaseException:
+      self._finish(items, False)
+      raise
+    self._finish(items, True)
+    self.last_launches = ops.launch_count() - before
     return tokens_out[:R]
 
   def _padded(self, a: "OrderedDict[str, np.ndarray]", bucket: int) -> "OrderedDict[str, np.ndarray]":
@@ -411,32 +515,39 @@ class ModelRunner:
       put(f"extra:{k}", v if v.dtype == np.int32 else v.view(np.int32))
     g.meta.send(g.total)
 
-  def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn) -> None:
+  def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn, rows: Optional[int] = None) -> None:
+    """Records forward pass (and sampler, if given) over the graph's own buffers.  ``rows``: sampled
+    rows (default: one per entry of the bucket)."""
     # every length of the context class must be served by the captured launch: size the split-KV grid for it
-    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=g.max_ctx_len)
-    g.tokens = torch.zeros(g.bucket, dtype=torch.int32, device=self.device)
+    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=g.max_ctx_len if g.max_ctx_len else None)
+    g.tokens = torch.zeros(max(g.bucket if rows is None else rows, 1), dtype=torch.int32, device=self.device)
 
     def run():
       g.logits = self.forward(g.ctx)
-      sample_fn(g.logits, g.ctx.extra, g.tokens, g.ws)
+      if sample_fn is not None and g.logits.shape[0] > 0:
+        sample_fn(g.logits, g.ctx.extra, g.tokens[:g.logits.shape[0]], g.ws)
 
-    run()                                   # sizes the workspace and configures the kernels
-    torch.cuda.current_stream().synchronize()
-    g.ws.frozen = True
-    before = ops.launch_count()
-    graph = torch.cuda.CUDAGraph()
-    with ops.recording_graph(), torch.cuda.graph(graph):
+    # The first run sizes the workspace, configures the kernels and makes the libraries load what
+    # they will launch (nothing may be loaded while a graph is recorded): it takes the same paths
+    # as the recording.
+    with ops.recording_graph():
       run()
+      torch.cuda.current_stream().synchronize()
+      g.ws.frozen = True
+      before = ops.launch_count()
+      graph = torch.cuda.CUDAGraph()
+      with torch.cuda.graph(graph):
+        run()
     g.launches = ops.launch_count() - before
     g.graph = graph
 
   def check_status(self) -> None:
     """Raises if a bounded wait inside a kernel ran out since the buffers were made (the step's
     results are then not to be trusted).  Reads a few words from the device."""
-    for ws in [self.ws] + [g.ws for g in self._graphs.values()]:
+    for ws in [self.ws] + [g.ws for g in self._graphs.values()] + [g.ws for g in self._step_graphs.values()]:
       code = ops.device_status(ws)
       if code:
         raise ops.KernelError(f"a bounded wait inside an attention kernel ran out (status {code})")
 
   def num_graphs(self) -> int:
-    return sum(1 for g in self._graphs.values() if g.graph is not None)
+    return sum(1 for g in list(self._graphs.values()) + list(self._step_graphs.values()) if g.graph is not None)

@@ -100,6 +100,38 @@ def test_float32_logits_do_not_depend_on_the_cut_at_all(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_a_repeated_shape_run_from_graphs_and_give_the_same_logits(model_dirs, dtype):
+  """A step whose shape (counts of tokens, items, tiles, decode items, wanted rows) has been seen
+  before is recorded as a CUDA graph and replayed: prompts of equal length, and mixed steps of one
+  decode token beside a prompt portion.  Same logits as the same steps run kernel by kernel."""
+  from miniinfer_b200.engine import StepItem
+  d = model_dirs("C")
+  V = ALL["C"]["vocab_size"]
+  with_graphs, eager = runner_for(d, dtype, 512, 64), runner_for(d, dtype, 512, 64)
+  g = torch.Generator().manual_seed(11)
+  tok = lambda n: torch.randint(0, V, (n,), generator=g).tolist()
+  for rnd in range(5):
+    a, b = f"a{rnd}", f"b{rnd}"
+    steps = [[StepItem(a, tok(70), [0, 69])],
+             [StepItem(a, tok(1), [0]), StepItem(b, tok(33), [32])],
+             [StepItem(a, tok(1), [0]), StepItem(b, tok(1), [0])]]
+    for r in (with_graphs, eager):
+      r.cache.admit(a); r.cache.admit(b)
+    for items in steps:
+      got = with_graphs.runner.step(items).float().cpu()
+      want = eager.runner.step(items, use_graphs=False).float().cpu()
+      assert got.shape == want.shape
+      if dtype == "float32":
+        assert torch.equal(got, want), (rnd, [len(i.tokens) for i in items])
+      else:
+        assert (got - want).abs().max() <= 1e-2 * max(1.0, float(want.abs().max())), rnd
+    for r in (with_graphs, eager):
+      r.cache.release_request(a); r.cache.release_request(b)
+  assert with_graphs.runner.num_graphs() == 3 and eager.runner.num_graphs() == 0
+  with_graphs.runner.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(model_dirs, tmp_path, dtype):
   """bin/trace_run as a user calls it: a child process, steps on standard input, files out."""
   d = model_dirs("A")
