@@ -1,5 +1,7 @@
 """The small configurations the tests run on.  A and B differ in every size and option; C adds a
-sliding window on some layers; all have sizes that are no power of two somewhere."""
+sliding window on some layers; D has head size 64, which with pages of 64 tokens takes the engine
+through the TMA decode kernel and the tcgen05 prefill kernel, with a window on its second layer; all
+have sizes that are no power of two somewhere."""
 
 TINY_A = dict(
   architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=64,
@@ -21,4 +23,12 @@ TINY_C = dict(
   attention_bias=False, use_sliding_window=True, sliding_window=40, max_window_layers=2,
   hidden_act="silu", initializer_range=0.02)
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head size 64, two query heads per kv head, a window of 100 on the second of two layers
+TINY_D = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=72,
+  num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=144, vocab_size=333,
+  rope_theta=20000.0, rms_norm_eps=1e-6, max_position_embeddings=512, tie_word_embeddings=False,
+  attention_bias=False, use_sliding_window=True, sliding_window=100, max_window_layers=1,
+  hidden_act="silu", initializer_range=0.02)
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
