@@ -168,6 +168,9 @@ CASES = [
   ([(700, 300), (130, 129), (2, 2)], 3, 3, 128, 64, None),
   ([(2500, 1100), (200, 1)], 4, 2, 128, 128, 700),
   ([(100, 100)], 6, 1, 64, 64, None),
+  # long prompts: ten and more key tiles per block of the tcgen05 prefill kernel, 64-token and 128-token blocks
+  ([(1500, 700), (1100, 1100)], 4, 2, 128, 64, None),
+  ([(1300, 1300), (40, 1)], 3, 1, 64, 64, None),
 ]
 
 
