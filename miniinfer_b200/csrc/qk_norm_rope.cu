@@ -197,6 +197,110 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
   }
 }
 
+// Head size 128 with many tokens, in 16-byte steps: a block takes one token, a warp four heads at a
+// time, eight lanes per head; a lane holds elements 8l .. 8l + 7 of the head and their partners
+// 64 further on, so the rotation needs no exchange and the sum of squares three shuffles.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_wide128_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                  const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                  const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ kv_layer, int nh, int nkv,
+                                  int page_size, float eps, int T) {
+  constexpr int HD = 128, HALF = 64;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hq = lane >> 3, l8 = lane & 7;
+  const int heads = nh + 2 * nkv;
+  bool waited = false;
+  for (int tkn = blockIdx.x; tkn < T; tkn += gridDim.x) {     // a few tokens per block
+  // what no kernel writes is fetched before the wait for the preceding kernel: the table's row
+  float c[8], sn[8];
+  {
+    const float* cs = cos_sin ? cos_sin + (size_t)positions[tkn] * HD : nullptr;
+    const float4 c0 = cs ? *reinterpret_cast<const float4*>(cs + 8 * l8) : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 c1 = cs ? *reinterpret_cast<const float4*>(cs + 8 * l8 + 4) : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 s0 = cs ? *reinterpret_cast<const float4*>(cs + HALF + 8 * l8) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 s1 = cs ? *reinterpret_cast<const float4*>(cs + HALF + 8 * l8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+  }
+  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
+  if (!waited) {
+    mi::grid_dependency_sync();
+    waited = true;
+  }
+  __nv_bfloat16* row = qkv + (size_t)tkn * heads * HD;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+
+  for (int hb = 0; hb < heads; hb += 32) {
+    const int h = hb + warp * 4 + hq;
+    const bool live = h < heads;
+    const bool is_q = h < nh;
+    const bool is_k = !is_q && h < nh + nkv;
+    __nv_bfloat16* x = row + (size_t)(live ? h : 0) * HD;
+    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+    if (live) {
+      ra = *reinterpret_cast<const uint4*>(x + 8 * l8);
+      rb = *reinterpret_cast<const uint4*>(x + HALF + 8 * l8);
+    }
+    const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+    __nv_bfloat16* dst = (live && !is_q && slot >= 0)
+        ? kv_layer + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD : nullptr;
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    float a[8], b[8];
+    {
+      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+        a[2 * i] = fa.x; a[2 * i + 1] = fa.y; b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+    // every lane takes part in the shuffles; the groups of eight lanes are heads
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    if (live && (is_q || is_k)) {
+      if (w) {
+        const float rstd = rsqrtf(ss / (float)HD + eps);
+        const float4 wa0 = *reinterpret_cast<const float4*>(w + 8 * l8), wa1 = *reinterpret_cast<const float4*>(w + 8 * l8 + 4);
+        const float4 wb0 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8), wb1 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8 + 4);
+        const float wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+        const float wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a[i] *= rstd * wa[i];
+          b[i] *= rstd * wb[i];
+        }
+      }
+      if (cos_sin) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float na = a[i] * c[i] - b[i] * sn[i], nb = b[i] * c[i] + a[i] * sn[i];
+          a[i] = na; b[i] = nb;
+        }
+      }
+      __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
+      __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        pb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+      }
+      *reinterpret_cast<uint4*>(x + 8 * l8) = ra;
+      *reinterpret_cast<uint4*>(x + HALF + 8 * l8) = rb;
+    }
+    if (dst) {                                         // keys as normed and rotated, values as they are
+      *reinterpret_cast<uint4*>(dst + 8 * l8) = ra;
+      *reinterpret_cast<uint4*>(dst + HALF + 8 * l8) = rb;
+    }
+  }
+  }
+  if (!waited) mi::grid_dependency_sync();
+}
+
 }  // namespace
 
 MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const float* k_w, const float* cos_sin,
@@ -213,7 +317,12 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
   const bool whole = !cos_sin || rotary_dim == hd;
   if (dtype == MI_BF16 && whole && (hd == 128 || hd == 256)) {
     const dim3 fast_grid(T, T <= 64 ? (nh + 2 * nkv + 7) / 8 : 1);
-    if (hd == 128)
+    const bool aligned16 = ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)kv_layer % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0 &&
+                           ((uintptr_t)q_w % 16) == 0 && ((uintptr_t)k_w % 16) == 0;
+    if (hd == 128 && T > 64 && aligned16)
+      mi::launch(qk_norm_rope_store_wide128_kernel, dim3(T < 148 * 8 ? T : 148 * 8), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w,
+                 cos_sin, positions, slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps, T);
+    else if (hd == 128)
       mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(fast_grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,
                                                                            slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps);
     else
