@@ -352,7 +352,7 @@ def main() -> int:
                "tied_head": True, "global_batch": args.batch, "seq_len": CONTEXT, "generated": GENERATED,
                "max_model_len": MAX_MODEL_LEN, "page_size": PAGE, "parallelism": "single GPU",
                "l2": "each step reads weights+cache (>1 GB), larger than L2", "sampling": "temperature 0.6",
-               "decode_path": "CUDA graph replay"},
+               "decode_path": "CUDA graph replay; e2e: a step is launched before the tokens of the step before are read (enable_overlap)"},
     "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "ms_per_step": round(e2e["ms"], 4),
             "h2d_bytes_per_step": int(e2e["h2d"]), "d2h_bytes_per_step": int(e2e["d2h"])},
     "gpu_launches": int(dec["launches_per_step"] * args.steps),

@@ -48,6 +48,7 @@ class EngineConfig:
   enable_chunked_prefill: bool = True
   # execution
   enforce_eager: bool = False              # True: no CUDA graphs for decode steps
+  enable_overlap: bool = True              # a decode step is launched before the tokens of the step before it are read back
   seed: int = 0
 
   def __post_init__(self):

@@ -79,6 +79,9 @@ class LLMEngine:
     self._next_id = 0
     self._tokens_host: Optional[torch.Tensor] = None
     self._tokens_dev: Optional[torch.Tensor] = None
+    self._host_tokens: List[Optional[torch.Tensor]] = [None, None]   # two pinned arrays: a step's tokens may still be on their way when the next is launched
+    self._flip = 0
+    self._inflight: Optional["LLMEngine._InFlight"] = None
     self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0,
                   "host_schedule_s": 0.0, "host_launch_s": 0.0, "host_wait_s": 0.0, "host_update_s": 0.0}
 
@@ -135,10 +138,10 @@ class LLMEngine:
     return rid
 
   def is_finished(self) -> bool:
-    return not self.scheduler.has_unfinished()
+    return not self.has_unfinished()
 
   def has_unfinished(self) -> bool:
-    return self.scheduler.has_unfinished()
+    return self._inflight is not None or self.scheduler.has_unfinished()
 
   # ------------------------------------------------------------------ one step
 
@@ -149,50 +152,130 @@ class LLMEngine:
       self._tokens_host = torch.empty(cap, dtype=torch.int32, pin_memory=self.device.type == "cuda")
     return self._tokens_dev, self._tokens_host
 
-  @torch.no_grad()
-  def step(self) -> List[Dict[str, Any]]:
-    """Schedules, runs and samples one step; returns the outputs of the requests that finished."""
-    t0 = time.perf_counter()
-    out = self.scheduler.schedule()
-    if not out.items:
-      return []
-    t1 = time.perf_counter()
+  # A launched step whose tokens the host has not read yet: its scheduler output, the requests it
+  # samples for (row order), the pinned array the tokens are copied to, the event after that copy,
+  # and the device view of the tokens (the next step may take its input there).
+  class _InFlight:
+    __slots__ = ("out", "reqs", "host", "done", "tokens_dev", "graph_decode")
+
+  def _launch(self, out: SchedulerOutput, ids_on_device: Optional[torch.Tensor] = None) -> "LLMEngine._InFlight":
+    """Describes and launches the scheduled step and starts the copy of its tokens to the host."""
     items, sampling_reqs = [], []
     for it in out.items:
       n = len(it.tokens)
       items.append(StepItem(it.request.req_id, it.tokens, (n - 1,) if it.samples else ()))
       if it.samples:
         sampling_reqs.append(it.request)
-    extras = Sampler.pack([r.params for r in sampling_reqs], [r.seed for r in sampling_reqs],
-                          [len(r.output_ids) for r in sampling_reqs]) if sampling_reqs else {}
-    sampled: Dict[Hashable, int] = {}
+    counters = [len(r.output_ids) + (1 if ids_on_device is not None else 0) for r in sampling_reqs]   # the token in flight counts
+    extras = Sampler.pack([r.params for r in sampling_reqs], [r.seed for r in sampling_reqs], counters) if sampling_reqs else {}
     R = len(sampling_reqs)
-    dev, host = self._token_buffers(max(R, 1))
-    toks_dev = self.runner.step_and_sample(items, extras, Sampler.sample, dev, use_graphs=not self.config.enforce_eager)
-    t2 = time.perf_counter()
+    dev, _ = self._token_buffers(max(R, 1))
+    toks_dev = self.runner.step_and_sample(items, extras, Sampler.sample, dev, use_graphs=not self.config.enforce_eager,
+                                           ids_on_device=ids_on_device)
     self.stats["h2d_bytes"] += self.runner.last_h2d_bytes
     self.stats["launches"] += self.runner.last_launches
-    if R:
-      host[:R].copy_(toks_dev, non_blocking=True)
-      if self.device.type == "cuda":
-        torch.cuda.current_stream().synchronize()
-      toks = host[:R].tolist()
-      sampled = {r.req_id: t for r, t in zip(sampling_reqs, toks)}
-      self.stats["d2h_bytes"] += 4 * R
-    t3 = time.perf_counter()
     self.stats["steps"] += 1
-    if self.stats["steps"] % 256 == 0:
-      self.runner.check_status()
     self.stats["prefill_tokens"] += out.num_prefill_tokens
     self.stats["decode_tokens"] += out.num_decode_tokens
-    done = self.scheduler.update(out, sampled)
-    outs = [self._output_of(r) for r in done]
-    t4 = time.perf_counter()
+    fl = LLMEngine._InFlight()
+    fl.out, fl.reqs, fl.tokens_dev = out, sampling_reqs, toks_dev
+    fl.graph_decode = not self.config.enforce_eager and self.runner.graph_decode_bucket(items) is not None
+    self._flip ^= 1
+    fl.host = self._host_tokens[self._flip]
+    if fl.host is None or fl.host.numel() < max(R, 1):
+      fl.host = self._host_tokens[self._flip] = torch.empty(max(R, 256), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+    fl.done = None
+    if R:
+      fl.host[:R].copy_(toks_dev, non_blocking=True)
+      self.stats["d2h_bytes"] += 4 * R
+      if self.device.type == "cuda":
+        fl.done = torch.cuda.Event()
+        fl.done.record()
+    return fl
+
+  def _finish(self, fl: "LLMEngine._InFlight") -> List[Dict[str, Any]]:
+    """Waits for the step's tokens and hands them to the scheduler; returns the outputs of the requests that finished."""
+    if fl.done is not None:
+      fl.done.synchronize()
+    toks = fl.host[:len(fl.reqs)].tolist() if fl.reqs else []
+    # a request that ended one step ago (a stop token the host had not seen yet) was run once more: that token is dropped
+    sampled = {r.req_id: t for r, t in zip(fl.reqs, toks)}
+    live = [it for it in fl.out.items if it.request.status != "finished"]
+    if len(live) != len(fl.out.items):
+      fl.out.items = live
+    done = self.scheduler.update(fl.out, sampled)
+    if self.stats["steps"] % 256 == 0:
+      self.runner.check_status()
+    return [self._output_of(r) for r in done]
+
+  def _continuation(self, fl: "LLMEngine._InFlight") -> Optional[SchedulerOutput]:
+    """The step after ``fl`` if it can be told without ``fl``'s tokens: ``fl`` was a graph step of
+    decode tokens only, nothing waits for admission, no request of it ends by length with the
+    token in flight, and every request finds room for one more token.  Its items carry a
+    placeholder token; the step takes the tokens from the device."""
+    sch = self.scheduler
+    if not self.config.enable_overlap or not fl.graph_decode or sch.waiting:
+      return None
+    if len(fl.reqs) != len(fl.out.items) or len(fl.reqs) != len(sch.running) or fl.out.num_prefill_tokens:
+      return None
+    for r, running in zip(fl.reqs, sch.running):
+      if r is not running or len(r.output_ids) + 2 > r.max_tokens:
+        return None
+    need = [0] * len(self.cache.paged_groups)
+    for r in fl.reqs:
+      if self.cache.length_of(r.req_id) + 1 > self.cache.max_model_len:
+        return None
+      for g, n in enumerate(self.cache.pages_needed(r.req_id, 1)):
+        need[g] += n
+    if any(n > f for n, f in zip(need, self.cache.free_pages())):
+      return None
+    from .scheduler import ScheduledItem
+    nxt = SchedulerOutput(items=[ScheduledItem(r, [0], True) for r in fl.reqs])
+    nxt.num_decode_tokens = len(fl.reqs)
+    return nxt
+
+  @torch.no_grad()
+  def step(self) -> List[Dict[str, Any]]:
+    """Schedules, runs and samples one step; returns the outputs of the requests that finished.
+    With ``enable_overlap`` a decode step that follows a decode step of the same requests is
+    launched before the tokens of the step before are read (it takes them on the device), so the
+    host's work on a step runs beside the device's; what a request generates does not change.  A
+    request that ends with a stop token is then run for one token more, which is dropped."""
+    t0 = time.perf_counter()
+    outs: List[Dict[str, Any]] = []
+    fl = self._inflight
+    if fl is not None:
+      nxt = self._continuation(fl)
+      if nxt is not None:
+        t1 = time.perf_counter()
+        self._inflight = self._launch(nxt, ids_on_device=fl.tokens_dev)
+        t2 = time.perf_counter()
+        outs = self._finish(fl)
+        t3 = time.perf_counter()
+        self.stats["host_schedule_s"] += t1 - t0
+        self.stats["host_launch_s"] += t2 - t1
+        self.stats["host_wait_s"] += t3 - t2
+        return outs
+      outs = self._finish(fl)
+      self._inflight = None
+    t0b = time.perf_counter()
+    out = self.scheduler.schedule()
+    if not out.items:
+      return outs
+    t1 = time.perf_counter()
+    fl = self._launch(out)
+    t2 = time.perf_counter()
+    if self.config.enable_overlap and fl.graph_decode:
+      self._inflight = fl              # its tokens are read at the next call
+      t3 = t4 = time.perf_counter()
+    else:
+      t3 = time.perf_counter()
+      outs += self._finish(fl)
+      t4 = time.perf_counter()
     # Host seconds by phase: deciding the step, describing and launching it, waiting for the tokens, book-keeping.
-    self.stats["host_schedule_s"] += t1 - t0
+    self.stats["host_schedule_s"] += t1 - t0b
     self.stats["host_launch_s"] += t2 - t1
-    self.stats["host_wait_s"] += t3 - t2
-    self.stats["host_update_s"] += t4 - t3
+    self.stats["host_wait_s"] += (t0b - t0) + (t4 - t3)
     return outs
 
   def _output_of(self, req: Request) -> Dict[str, Any]:

@@ -388,17 +388,30 @@ class ModelRunner:
   # ------------------------------------------------------------------ sampling steps, with CUDA graphs for decode
 
   @torch.no_grad()
+  def graph_decode_bucket(self, items: Sequence[StepItem]) -> Optional[int]:
+    """The batch-size bucket whose CUDA graph runs this step, if it is a step of decode tokens only,
+    each wanting its one row; else None."""
+    if not (self.graphs_allowed and self.device.type == "cuda"):
+      return None
+    if not all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items):
+      return None
+    return next((b for b in GRAPH_BUCKETS if b >= len(items)), None)
+
   def step_and_sample(self, items: Sequence[StepItem], sampling: Dict[str, np.ndarray],
                       sample_fn: Callable[..., None],
-                      tokens_out: torch.Tensor, use_graphs: bool = True) -> torch.Tensor:
+                      tokens_out: torch.Tensor, use_graphs: bool = True,
+                      ids_on_device: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Runs the step and samples one token for each wanted row into ``tokens_out`` (int32, device).
     ``sampling``: packed per-row options (``Sampler.pack``).  Returns the tokens' device view.
-    A step of decode tokens only, each wanting its one row, is replayed from a CUDA graph."""
+    A step of decode tokens only, each wanting its one row, is replayed from a CUDA graph; for such
+    a step ``ids_on_device`` (int32, one per item) may give the tokens instead of the items: the
+    tokens a step before has sampled and the host has not read yet."""
     R = sum(len(it.want) for it in items)
-    decode_only = all(len(it.tokens) == 1 and tuple(it.want) == (0,) for it in items)
-    bucket = next((b for b in GRAPH_BUCKETS if b >= len(items)), None)
-    if use_graphs and self.graphs_allowed and decode_only and bucket is not None and self.device.type == "cuda":
-      return self._graph_step(items, sampling, sample_fn, tokens_out, bucket)
+    bucket = self.graph_decode_bucket(items) if use_graphs else None
+    if ids_on_device is not None and bucket is None:
+      raise ValueError("tokens on the device are taken by graph decode steps only")
+    if bucket is not None:
+      return self._graph_step(items, sampling, sample_fn, tokens_out, bucket, ids_on_device)
     if use_graphs and R:
       g = self._shape_step(items, sampling, sample_fn)      # a step of a repeated shape: forward pass and sampler from one graph
       if g is not None:
@@ -449,7 +462,7 @@ class ModelRunner:
         raise KeyError(k)
     return out
 
-  def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int) -> torch.Tensor:
+  def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int, ids_on_device=None) -> torch.Tensor:
     starts = self._check_and_reserve(items)
     B = len(items)
     try:
@@ -469,6 +482,11 @@ class ModelRunner:
         self._fill_decode(g, items, starts, sampling)
         self.cache.sync()
       self.last_h2d_bytes = g.meta.bytes_copied
+      if ids_on_device is not None:
+        # after the upload, before the replay, in stream order: the tokens go from where the step
+        # before left them (possibly this graph's own token buffer) into this step's description
+        o, _ = g.offsets["ids"]
+        g.meta.dev[o:o + B].copy_(ids_on_device[:B], non_blocking=True)
       g.graph.replay()
       self.last_launches = g.launches
     except BaseException:

@@ -77,6 +77,29 @@ def test_preemption_on_the_gpu_keeps_the_tokens(model_dirs):
     assert o["token_ids"] == plain.generate(w, c, p, 20, temperature=0.7, seed=9)
 
 
+def test_overlap_gives_the_same_tokens_also_when_a_request_ends_with_a_stop_token(model_dirs):
+  """With enable_overlap a decode step is launched before the tokens of the step before are read; a
+  request that ends with a stop token is then run once more and that token dropped.  Same tokens,
+  same finish reasons, every page back."""
+  from miniinfer_b200 import SamplingParams
+  d = model_dirs("B")
+  prompts = list(rc.make_requests(512, (9, 40, 71, 3), seed=2).values())
+  sp = [SamplingParams(temperature=0.8, max_tokens=(16, 24, 9, 30)[i], seed=50 + i) for i in range(4)]
+  kw = dict(page_size=8, num_pages=60, max_num_seqs=4, max_model_len=160)
+  plain_loop, overlapped = engine(d, "float32", enable_overlap=False, **kw), engine(d, "float32", enable_overlap=True, **kw)
+  first = plain_loop.generate(prompts, sp)
+  stop = first[1]["token_ids"][6]              # becomes a stop token: at least the second request ends early
+  for e in (plain_loop, overlapped):
+    e.scheduler.eos_ids = {stop}
+  a, b = plain_loop.generate(prompts, sp), overlapped.generate(prompts, sp)
+  assert [o["token_ids"] for o in a] == [o["token_ids"] for o in b]
+  assert [o["finish_reason"] for o in a] == [o["finish_reason"] for o in b]
+  assert a[1]["finish_reason"] == "eos" and len(a[1]["token_ids"]) <= 7
+  assert overlapped.cache.free_pages() == [60] and plain_loop.cache.free_pages() == [60]
+  overlapped.cache.check_invariants()
+  assert overlapped.runner.num_graphs() >= 1
+
+
 def test_command_line(model_dirs):
   d = model_dirs("A")
   proc = subprocess.run([sys.executable, os.path.join(ROOT, "main.py"), "--model", d, "--prompt-ids", "5,17,3,200",
