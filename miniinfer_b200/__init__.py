@@ -9,6 +9,7 @@ __version__ = "0.1.0"
 
 _LAZY = {
   "LLMEngine": ("miniinfer_b200.engine.llm_engine", "LLMEngine"),
+  "RequestOutput": ("miniinfer_b200.engine.llm_engine", "RequestOutput"),
   "SamplingParams": ("miniinfer_b200.sampling.params", "SamplingParams"),
   "EngineConfig": ("miniinfer_b200.config.engine_config", "EngineConfig"),
 }

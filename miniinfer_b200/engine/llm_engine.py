@@ -11,7 +11,10 @@ One process, one GPU; no server, no worker processes.
 from __future__ import annotations
 
 import os
+import queue
+import threading
 import time
+from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 
 import numpy as np
@@ -48,6 +51,20 @@ def size_cache_pages(layer_specs, page_size: int, dtype: torch.dtype, device: to
   return min(pages, cap)
 
 
+@dataclass
+class RequestOutput:
+  """What ``stream_generate`` yields for a request and a generated token (the reference's fields,
+  miniinfer/engine/llm_engine.py:50-59)."""
+
+  request_id: Hashable
+  delta_text: str
+  full_text: str
+  token_id: int
+  output_token_ids: List[int]
+  finished: bool
+  finish_reason: Optional[str] = None
+
+
 class LLMEngine:
   def __init__(self, model: str, **kwargs: Any):
     self.config = EngineConfig.from_kwargs(model, **kwargs)
@@ -77,11 +94,14 @@ class LLMEngine:
     self.tokenizer = self._load_tokenizer(cfg.model_path)
     self._requests: Dict[Hashable, Request] = {}
     self._next_id = 0
+    self._submit_lock = threading.Lock()
     self._tokens_host: Optional[torch.Tensor] = None
     self._tokens_dev: Optional[torch.Tensor] = None
     self._host_tokens: List[Optional[torch.Tensor]] = [None, None]   # two pinned arrays: a step's tokens may still be on their way when the next is launched
     self._flip = 0
     self._inflight: Optional["LLMEngine._InFlight"] = None
+    self._new_tokens: List[tuple] = []          # (request, token) of the step whose tokens were read last
+    self._submitted: "queue.Queue" = queue.Queue()   # requests handed in from other threads (submit_request)
     self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "h2d_bytes": 0, "d2h_bytes": 0, "launches": 0,
                   "host_schedule_s": 0.0, "host_launch_s": 0.0, "host_wait_s": 0.0, "host_update_s": 0.0}
 
@@ -127,21 +147,49 @@ class LLMEngine:
   def add_request(self, prompt: Union[str, Sequence[int]], sampling_params: Optional[SamplingParams] = None,
                   request_id: Optional[Hashable] = None) -> Hashable:
     params = sampling_params or SamplingParams()
-    rid = request_id if request_id is not None else self._next_id
-    if rid in self._requests:
-      raise ValueError(f"request id {rid!r} is in use")
-    self._next_id += 1
+    with self._submit_lock:
+      rid = request_id if request_id is not None else self._next_id
+      if rid in self._requests:
+        raise ValueError(f"request id {rid!r} is in use")
+      self._next_id += 1
     req = Request(req_id=rid, prompt_ids=self._encode(prompt), params=params)
     self.scheduler.add(req)
     req.seed = params.seed if params.seed is not None else derive_seed(self.config.seed, req.number)
     self._requests[rid] = req
     return rid
 
+  def add_requests(self, prompts: Sequence[Union[str, Sequence[int]]],
+                   sampling_params: Sequence[SamplingParams]) -> List[Hashable]:
+    """Several requests at once (miniinfer/engine/llm_engine.py:325); returns their ids."""
+    if len(prompts) != len(sampling_params):
+      raise ValueError(f"prompts and sampling_params length mismatch: {len(prompts)} vs {len(sampling_params)}")
+    return [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+
+  def submit_request(self, prompt: Union[str, Sequence[int]], sampling_params: Optional[SamplingParams] = None) -> Hashable:
+    """Hands a request in from any thread (miniinfer/engine/llm_engine.py:362); it joins the
+    waiting queue at the next ``step``.  Returns its id."""
+    with self._submit_lock:
+      rid = self._next_id
+      self._next_id += 1
+    self._submitted.put((rid, self._encode(prompt), sampling_params or SamplingParams()))
+    return rid
+
+  def _take_submitted(self) -> None:
+    while True:
+      try:
+        rid, ids, params = self._submitted.get_nowait()
+      except queue.Empty:
+        return
+      req = Request(req_id=rid, prompt_ids=ids, params=params)
+      self.scheduler.add(req)
+      req.seed = params.seed if params.seed is not None else derive_seed(self.config.seed, req.number)
+      self._requests[rid] = req
+
   def is_finished(self) -> bool:
     return not self.has_unfinished()
 
   def has_unfinished(self) -> bool:
-    return self._inflight is not None or self.scheduler.has_unfinished()
+    return self._inflight is not None or self.scheduler.has_unfinished() or not self._submitted.empty()
 
   # ------------------------------------------------------------------ one step
 
@@ -203,6 +251,7 @@ class LLMEngine:
     live = [it for it in fl.out.items if it.request.status != "finished"]
     if len(live) != len(fl.out.items):
       fl.out.items = live
+    self._new_tokens = [(it.request, sampled[it.request.req_id]) for it in fl.out.items if it.samples]
     done = self.scheduler.update(fl.out, sampled)
     if self.stats["steps"] % 256 == 0:
       self.runner.check_status()
@@ -243,6 +292,9 @@ class LLMEngine:
     request that ends with a stop token is then run for one token more, which is dropped."""
     t0 = time.perf_counter()
     outs: List[Dict[str, Any]] = []
+    self._new_tokens = []
+    if not self._submitted.empty():
+      self._take_submitted()
     fl = self._inflight
     if fl is not None:
       nxt = self._continuation(fl)
@@ -277,6 +329,32 @@ class LLMEngine:
     self.stats["host_launch_s"] += t2 - t1
     self.stats["host_wait_s"] += (t0b - t0) + (t4 - t3)
     return outs
+
+  def stream_generate(self, prompts: Union[str, Sequence[int], Sequence[Union[str, Sequence[int]]]],
+                      sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None):
+    """Generator over the tokens as they come (miniinfer/engine/llm_engine.py:1341): one
+    ``RequestOutput`` per request and generated token.  Requests added meanwhile are served too."""
+    if isinstance(prompts, str) or (len(prompts) > 0 and isinstance(prompts[0], int)):
+      prompts = [prompts]  # type: ignore[list-item]
+    if sampling_params is None or isinstance(sampling_params, SamplingParams):
+      plist = [sampling_params or SamplingParams()] * len(prompts)
+    else:
+      plist = list(sampling_params)
+    self.add_requests(prompts, plist)
+    texts: Dict[Hashable, str] = {}
+    while self.has_unfinished():
+      self.step()
+      for req, tok in self._new_tokens:
+        full = self._decode(req.output_ids) or ""
+        before = texts.get(req.req_id, "")
+        texts[req.req_id] = full
+        finished = req.status == "finished"
+        yield RequestOutput(request_id=req.req_id, delta_text=full[len(before):] if full.startswith(before) else full,
+                            full_text=full, token_id=tok, output_token_ids=list(req.output_ids), finished=finished,
+                            finish_reason=req.finish_reason if finished else None)
+        if finished:
+          texts.pop(req.req_id, None)
+          self._requests.pop(req.req_id, None)
 
   def _output_of(self, req: Request) -> Dict[str, Any]:
     return {"text": self._decode(req.output_ids), "token_ids": list(req.output_ids), "request_id": req.req_id,

@@ -163,3 +163,38 @@ def test_decode_description_written_in_place_equals_the_general_one(cpu_kernels,
   for rid in lengths:
     r.cache.release_request(rid)
   r.cache.check_invariants()
+
+
+def test_stream_generate_add_requests_and_submit_request(cpu_kernels, model_dirs):
+  """The other entry points of the reference's engine: tokens streamed one by one (with requests
+  that are handed in meanwhile from another thread), several requests added at once."""
+  import threading
+  from miniinfer_b200 import LLMEngine, RequestOutput, SamplingParams
+  d = model_dirs("A", "float32")
+  w, c = plain.read_weights(d), plain.read_config(d)
+  prompts = [[5, 17, 3, 200, 9], list(range(40, 60)), [7]]
+  eng = LLMEngine(d, dtype="float32", device="cpu", page_size=16, num_pages=24, max_num_seqs=4, max_model_len=128)
+  sp = SamplingParams(temperature=0.0, max_tokens=6)
+  late = {}
+  seen = {}
+  for out in eng.stream_generate(prompts[:2], sp):
+    assert isinstance(out, RequestOutput)
+    seen.setdefault(out.request_id, []).append(out.token_id)
+    assert out.output_token_ids == seen[out.request_id]
+    assert out.finished == (len(seen[out.request_id]) == 6) and (out.finish_reason == "max_tokens") == out.finished
+    if not late:                       # from another thread, while the generator runs
+      t = threading.Thread(target=lambda: late.setdefault("id", eng.submit_request(prompts[2], sp)))
+      t.start(); t.join()
+  assert sorted(seen) == [0, 1, late["id"]]
+  for rid, p in zip((0, 1, late["id"]), prompts):
+    assert seen[rid] == plain.generate(w, c, p, 6)
+  ids = eng.add_requests(prompts, [sp] * 3)
+  assert len(set(ids)) == 3 and not eng.is_finished()
+  done = {}
+  while not eng.is_finished():
+    for o in eng.step():
+      done[o["request_id"]] = o["token_ids"]
+  assert [done[i] for i in ids] == [plain.generate(w, c, p, 6) for p in prompts]
+  with pytest.raises(ValueError, match="mismatch"):
+    eng.add_requests(prompts, [sp])
+  assert eng.cache.free_pages() == [24]
