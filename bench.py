@@ -61,7 +61,7 @@ class ClockSampler:
 
   def start(self):
     try:
-      self.proc = subprocess.Popen(["nvidia-smi", "--id=0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+      self.proc = subprocess.Popen(["nvidia-smi", "--id=0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
                                    stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     except OSError:
       return
