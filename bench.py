@@ -114,7 +114,7 @@ def prefill_flops(cfg: dict, layers: int, T: int) -> float:
 
 def build_engine(model_dir: str, batch: int):
   from miniinfer_b200 import LLMEngine
-  pages = batch * (-(-(CONTEXT + GENERATED + 128) // PAGE)) + 8
+  pages = batch * (-(-(CONTEXT + GENERATED + 128) // PAGE)) + 8          # GENERATED covers warm-up + steps (see main)
   pages = max(pages, -(-PREFILL_TOKENS // PAGE) + 8)
   return LLMEngine(model_dir, dtype="bfloat16", device="cuda:0", load_format="random", page_size=PAGE, num_pages=pages,
                    max_num_seqs=max(batch, 1), max_model_len=MAX_MODEL_LEN, max_num_batched_tokens=PREFILL_TOKENS, seed=0)
@@ -316,6 +316,11 @@ def main() -> int:
   pk = peaks()
   cfg = dict(MODEL, num_hidden_layers=args.layers)
   warmup = max(args.warmup, 3)
+  # room for the tokens that the timed steps generate, whatever --steps says
+  global GENERATED, MAX_MODEL_LEN
+  GENERATED = max(GENERATED, warmup + args.steps + args.batch + 64)
+  MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
+  cfg["max_position_embeddings"] = max(cfg.get("max_position_embeddings", 0), MAX_MODEL_LEN)
   with tempfile.TemporaryDirectory() as d:
     with open(os.path.join(d, "config.json"), "w") as f:
       json.dump(cfg, f)
