@@ -126,15 +126,16 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
     }
   };
 
-  // The first group of weights is on its way before this kernel waits for its predecessor: the
-  // weights are written by no kernel, the activations are.
+  // The first two groups of weights are on their way before this kernel waits for its predecessor:
+  // the weights are written by no kernel, the activations are.
   if (kb_begin < kb_end) load_w(kb_begin, wv);
+  if (kb_begin + U < kb_end) load_w(kb_begin + U, wn);
   mi::grid_dependency_sync();
   if (kb_begin < kb_end) load_x(kb_begin, xa, xb);
   for (int kb = kb_begin; kb < kb_end; kb += U) {
     const bool more = kb + U < kb_end;
     if (more) {
-      load_w(kb + U, wn);
+      if (kb != kb_begin) load_w(kb + U, wn);
       load_x(kb + U, xan, xbn);
     }
 #pragma unroll
