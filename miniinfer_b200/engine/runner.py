@@ -12,7 +12,11 @@ miniinfer/scheduler/scheduler_batch.py:320-429) and returns the last row of ever
 Steps that hold only decode tokens can be replayed from a CUDA graph (``step_and_sample`` with
 ``use_graphs``): the same forward pass, captured once per batch-size bucket with the batch padded
 by entries that read and write the dummy page (the reference captures decode at power-of-two batch
-sizes as well, miniinfer/engine/cuda_graph_runner.py:121-131,289-381).
+sizes as well, miniinfer/engine/cuda_graph_runner.py:121-131,289-381).  Such a step may take its
+token ids from a device buffer - the tokens the step before has sampled - so that the host need not
+have read them yet.  Any other step (a prompt portion, a mixed step) is recorded as a graph of its
+own once its shape has been seen twice, and replayed when that shape comes again
+(``_shape_step``); kernel by kernel a step is bound by the host's time per launch.
 """
 
 from __future__ import annotations
