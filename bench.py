@@ -178,7 +178,9 @@ def time_e2e(engine, batch: int, steps: int, warmup: int) -> dict:
   from miniinfer_b200 import SamplingParams
   g = torch.Generator().manual_seed(100 + batch)
   V = engine.model_config.vocab_size
-  sp = SamplingParams(temperature=0.6, max_tokens=max(warmup, 3) + steps + batch + 16, ignore_eos=True)
+  # the first requests decode while the later ones' prompts still run, portion by portion
+  early = batch * -(-CONTEXT // PREFILL_TOKENS)
+  sp = SamplingParams(temperature=0.6, max_tokens=max(warmup, 3) + steps + early + 16, ignore_eos=True)
   for b in range(batch):
     engine.add_request(torch.randint(0, V, (CONTEXT,), generator=g).tolist(), sp)
   while any(r.total_len - r.num_computed != 1 for r in engine.scheduler.running) or engine.scheduler.waiting:
@@ -295,6 +297,7 @@ def reference_arm() -> int:
 
 
 def main() -> int:
+  global CONTEXT
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=128)
@@ -302,6 +305,7 @@ def main() -> int:
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+  ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
   ap.add_argument("--skip-points", action="store_true")
   ap.add_argument("--kernel-table", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                   help="print the device time of each kernel of a decode step (default) or a prefill step and exit")
@@ -318,7 +322,8 @@ def main() -> int:
   warmup = max(args.warmup, 3)
   # room for the tokens that the timed steps generate, whatever --steps says
   global GENERATED, MAX_MODEL_LEN
-  GENERATED = max(GENERATED, warmup + args.steps + args.batch + 64)
+  CONTEXT = args.context
+  GENERATED = max(GENERATED, warmup + args.steps + args.batch * -(-CONTEXT // PREFILL_TOKENS) + 64)
   MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
   cfg["max_position_embeddings"] = max(cfg.get("max_position_embeddings", 0), MAX_MODEL_LEN)
   with tempfile.TemporaryDirectory() as d:
