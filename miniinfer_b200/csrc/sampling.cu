@@ -210,6 +210,9 @@ sample_pick_kernel(int* __restrict__ out, const float* __restrict__ logits, cons
     for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) {
       const float z = x[i] / temp;
       if (ordered(z) < thr || !(z > -INFINITY)) continue;
+      // u <= 1 - 2^-25, so the noise -log(-log(u)) stays below 17.4: a score that far under this
+      // thread's best cannot win, and its draw need not be worked out
+      if (z + 17.4f < b.v) continue;
       const float u = uniform_for(key, i);
       b = better(b, Best{z - logf(-logf(u)), i});
     }
