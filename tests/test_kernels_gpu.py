@@ -278,10 +278,11 @@ def test_sampler_greedy_and_ties(ops):
   assert got == logits.argmax(-1).tolist() and got[1] == 40 and got[2] == 999
 
 
+@pytest.mark.parametrize("scale", [2.0, 12.0])       # 12: most scores lie too far under the best to win, and are passed over
 @pytest.mark.parametrize("V", [1000, 151936])
-def test_sampler_draws_match_the_statement(ops, V):
+def test_sampler_draws_match_the_statement(ops, V, scale):
   R = 6
-  logits = rnd(R, V, seed=5, scale=2.0)
+  logits = rnd(R, V, seed=5, scale=scale)
   temp = [0.8, 1.0, 0.5, 1.3, 0.7, 0.0]
   k = [0, 20, 0, 50, 1, 0]
   p = [1.0, 1.0, 0.9, 0.6, 1.0, 1.0]
