@@ -1,4 +1,5 @@
-// SwiGLU activation: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu in float32, one rounding.
+// SwiGLU activation: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu in float32, one rounding
+// (bfloat16: with the hardware's exponential and reciprocal; float32: exact division and expf).
 // Stands where the reference runs a Triton kernel (kernels/triton/silu_mul.py:6-42).
 #include "common.cuh"
 
@@ -13,7 +14,7 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     const int i = (int)(idx - t * I);
     const float g = mi::to_float(gu[t * 2 * I + i]);
     const float u = mi::to_float(gu[t * 2 * I + I + i]);
-    out[idx] = mi::from_float<T>(g / (1.f + expf(-g)) * u);
+    out[idx] = mi::from_float<T>(sizeof(T) == 4 ? mi::silu_mul_exact(g, u) : mi::silu_mul_fast(g, u));
   }
 }
 
@@ -32,7 +33,7 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
-      rp[k] = __floats2bfloat162_rn(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y);
+      rp[k] = __floats2bfloat162_rn(mi::silu_mul_fast(a.x, b.x), mi::silu_mul_fast(a.y, b.y));
     }
     *reinterpret_cast<uint4*>(out + idx * 8) = r;
   }

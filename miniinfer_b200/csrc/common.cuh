@@ -84,6 +84,13 @@ __device__ __forceinline__ void grid_dependency_sync() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// silu(g) * u as the bfloat16 paths compute it: in float32 with the hardware's exponential and
+// reciprocal (errors of a few units in the last place of float32, far below the rounding to bf16
+// that follows).  Every bf16 kernel that applies SwiGLU uses this one function, so the fused and the
+// two-kernel path agree bit for bit on the same products; the float32 path divides exactly.
+__device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float silu_mul_exact(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 

@@ -59,7 +59,7 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float swiglu(float gate, float up) {
   const float g = round_bf16(gate), u = round_bf16(up);
-  return g / (1.f + expf(-g)) * u;
+  return mi::silu_mul_fast(g, u);
 }
 
 template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false, int W = WARPS>

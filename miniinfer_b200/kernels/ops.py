@@ -253,8 +253,9 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
 
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
-  bfloat16 with M <= 16: one kernel, the activation in the product's epilogue.  Otherwise the product
-  into a buffer of ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
+  bfloat16 with M <= 16 or M > 64: one kernel, the activation in the product's epilogue (few rows: the
+  weight-streaming kernel; many: the tcgen05 kernel).  Otherwise the product into a buffer of
+  ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
   M, K = x.shape
   I = out.shape[1]
   if w.shape != (2 * I, K) or out.shape[0] != M or out.dtype != x.dtype:
@@ -265,9 +266,37 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     lib = common_lib()
     _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
     return
+  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > SKINNY_MAX_M and K >= 64 and K % 8 == 0 and I % 8 == 0
+      and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):
+    # many rows: the product on tcgen05 with the activation in its epilogue; [M, 2I] is never written
+    lib = common_lib()
+    status = workspace.zeros("gemm_tc_status", 1, torch.int32)
+    _check(lib, lib.mi_gemm_tc_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _ptr(status, torch.int32), _tc_pairs(), _stream()))
+    return
   gu = workspace.buffer("gate_up", (M, 2 * I), x.dtype)
   linear(gu, x, w)
   silu_mul(out, gu)
+
+
+def _tc_pairs() -> int:
+  """Whether the tcgen05 product lets two blocks share a tile (MINIINFER_B200_GEMM_TC=1: blocks work alone)."""
+  return 0 if os.environ.get("MINIINFER_B200_GEMM_TC", "2") == "1" else 1
+
+
+def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace) -> None:
+  """out = x @ w^T in bfloat16 through the tcgen05 kernel that `linear_swiglu` uses for many rows,
+  without the activation (the engine's plain products with many rows go to the library)."""
+  M, K = x.shape
+  N = w.shape[0]
+  if w.shape[1] != K or out.shape != (M, N) or not (x.dtype == w.dtype == out.dtype == torch.bfloat16):
+    raise KernelError(f"linear_tc: shapes or dtypes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if not (x.is_contiguous() and w.is_contiguous() and out.is_contiguous()):
+    raise KernelError("linear_tc: operands must be contiguous")
+  if M == 0:
+    return
+  lib = common_lib()
+  status = workspace.zeros("gemm_tc_status", 1, torch.int32)
+  _check(lib, lib.mi_gemm_tc_bf16(_ptr(out), _ptr(x), _ptr(w), M, N, K, N, _ptr(status, torch.int32), _tc_pairs(), _stream()))
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
@@ -465,7 +494,7 @@ def _qkv_tensor_map(lib, qkv: torch.Tensor):
 def device_status(ws) -> int:
   """The status words that kernels with bounded waits set when a wait ran out (0: all well)."""
   code = 0
-  for name in ("attention_decode_counters", "attention_prefill_status"):
+  for name in ("attention_decode_counters", "attention_prefill_status", "gemm_tc_status"):
     buf = ws._bufs.get((name, torch.int32))
     if buf is not None:
       code |= int(buf[0])

@@ -223,8 +223,16 @@ def test_silu_mul(ops, dtype, T, I):
 
 
 class _Scratch:
+  def __init__(self):
+    self.made = {}
+
   def buffer(self, name, shape, dtype):
     return torch.empty(shape, dtype=dtype, device=DEV)
+
+  def zeros(self, name, n, dtype):
+    if name not in self.made:
+      self.made[name] = torch.zeros(n, dtype=dtype, device=DEV)
+    return self.made[name]
 
 
 @pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (7, 8), (333, 2048)])
@@ -234,7 +242,7 @@ def test_linear_swiglu(ops, I, K):
   w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.08)
   xs = rnd(100, K, dtype=torch.bfloat16, seed=1)
   full = {}
-  for M in (64, 16, 1, 3, 8, 9, 17, 33, 100):       # 100 rows: the unfused path
+  for M in (64, 16, 1, 3, 8, 9, 17, 33, 100):       # 100 rows: the tcgen05 kernel, or the unfused path
     x = xs[:M].contiguous()
     gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
     want = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
@@ -260,6 +268,51 @@ def test_linear_swiglu(ops, I, K):
   ops.linear_swiglu(out32, x32, w32, _Scratch())
   g = x32 @ w32.t()
   assert torch.allclose(out32, torch.nn.functional.silu(g[:, :I]) * g[:, I:], atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("mode", ["2", "1"])          # blocks in pairs, blocks alone
+@pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (200, 72), (128, 4096)])
+def test_linear_swiglu_many_rows(ops, I, K, mode, monkeypatch):
+  """The tcgen05 product with the activation in its epilogue: tiles of 128 rows, edges in every
+  direction, against product + activation; a row's value must not depend on the other rows."""
+  monkeypatch.setenv("MINIINFER_B200_GEMM_TC", mode)
+  w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.08)
+  xs = rnd(700, K, dtype=torch.bfloat16, seed=1)
+  scratch = _Scratch()
+  first = None
+  for M in (700, 65, 128, 129, 384):
+    x = xs[:M].contiguous()
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    want = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ref.linear(gu, x, w)
+    ref.silu_mul(want, gu)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(out, x, w, scratch)
+    assert int(scratch.made["gemm_tc_status"][0]) == 0
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
+    if first is None:
+      first = out
+    else:
+      assert torch.equal(out, first[:M]), "a row's value must not depend on the other rows"
+
+
+@pytest.mark.parametrize("mode", ["2", "1"])
+@pytest.mark.parametrize("N,K", [(256, 64), (4096, 1024), (1000, 136), (8, 72), (384, 2048)])
+def test_linear_tc(ops, N, K, mode, monkeypatch):
+  monkeypatch.setenv("MINIINFER_B200_GEMM_TC", mode)
+  w = rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.08)
+  xs = rnd(300, K, dtype=torch.bfloat16, seed=1)
+  scratch = _Scratch()
+  for M in (300, 1, 128, 130):
+    x = xs[:M].contiguous()
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ref.linear(want, x, w)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_tc(out, x, w, scratch)
+    assert int(scratch.made["gemm_tc_status"][0]) == 0
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
 
 
 def _sample(ops, logits, temp, k, p, seed, counter):
