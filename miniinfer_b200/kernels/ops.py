@@ -23,6 +23,8 @@ from . import build
 F32, BF16 = 0, 1
 SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
 SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
+GEMM_TC_MIN_M = 1280  # from here the tcgen05 gate-up product with SwiGLU beats cuBLAS + activation (measured on B200
+                      # at K = 1024, I = 3072 and at K = 4096, I = 12288; below, its tiles of 256 rows leave SMs idle)
 _MM_F32_OUT: Optional[bool] = None   # whether torch.mm writes float32 from bf16 operands into a given tensor
 
 
@@ -251,9 +253,10 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
     _ptr(kv_layer), T, num_heads, num_kv_heads, head_dim, page_size, ctypes.c_float(eps), _stream()))
 
 
-def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False) -> None:
+def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
+                  force_tc: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
-  bfloat16 with M <= 16 or M > 64: one kernel, the activation in the product's epilogue (few rows: the
+  bfloat16 with M <= 16 or M >= 1280: one kernel, the activation in the product's epilogue (few rows: the
   weight-streaming kernel; many: the tcgen05 kernel).  Otherwise the product into a buffer of
   ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
   M, K = x.shape
@@ -266,7 +269,7 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     lib = common_lib()
     _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
     return
-  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > SKINNY_MAX_M and K >= 64 and K % 8 == 0 and I % 8 == 0
+  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (M >= GEMM_TC_MIN_M or force_tc) and K >= 64 and K % 8 == 0 and I % 8 == 0
       and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):
     # many rows: the product on tcgen05 with the activation in its epilogue; [M, 2I] is never written
     lib = common_lib()

@@ -100,7 +100,7 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
   out.copy_(res.reshape(T, nh * hd).to(out.dtype))
 
 
-def linear_swiglu(out, x, w, workspace, force_skinny=False):
+def linear_swiglu(out, x, w, workspace, force_skinny=False, force_tc=False):
   gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype)
   linear(gu, x, w)
   silu_mul(out, gu)
