@@ -197,108 +197,139 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
   }
 }
 
-// Head size 128 with many tokens, in 16-byte steps: a block takes one token, a warp four heads at a
-// time, eight lanes per head; a lane holds elements 8l .. 8l + 7 of the head and their partners
-// 64 further on, so the rotation needs no exchange and the sum of squares three shuffles.
-__global__ void __launch_bounds__(256)
+// Head size 128 with many tokens, in 16-byte steps: a block takes a token at a time, a warp four
+// heads at a time, eight lanes per head; a lane holds elements 8l .. 8l + 7 of the head and their
+// partners 64 further on, so the rotation needs no exchange and the sum of squares three shuffles.
+// The norm weights and the token's row of the rotation table lie in shared memory (every head of a
+// token uses the same); while a token is worked on, the first heads of the block's next token and
+// its table row are already on their way.
+__global__ void __launch_bounds__(256, 4)
 qk_norm_rope_store_wide128_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
                                   const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                   const int* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ kv_layer, int nh, int nkv,
                                   int page_size, float eps, int T) {
   constexpr int HD = 128, HALF = 64;
+  __shared__ __align__(16) float w_s[2][HD];        // q and k norm weights (ones where there is none)
+  __shared__ __align__(16) float cs_s[2][HD];       // cos | sin of the current and of the next token
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int hq = lane >> 3, l8 = lane & 7;
   const int heads = nh + 2 * nkv;
-  bool waited = false;
-  for (int tkn = blockIdx.x; tkn < T; tkn += gridDim.x) {     // a few tokens per block
-  // what no kernel writes is fetched before the wait for the preceding kernel: the table's row
-  float c[8], sn[8];
-  {
-    const float* cs = cos_sin ? cos_sin + (size_t)positions[tkn] * HD : nullptr;
-    const float4 c0 = cs ? *reinterpret_cast<const float4*>(cs + 8 * l8) : make_float4(1.f, 1.f, 1.f, 1.f);
-    const float4 c1 = cs ? *reinterpret_cast<const float4*>(cs + 8 * l8 + 4) : make_float4(1.f, 1.f, 1.f, 1.f);
-    const float4 s0 = cs ? *reinterpret_cast<const float4*>(cs + HALF + 8 * l8) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 s1 = cs ? *reinterpret_cast<const float4*>(cs + HALF + 8 * l8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
-    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+  // what no kernel writes is fetched before the wait for the preceding kernel: weights, the first token's table row
+  if (threadIdx.x < 64) {
+    const float* w = threadIdx.x < 32 ? q_w : k_w;
+    const int i = threadIdx.x & 31;
+    reinterpret_cast<float4*>(w_s[threadIdx.x >> 5])[i] = w ? reinterpret_cast<const float4*>(w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+  } else if (threadIdx.x < 96 && blockIdx.x < T) {
+    const int i = threadIdx.x - 64;
+    reinterpret_cast<float4*>(cs_s[0])[i] = cos_sin ? reinterpret_cast<const float4*>(cos_sin + (size_t)positions[blockIdx.x] * HD)[i]
+                                                    : (i < 16 ? make_float4(1.f, 1.f, 1.f, 1.f) : make_float4(0.f, 0.f, 0.f, 0.f));
   }
-  const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
-  if (!waited) {
-    mi::grid_dependency_sync();
-    waited = true;
-  }
-  __nv_bfloat16* row = qkv + (size_t)tkn * heads * HD;
-  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  mi::grid_dependency_sync();
+  __syncthreads();
 
-  for (int hb = 0; hb < heads; hb += 32) {
-    const int h = hb + warp * 4 + hq;
-    const bool live = h < heads;
-    const bool is_q = h < nh;
-    const bool is_k = !is_q && h < nh + nkv;
-    __nv_bfloat16* x = row + (size_t)(live ? h : 0) * HD;
-    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
-    if (live) {
-      ra = *reinterpret_cast<const uint4*>(x + 8 * l8);
-      rb = *reinterpret_cast<const uint4*>(x + HALF + 8 * l8);
-    }
-    const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
-    __nv_bfloat16* dst = (live && !is_q && slot >= 0)
-        ? kv_layer + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD : nullptr;
-    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
-    float a[8], b[8];
-    {
-      const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&ra);
-      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&rb);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
-        a[2 * i] = fa.x; a[2 * i + 1] = fa.y; b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
-      }
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-    // every lane takes part in the shuffles; the groups of eight lanes are heads
-    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-    if (live && (is_q || is_k)) {
-      if (w) {
-        const float rstd = rsqrtf(ss / (float)HD + eps);
-        const float4 wa0 = *reinterpret_cast<const float4*>(w + 8 * l8), wa1 = *reinterpret_cast<const float4*>(w + 8 * l8 + 4);
-        const float4 wb0 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8), wb1 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8 + 4);
-        const float wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
-        const float wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          a[i] *= rstd * wa[i];
-          b[i] *= rstd * wb[i];
+  // the first four heads of this warp for the first token
+  const int h0 = warp * 4 + hq;
+  uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+  if (blockIdx.x < T && h0 < heads) {
+    const __nv_bfloat16* x = qkv + ((size_t)blockIdx.x * heads + h0) * HD;
+    ra = *reinterpret_cast<const uint4*>(x + 8 * l8);
+    rb = *reinterpret_cast<const uint4*>(x + HALF + 8 * l8);
+  }
+  int buf = 0;
+  for (int tkn = blockIdx.x; tkn < T; tkn += gridDim.x, buf ^= 1) {
+    const int next = tkn + gridDim.x;
+    // the next token's table row: asked for now, put into shared memory at the end of this round
+    float4 cs_next = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (warp == 7 && next < T)
+      cs_next = cos_sin ? reinterpret_cast<const float4*>(cos_sin + (size_t)positions[next] * HD)[lane]
+                        : (lane < 16 ? make_float4(1.f, 1.f, 1.f, 1.f) : make_float4(0.f, 0.f, 0.f, 0.f));
+    const int slot = (slot_mapping && kv_layer) ? slot_mapping[tkn] : -1;
+    __nv_bfloat16* row = qkv + (size_t)tkn * heads * HD;
+    const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+
+    for (int hb = 0; hb < heads; hb += 32) {
+      const int h = hb + h0;
+      const bool live = h < heads;
+      const bool is_q = h < nh;
+      const bool is_k = !is_q && h < nh + nkv;
+      __nv_bfloat16* x = row + (size_t)(live ? h : 0) * HD;
+      uint4 xa = ra, xb = rb;
+      if (hb > 0) {
+        xa = xb = make_uint4(0u, 0u, 0u, 0u);
+        if (live) {
+          xa = *reinterpret_cast<const uint4*>(x + 8 * l8);
+          xb = *reinterpret_cast<const uint4*>(x + HALF + 8 * l8);
         }
       }
-      if (cos_sin) {
+      float a[8], b[8];
+      {
+        const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&xa);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&xb);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float na = a[i] * c[i] - b[i] * sn[i], nb = b[i] * c[i] + a[i] * sn[i];
-          a[i] = na; b[i] = nb;
+        for (int i = 0; i < 4; ++i) {
+          const float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+          a[2 * i] = fa.x; a[2 * i + 1] = fa.y; b[2 * i] = fb.x; b[2 * i + 1] = fb.y;
         }
       }
-      __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
-      __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        pa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
-        pb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+      if (hb == 0 && next < T && h0 < heads) {       // the same heads of the next token, in flight during what follows
+        const __nv_bfloat16* xn = qkv + ((size_t)next * heads + h0) * HD;
+        ra = *reinterpret_cast<const uint4*>(xn + 8 * l8);
+        rb = *reinterpret_cast<const uint4*>(xn + HALF + 8 * l8);
       }
-      *reinterpret_cast<uint4*>(x + 8 * l8) = ra;
-      *reinterpret_cast<uint4*>(x + HALF + 8 * l8) = rb;
+      const int kvh = is_q ? 0 : (is_k ? h - nh : h - nh - nkv);
+      __nv_bfloat16* dst = (live && !is_q && slot >= 0)
+          ? kv_layer + (((page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * HD : nullptr;
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+      // every lane takes part in the shuffles; the groups of eight lanes are heads
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      if (live && (is_q || is_k)) {
+        if (is_q ? q_w != nullptr : k_w != nullptr) {
+          const float rstd = rsqrtf(ss / (float)HD + eps);
+          const float* w = w_s[is_q ? 0 : 1];
+          const float4 wa0 = *reinterpret_cast<const float4*>(w + 8 * l8), wa1 = *reinterpret_cast<const float4*>(w + 8 * l8 + 4);
+          const float4 wb0 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8), wb1 = *reinterpret_cast<const float4*>(w + HALF + 8 * l8 + 4);
+          const float wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+          const float wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a[i] *= rstd * wa[i];
+            b[i] *= rstd * wb[i];
+          }
+        }
+        if (cos_sin) {
+          const float* cs = cs_s[buf];
+          const float4 c0 = *reinterpret_cast<const float4*>(cs + 8 * l8), c1 = *reinterpret_cast<const float4*>(cs + 8 * l8 + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(cs + HALF + 8 * l8), s1 = *reinterpret_cast<const float4*>(cs + HALF + 8 * l8 + 4);
+          const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float na = a[i] * c[i] - b[i] * sn[i], nb = b[i] * c[i] + a[i] * sn[i];
+            a[i] = na; b[i] = nb;
+          }
+        }
+        __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&xa);
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&xb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pa[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+          pb[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+        }
+        *reinterpret_cast<uint4*>(x + 8 * l8) = xa;
+        *reinterpret_cast<uint4*>(x + HALF + 8 * l8) = xb;
+      }
+      if (dst) {                                         // keys as normed and rotated, values as they are
+        *reinterpret_cast<uint4*>(dst + 8 * l8) = xa;
+        *reinterpret_cast<uint4*>(dst + HALF + 8 * l8) = xb;
+      }
     }
-    if (dst) {                                         // keys as normed and rotated, values as they are
-      *reinterpret_cast<uint4*>(dst + 8 * l8) = ra;
-      *reinterpret_cast<uint4*>(dst + HALF + 8 * l8) = rb;
-    }
+    if (warp == 7 && next < T) reinterpret_cast<float4*>(cs_s[buf ^ 1])[lane] = cs_next;
+    __syncthreads();       // the next row is in place, and nobody reads this round's row any more
   }
-  }
-  if (!waited) mi::grid_dependency_sync();
 }
 
 }  // namespace
@@ -320,7 +351,7 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
     const bool aligned16 = ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)kv_layer % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0 &&
                            ((uintptr_t)q_w % 16) == 0 && ((uintptr_t)k_w % 16) == 0;
     if (hd == 128 && T > 64 && aligned16)
-      mi::launch(qk_norm_rope_store_wide128_kernel, dim3(T < 148 * 8 ? T : 148 * 8), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w,
+      mi::launch(qk_norm_rope_store_wide128_kernel, dim3(T < 148 * 4 ? T : 148 * 4), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w,
                  cos_sin, positions, slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps, T);
     else if (hd == 128)
       mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(fast_grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,

@@ -118,7 +118,8 @@ def test_linear_bf16_many_rows_and_float32_logits(ops):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nh,nkv,hd,P,T", [(6, 2, 48, 8, 23), (4, 4, 16, 16, 23), (16, 8, 128, 64, 23), (3, 1, 256, 32, 23),
-                                             (16, 8, 128, 64, 200), (5, 3, 128, 16, 77), (3, 1, 256, 32, 100)])   # many tokens: the wide kernels
+                                             (16, 8, 128, 64, 200), (5, 3, 128, 16, 77), (3, 1, 256, 32, 100),    # many tokens: the wide kernels
+                                             (5, 3, 128, 16, 1300), (40, 4, 128, 64, 700)])   # several tokens per block; more than 32 heads
 def test_qk_norm_rope_store(ops, dtype, nh, nkv, hd, P, T):
   pages, max_pos = max(9, -(-T // P) + 2), 300
   g = torch.Generator().manual_seed(4)
