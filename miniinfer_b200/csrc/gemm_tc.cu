@@ -30,7 +30,7 @@
 // device where pairs cannot be placed.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag that ends all other
-// waits of the block, sets the status word to 3, and the block runs to its end, tensor memory freed.
+// waits of the block, sets the status word to 4, and the block runs to its end, tensor memory freed.
 //
 // Stands where the reference calls torch.nn.functional.linear followed by its Triton silu_mul
 // kernel (miniinfer/layers/mlp.py, kernels/triton/silu_mul.py:6-42).
@@ -89,7 +89,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
     if ((i & 63) == 63 && *abort) return;
   }
   *abort = 1;
-  atomicExch(status, 3);
+  atomicExch(status, 4);
 }
 // One look at the barrier: has the phase of this parity completed?  The answer is not needed at once,
 // so the instruction's latency passes behind what the thread issues next.
@@ -494,7 +494,7 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
 
 }  // namespace
 
-// out[M, I] = silu(x w[0:I]^T) * (x w[I:2I]^T), all bf16; status: one word, set to 3 if a bounded wait ran out.
+// out[M, I] = silu(x w[0:I]^T) * (x w[I:2I]^T), all bf16; status: one word, set to 4 if a bounded wait ran out.
 // pairs: non-zero to let two blocks share a tile (the default of the engine), zero for blocks that work alone.
 MI_API int mi_gemm_tc_swiglu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo, int* status,
                                   int pairs, cudaStream_t stream) {
