@@ -23,6 +23,8 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+STAGING_SLOTS = 8     # pinned snapshots of a block table that uploads in flight may still read
+
 from .specs import CacheSpec, FixedStateSpec, PagedKVSpec
 
 
@@ -90,6 +92,16 @@ class PagedGroup:
     self.block_table_host = np.zeros((max_num_seqs + 1, self.max_pages_per_seq), dtype=np.int32)
     self.block_table = torch.zeros((max_num_seqs + 1, self.max_pages_per_seq), dtype=torch.int32, device=device)
     self._dirty: set = set()
+    # Uploads go through a ring of pinned copies of the table: the copy is queued on the stream and
+    # reads host memory when the device gets to it, by when the host may have changed the table
+    # again for a later step - so each upload reads a snapshot of its own, taken when it is queued.
+    self._staging: List[torch.Tensor] = []
+    self._staging_events: List[Optional[torch.cuda.Event]] = []
+    self._staging_next = 0
+    if torch.device(device).type == "cuda":
+      for _ in range(STAGING_SLOTS):
+        self._staging.append(torch.zeros((max_num_seqs + 1, self.max_pages_per_seq), dtype=torch.int32).pin_memory())
+        self._staging_events.append(None)
 
   def bytes_per_token(self) -> int:
     return 2 * self.num_layers * self.spec.num_kv_heads * self.spec.head_dim * self.kv.element_size()
@@ -106,12 +118,20 @@ class PagedGroup:
       return
     rows = sorted(self._dirty)
     self._dirty.clear()
-    if len(rows) == 1:
-      r = rows[0]
-      self.block_table[r].copy_(torch.from_numpy(self.block_table_host[r]), non_blocking=False)
+    lo, hi = rows[0], rows[-1] + 1
+    if not self._staging:                 # a table on the host (tests of the host path): plain copy
+      self.block_table[lo:hi].copy_(torch.from_numpy(self.block_table_host[lo:hi]))
+      return
+    k = self._staging_next
+    self._staging_next = (k + 1) % len(self._staging)
+    if self._staging_events[k] is not None:
+      self._staging_events[k].synchronize()      # the upload that used this snapshot last has run (long ago, as a rule)
     else:
-      lo, hi = rows[0], rows[-1] + 1
-      self.block_table[lo:hi].copy_(torch.from_numpy(self.block_table_host[lo:hi]), non_blocking=False)
+      self._staging_events[k] = torch.cuda.Event()
+    snap = self._staging[k]
+    snap.numpy()[lo:hi] = self.block_table_host[lo:hi]
+    self.block_table[lo:hi].copy_(snap[lo:hi], non_blocking=True)
+    self._staging_events[k].record()
 
 
 class StateGroup:

@@ -38,7 +38,9 @@ PREFILL_TILE = 64   # query rows of one prefill-attention tile
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 GRAPH_CONTEXT_STEP = 1024   # a captured decode step serves contexts up to a multiple of this
 STEP_GRAPHS_KEPT = 8        # graphs of steps other than decode-only ones (prompt portions, mixed steps) that are kept
-STEP_GRAPH_AFTER = 2        # a step of a shape is recorded once that shape has been seen this many times
+STEP_GRAPH_AFTER = 2        # a step of a shape is recorded once that shape has been seen this many times ...
+STEP_GRAPH_WINDOW = 64      # ... no more than this many steps apart: recording costs about twenty steps' worth of host
+                            # time, which a shape that comes back once in a few hundred steps never repays
 
 
 @dataclass
@@ -155,7 +157,8 @@ class ModelRunner:
     self.graphs_allowed = not any(getattr(p, "reads_step_on_host", False) for p in parts)
     self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
     # steps of any other kind, by shape (see _shape_key): how often seen, and the graphs of the repeated ones
-    self._shape_seen: Dict[tuple, int] = {}
+    self._shape_seen: Dict[tuple, Tuple[int, int]] = {}      # shape -> (times seen, step it was last seen at)
+    self._shape_steps = 0
     self._step_graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
     self.last_h2d_bytes = 0
     self.last_launches = 0
@@ -328,15 +331,17 @@ class ModelRunner:
     a returned graph means the step has run and is committed."""
     starts = self._check_and_reserve(items)
     self._reserved_starts = starts
+    self._shape_steps += 1
     if not (self.graphs_allowed and self.device.type == "cuda"):
       return None
     key = self._shape_key(items, starts, sample_fn is not None)
     g = self._step_graphs.get(key)
     if g is None:
-      seen = self._shape_seen.get(key, 0) + 1
+      seen, last = self._shape_seen.get(key, (0, 0))
+      seen = seen + 1 if seen and self._shape_steps - last <= STEP_GRAPH_WINDOW else 1
       if len(self._shape_seen) > 4096:
         self._shape_seen.clear()
-      self._shape_seen[key] = seen
+      self._shape_seen[key] = (seen, self._shape_steps)
       if seen < STEP_GRAPH_AFTER:
         return None
     try:
@@ -468,6 +473,7 @@ class ModelRunner:
 
   def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int, ids_on_device=None) -> torch.Tensor:
     starts = self._check_and_reserve(items)
+    self._shape_steps += 1
     B = len(items)
     try:
       # the split-KV grid is part of the capture: one graph per (bucket, context class)
