@@ -288,6 +288,36 @@ def _table_of(prof, steps: int, title: str) -> str:
   return "\n".join(lines)
 
 
+def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
+  """A continuous batch through `LLMEngine.generate`: prompts of 128 .. 2048 uniform random tokens, `outputs`
+  generated tokens each, prompts cut under a budget of 2048 tokens a step.  Run twice; the second run
+  (graphs recorded, kernels loaded) is reported."""
+  import torch
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  pages = requests * (-(-(2048 + outputs) // PAGE) + 1) + 8
+  engine = LLMEngine(model_dir, dtype="bfloat16", device="cuda:0", load_format="random", page_size=PAGE, num_pages=pages,
+                     max_num_seqs=requests, max_model_len=MAX_MODEL_LEN, max_num_batched_tokens=PREFILL_TOKENS, seed=0)
+  g = torch.Generator().manual_seed(0)
+  lens = torch.randint(128, 2049, (requests,), generator=g).tolist()
+  V = engine.model_config.vocab_size
+  prompts = [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+  sp = SamplingParams(temperature=0.6, max_tokens=outputs, ignore_eos=True)
+  res = {}
+  for _ in range(2):
+    s0 = dict(engine.stats)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    engine.generate(prompts, sp)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    steps = engine.stats["steps"] - s0["steps"]
+    res = {"workload": f"{requests} requests, prompts 128..2048, {outputs} outputs each, 2048 tokens a step",
+           "seconds": round(dt, 3), "prompt_tokens": sum(lens), "output_tokens": requests * outputs,
+           "total_tok_s": round((sum(lens) + requests * outputs) / dt, 1), "output_tok_s": round(requests * outputs / dt, 1),
+           "steps": steps, "ms_per_step": round(1000 * dt / steps, 3)}
+  return res
+
+
 def reference_arm() -> int:
   print(json.dumps({"impl": "reference", "unavailable": (
     "the reference installs (pip --no-deps into baseline/_ref) but cannot be imported as installed: its pyproject "
@@ -307,6 +337,8 @@ def main() -> int:
   ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
   ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
   ap.add_argument("--skip-points", action="store_true")
+  ap.add_argument("--mixed", action="store_true",
+                  help="run a continuous batch of 64 requests through LLMEngine.generate, print its throughput and exit")
   ap.add_argument("--kernel-table", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                   help="print the device time of each kernel of a decode step (default) or a prefill step and exit")
   args = ap.parse_args()
@@ -329,6 +361,9 @@ def main() -> int:
   with tempfile.TemporaryDirectory() as d:
     with open(os.path.join(d, "config.json"), "w") as f:
       json.dump(cfg, f)
+    if args.mixed:
+      print(json.dumps(dict(mixed_workload(d), layers=args.layers, model="Qwen3-0.6B shape")))
+      return 0
     if args.kernel_table:
       print(kernel_table(build_engine(d, args.batch), args.batch, mode=args.kernel_table))
       return 0
