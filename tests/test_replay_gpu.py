@@ -72,6 +72,28 @@ def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_more_than_a_thousand_tokens(model_dirs, dtype):
+  """Prompts of 1500 and 1400 tokens, whole and then cut into a step of 1300 tokens and the rest: in
+  bfloat16 the gate-and-up product of such a step is the tcgen05 kernel with the activation in its
+  epilogue, and the QK norm and rotation take their many-token form."""
+  d = model_dirs("E")
+  reqs = rc.make_requests(ALL["E"]["vocab_size"], (1500, 1400), seed=8)
+  ref = reference(d, "E", reqs)
+  runner = runner_for(d, dtype, 1536 + 1408, 64)
+  if dtype == "bfloat16":
+    from miniinfer_b200.kernels import ops
+    assert 1400 >= ops.GEMM_TC_MIN_M
+  got = rc.run_in_process(runner, rc.whole(reqs))
+  rc.compare(got, ref, tolerance(dtype, ref), f"E/{dtype}/whole")
+  if dtype == "bfloat16":       # the kernel leaves its status word in the workspace: it has run
+    assert ("gemm_tc_status", torch.int32) in runner.runner.ws._bufs
+  got = rc.run_in_process(runner, rc.portions(reqs, sizes=(1300, 64, 2, 150)))
+  rc.compare(got, ref, tolerance(dtype, ref), f"E/{dtype}/portions")
+  runner.runner.check_status()
+  runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(model_dirs, dtype):
   d = model_dirs("C")
   reqs = rc.make_requests(1000, (400,), seed=8)

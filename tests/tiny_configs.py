@@ -31,4 +31,12 @@ TINY_D = dict(
   attention_bias=False, use_sliding_window=True, sliding_window=100, max_window_layers=1,
   hidden_act="silu", initializer_range=0.02)
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head size 128 and room for prompts of more than a thousand tokens: what a step of many rows runs
+# through (the tcgen05 gate-and-up product, the many-token form of the QK-norm/rotation kernel)
+TINY_E = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=136,
+  num_attention_heads=2, num_key_value_heads=1, head_dim=128, intermediate_size=200, vocab_size=300,
+  rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=2048, tie_word_embeddings=True,
+  attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
