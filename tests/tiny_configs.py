@@ -1,7 +1,8 @@
 """The small configurations the tests run on.  A and B differ in every size and option; C adds a
 sliding window on some layers; D has head size 64, which with pages of 64 tokens takes the engine
-through the TMA decode kernel and the tcgen05 prefill kernel, with a window on its second layer; all
-have sizes that are no power of two somewhere."""
+through the TMA decode kernel and the tcgen05 prefill kernel, with a window on its second layer; E
+has head size 128 and room for prompts of more than a thousand tokens; all have sizes that are no
+power of two somewhere."""
 
 TINY_A = dict(
   architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=64,
