@@ -114,6 +114,14 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort = 1;
   atomicExch(status, 2);
 }
+// One look at a barrier, without blocking: has the phase of this parity completed?
+__device__ __forceinline__ uint32_t mbar_peek(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -325,39 +333,45 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       // products of one stream to do while the softmax warps of the other work.  The tensor cores
       // run the products in the order they are issued: P V of a tile (which reads P from the
       // columns of S) is issued before S of the stream's next tile overwrites them.
-      auto issue_s = [&](int i) {
+      // What this one thread issues is on the path of both streams, so it is kept short: the
+      // descriptors are made once and stepped by addition (the address field counts 16 bytes), a
+      // barrier that copies complete is looked at before the thread blocks on the softmax warps'
+      // barrier (the look's latency passes meanwhile), and only that barrier - behind which other
+      // threads wrote P with tcgen05.st - is followed by a fence.
+      const uint64_t q_desc = smem_desc(q_addr, 16, 1024);
+      auto k_step = [](int ks) { return (uint64_t)((ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2); };
+      auto issue_s = [&](int i, uint32_t ready) {
         const int s = i % STAGES, b = i & 1;
-        mbar_wait(&k_full[s], (i / STAGES) & 1, abort, a.status);
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES);
+        if (!ready) mbar_wait(&k_full[s], (i / STAGES) & 1, abort, a.status);
+        const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES), 16, 1024);
         const uint32_t d = tmem_base + S_COL + 128 * b;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * HALF_BYTES + (ks & 3) * 32);
-          tc_mma(d, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), IDESC_S, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < HD / 16; ++ks)
+          tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
         tc_commit(&s_full[b]);
         tc_commit(&k_empty[s]);
       };
       mbar_wait(q_full, 0, abort, a.status);
-      if (!*abort) issue_s(0);
-      if (!*abort && n > 1) issue_s(1);
+      if (!*abort) issue_s(0, 0u);
+      if (!*abort && n > 1) issue_s(1, 0u);
       for (int j = 0; j < n && !*abort; ++j) {
         const int s = j % STAGES, b = j & 1;
+        const uint32_t v_ready = mbar_peek(&v_full[s], (j / STAGES) & 1);
+        const uint32_t k_ready = j + 2 < n ? mbar_peek(&k_full[(j + 2) % STAGES], ((j + 2) / STAGES) & 1) : 1u;
         mbar_wait(&p_full[b], (j / 2) & 1, abort, a.status);
-        mbar_wait(&v_full[s], (j / STAGES) & 1, abort, a.status);
+        if (!v_ready) mbar_wait(&v_full[s], (j / STAGES) & 1, abort, a.status);
         if (*abort) break;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES);
+        const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
         const uint32_t p_tmem = tmem_base + S_COL + 128 * b;   // thread `ch` of a row leaves its 64 keys in its first 32 columns
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks)
+        for (int ks = 0; ks < BN / 16; ++ks)                   // 16 keys further: 2048 bytes of V
           tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(64 * (ks >> 2) + 8 * (ks & 3)),
-                    smem_desc(v_addr + (uint32_t)ks * 2048u, HALF_BYTES, 1024), IDESC_PV,
+                    v_desc + (uint64_t)(ks * (2048 >> 4)), IDESC_PV,
                     (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over its tiles in tensor memory
         tc_commit(&o_full[b]);
         tc_commit(&v_empty[s]);
-        if (j + 2 < n) issue_s(j + 2);
+        if (j + 2 < n) issue_s(j + 2, k_ready);
       }
     }
   } else {
