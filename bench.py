@@ -32,6 +32,10 @@ sys.path.insert(0, ROOT)
 MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=28, hidden_size=1024,
              num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936,
              rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=True)
+# other shapes for --shape: what differs from MODEL
+SHAPES = {"0.6b": {},
+          "8b": dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                     intermediate_size=12288, tie_word_embeddings=False)}
 CONTEXT = 2048
 GENERATED = 256
 MAX_MODEL_LEN = 4096
@@ -334,7 +338,8 @@ def main() -> int:
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--batch", type=int, default=8)
-  ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help="fewer layers than the model has (named in config)")
+  ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")
+  ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
   ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
   ap.add_argument("--skip-points", action="store_true")
   ap.add_argument("--mixed", action="store_true",
@@ -344,6 +349,10 @@ def main() -> int:
   args = ap.parse_args()
   if args.impl == "reference":
     return reference_arm()
+  MODEL.update(SHAPES[args.shape])
+  shape_name = f"Qwen3-{args.shape.upper()} shape"
+  if args.layers is None:
+    args.layers = MODEL["num_hidden_layers"]
   if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
     print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
     return 2
@@ -362,7 +371,7 @@ def main() -> int:
     with open(os.path.join(d, "config.json"), "w") as f:
       json.dump(cfg, f)
     if args.mixed:
-      print(json.dumps(dict(mixed_workload(d), layers=args.layers, model="Qwen3-0.6B shape")))
+      print(json.dumps(dict(mixed_workload(d), layers=args.layers, model=shape_name)))
       return 0
     if args.kernel_table:
       print(kernel_table(build_engine(d, args.batch), args.batch, mode=args.kernel_table))
@@ -387,14 +396,14 @@ def main() -> int:
   achieved = step_bytes / (dec["ms"] * 1e-3) / 1e9
   flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
   line = {
-    "metric": "decode tok/s at batch 8 (Qwen3-0.6B shape, 2048-token contexts, bf16)",
+    "metric": f"decode tok/s at batch {args.batch} ({shape_name}, {CONTEXT}-token contexts, bf16)",
     "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
     "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
     "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids", "impl": "ours",
-    "config": {"model": "Qwen3-0.6B shape", "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
+    "config": {"model": shape_name, "layers": args.layers, "layers_of_model": MODEL["num_hidden_layers"],
                "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-               "tied_head": True, "global_batch": args.batch, "seq_len": CONTEXT, "generated": GENERATED,
+               "tied_head": bool(cfg["tie_word_embeddings"]), "global_batch": args.batch, "seq_len": CONTEXT, "generated": GENERATED,
                "max_model_len": MAX_MODEL_LEN, "page_size": PAGE, "parallelism": "single GPU",
                "l2": "each step reads weights+cache (>1 GB), larger than L2", "sampling": "temperature 0.6",
                "decode_path": "CUDA graph replay; e2e: a step is launched before the tokens of the step before are read (enable_overlap)"},
