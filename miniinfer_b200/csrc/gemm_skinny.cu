@@ -15,6 +15,13 @@
 // 16-byte load is exactly its fragment of two consecutive MMAs (thread t of a quad loads
 // k = 8t..8t+7; MMA s uses elements 4s..4s+3 of it).
 //
+// At the sizes of larger models the kernel is further from the memory system's speed than at the
+// benchmark's (measured alone with cold weights, 8 rows: 8B-shape QKV, 50 MB, 17.5 us; o, 34 MB,
+// 11.1 us; gate-up with SwiGLU, 201 MB, 43 us; the LM head's 1.2 GB stream at 5.8 TB/s).  A
+// variant with the activations in shared memory and three groups of weight registers, two of them
+// in flight, was tried for those sizes and was slower (QKV 20.5 us, gate-up 49.6 us): copying the
+// activations in costs more than the deeper queue of loads gains.
+//
 // The reference calls cuBLAS through nn.Linear for these products
 // (miniinfer/models/fused_qwen3.py:95,107,135,137; miniinfer/layers/embedding.py:29-32).
 #include "common.cuh"
