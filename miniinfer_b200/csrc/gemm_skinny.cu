@@ -276,6 +276,13 @@ int dispatch(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M, i
   // Wider warp tiles re-use the activation fragments; narrower ones make more blocks.
   const bool wide = N >= 2048;
   // (16 weight rows per warp where there are many rows: half as many blocks, all of them on the SMs at once)
+  // With 16 rows per warp and K split eight ways a block covers 16 rows.  If that makes a little more
+  // blocks than the SMs hold at once (two each), 24 rows per warp bring them back under: one round of
+  // blocks that all run together instead of a full round and a nearly empty one.
+  const int blocks16 = (N + 15) / 16;
+  if (M <= 16 && blocks16 > 296 && blocks16 <= 444 && K >= 512)
+    return M <= 8 ? launch<1, 3, 8, true, TOut, false>(out, x, w, M, N, K, ldo, stream)
+                  : launch<1, 3, 8, false, TOut, false>(out, x, w, M, N, K, ldo, stream);
   if (M <= 8) return wide ? pick_ksplit<1, 2, true, TOut>(out, x, w, M, N, K, ldo, stream)
                           : pick_ksplit<1, 1, true, TOut>(out, x, w, M, N, K, ldo, stream);
   if (M <= 16) return wide ? pick_ksplit<1, 2, false, TOut>(out, x, w, M, N, K, ldo, stream)

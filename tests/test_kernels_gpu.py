@@ -73,7 +73,8 @@ def test_linear_float32_is_true_float32_and_row_invariant(ops, M, N, K):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("N,K", [(24, 64), (1000, 136), (4096, 1024), (333, 2048), (8, 8)])
+@pytest.mark.parametrize("N,K", [(24, 64), (1000, 136), (4096, 1024), (333, 2048), (8, 8),
+                                 (6144, 512), (5000, 520)])     # a little more than 296 blocks of 16 rows: 24 rows per warp
 def test_linear_bf16_few_rows(ops, out_dtype, N, K):
   w = rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.05)
   xs = rnd(64, K, dtype=torch.bfloat16, seed=1)
