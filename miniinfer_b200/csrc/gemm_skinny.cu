@@ -17,10 +17,12 @@
 //
 // At the sizes of larger models the kernel is further from the memory system's speed than at the
 // benchmark's (measured alone with cold weights, 8 rows: 8B-shape QKV, 50 MB, 17.5 us; o, 34 MB,
-// 11.1 us; gate-up with SwiGLU, 201 MB, 43 us; the LM head's 1.2 GB stream at 5.8 TB/s).  A
-// variant with the activations in shared memory and three groups of weight registers, two of them
-// in flight, was tried for those sizes and was slower (QKV 20.5 us, gate-up 49.6 us): copying the
-// activations in costs more than the deeper queue of loads gains.
+// 11.1 us; gate-up with SwiGLU, 201 MB, 43 us; down, 101 MB, 22.9 us; the LM head's 1.2 GB stream
+// at 5.8 TB/s).  Two variants that keep more bytes in flight were tried for those sizes and were no
+// faster: the activations in shared memory and three groups of weight registers (QKV 20.5 us,
+// gate-up 49.6 us), and the weights through shared memory with cp.async, three groups deep (gate-up
+// 49.0 us, down 27.1 us).  So it is not the depth of the queue of loads that limits these launches;
+// their times fit 4 to 5 us per launch for starting and ending plus the bytes at 5.3 TB/s.
 //
 // The reference calls cuBLAS through nn.Linear for these products
 // (miniinfer/models/fused_qwen3.py:95,107,135,137; miniinfer/layers/embedding.py:29-32).

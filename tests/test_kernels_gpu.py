@@ -237,6 +237,35 @@ class _Scratch:
     return self.made[name]
 
 
+@pytest.mark.parametrize("N,K,swiglu", [(6144, 4096, False), (4096, 4096, False), (3080, 4104, False), (3072, 4096, True),
+                                          (12288, 2048, True), (2056, 6152, True)])
+def test_few_rows_times_many_megabytes_of_weights(ops, N, K, swiglu):
+  """The few-row product at the sizes of larger models (24 MB of weights and more) against the
+  statement; a row's value must not depend on the other rows."""
+  w = rnd((2 if swiglu else 1) * N, K, dtype=torch.bfloat16, seed=2, scale=0.03)
+  xs = rnd(16, K, dtype=torch.bfloat16, seed=1)
+  first = {}
+  for M in (16, 8, 1, 5, 11):
+    x = xs[:M].contiguous()
+    want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    if swiglu:
+      gu = torch.empty(M, 2 * N, dtype=torch.bfloat16, device=DEV)
+      ref.linear(gu, x, w)
+      ref.silu_mul(want, gu)
+      ops.linear_swiglu(out, x, w, _Scratch())
+    else:
+      ref.linear(want, x, w)
+      ops.linear(out, x, w)
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
+    if M in (16, 8):
+      first[M] = out
+    else:
+      assert torch.equal(out, first[16][:M]), "a row's value must not depend on the other rows"
+  assert torch.equal(first[8], first[16][:8])
+
+
 @pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (7, 8), (333, 2048)])
 def test_linear_swiglu(ops, I, K):
   """The fused gate-and-up product against product + activation (which it must match up to the
