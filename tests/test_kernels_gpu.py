@@ -41,7 +41,8 @@ def test_embedding(ops, dtype, V, H, T):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H,eps", [(5, 200, 1e-5), (3, 1024, 1e-6), (2, 5120, 1e-6), (1, 7, 1e-3)])
+@pytest.mark.parametrize("T,H,eps", [(5, 200, 1e-5), (3, 1024, 1e-6), (2, 5120, 1e-6), (1, 7, 1e-3),
+                                     (300, 1024, 1e-6), (257, 200, 1e-5), (260, 520, 1e-6), (256, 4096, 1e-6)])   # many rows
 def test_add_rmsnorm(ops, dtype, T, H, eps):
   w = 1 + 0.1 * rnd(H, seed=1)
   for delta_on, rows_on, wb in ((True, False, True), (False, False, True), (True, True, False), (False, True, False)):
