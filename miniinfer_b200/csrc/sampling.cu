@@ -36,8 +36,10 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
 }
 
 __device__ __forceinline__ float uniform_for(uint64_t key, int index) {
+  // 23 bits: (n + 0.5) * 2^-23 is exact in float32 and lies in [2^-24, 1 - 2^-24], strictly inside
+  // (0, 1).  With 24 bits the largest n + 0.5 would round up and give u = 1, whose noise is +inf.
   const uint64_t bits = mix64(key ^ ((uint64_t)index * 0xD1342543DE82EF95ull));
-  return ((float)(bits >> 40) + 0.5f) * (1.0f / 16777216.0f);
+  return ((float)(bits >> 41) + 0.5f) * (1.0f / 8388608.0f);
 }
 
 __device__ __forceinline__ uint32_t ordered(float f) {
@@ -210,7 +212,7 @@ sample_pick_kernel(int* __restrict__ out, const float* __restrict__ logits, cons
     for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) {
       const float z = x[i] / temp;
       if (ordered(z) < thr || !(z > -INFINITY)) continue;
-      // u <= 1 - 2^-25, so the noise -log(-log(u)) stays below 17.4: a score that far under this
+      // u <= 1 - 2^-24, so the noise -log(-log(u)) stays below 16.7 < 17.4: a score that far under this
       // thread's best cannot win, and its draw need not be worked out
       if (z + 17.4f < b.v) continue;
       const float u = uniform_for(key, i);
@@ -310,7 +312,9 @@ MI_API int mi_sample_static(int* out, const float* logits, const float* temperat
     g_sample_static_addr[device] = p;
   }
   unsigned int* base = (unsigned int*)g_sample_static_addr[device];
-  // the same slicing rule as the callers of mi_sample use
+  // slices of the vocabulary per row: about two blocks of the pick kernel per SM of a B200, bounded so that
+  // the results fit the fixed scratch.  Callers of mi_sample choose their own count (the engine asks for
+  // more); the token is the same for any count, since the arg-max over slices is associative.
   int slices = 296 / R;
   if (slices > 64) slices = 64;
   if (slices > (V + 1023) / 1024) slices = (V + 1023) / 1024;

@@ -35,7 +35,7 @@ MAX_LIVE_REQUESTS = 8
 
 class TraceRunner:
   def __init__(self, model_dir: str, dtype, max_tokens: int, device: str = "cuda:0",
-               page_size: int = TRACE_PAGE_SIZE):
+               page_size: int = TRACE_PAGE_SIZE, num_pages: Optional[int] = None):
     self.dtype = parse_dtype(dtype)
     self.device = torch.device(device)
     if self.device.type == "cuda":
@@ -45,7 +45,10 @@ class TraceRunner:
     self.model_config = load_model_config(model_dir)
     self.spec = build_model_spec(self.model_config)
     load_weights(self.spec, model_dir, self.dtype, self.device)
-    num_pages = max(1, -(-int(max_tokens) // page_size))
+    if page_size < 1:
+      raise ValueError(f"page size must be positive, got {page_size}")
+    if num_pages is None:
+      num_pages = max(1, -(-int(max_tokens) // page_size))
     max_len = min(self.model_config.max_position_embeddings, num_pages * page_size)
     self.cache = KVCacheManager(self.spec.cache_layer_specs(), page_size, num_pages, MAX_LIVE_REQUESTS, max_len,
                                 self.dtype, self.device)
@@ -82,12 +85,15 @@ def main(argv=None, stdin: Optional[IO[str]] = None, stdout: Optional[IO[str]] =
   p.add_argument("--out", required=True, help="folder for <step>.f32 files")
   p.add_argument("--max-tokens", type=int, required=True,
                  help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+  p.add_argument("--page-size", type=int, default=TRACE_PAGE_SIZE, help="tokens per page of the cache (default 64)")
+  p.add_argument("--num-pages", type=int, default=None,
+                 help="pages of the cache pool (default: --max-tokens divided by the page size, rounded up)")
   p.add_argument("--device", default="cuda:0")
   args = p.parse_args(argv)
   stdin = stdin or sys.stdin
   stdout = stdout or sys.stdout
   os.makedirs(args.out, exist_ok=True)
-  tr = TraceRunner(args.model, args.dtype, args.max_tokens, args.device)
+  tr = TraceRunner(args.model, args.dtype, args.max_tokens, args.device, page_size=args.page_size, num_pages=args.num_pages)
   for line in stdin:
     line = line.strip()
     if not line:

@@ -9,7 +9,7 @@ reaches ``top_p`` (top-k first, then top-p, as sample.py:115-122); the token is
 
     mix(x): x ^= x >> 30; x *= 0xBF58476D1CE4E5B9; x ^= x >> 27; x *= 0x94D049BB133111EB; x ^= x >> 31
     key  = mix(seed ^ mix(counter + 0x9E3779B97F4A7C15))
-    u_i  = ((mix(key ^ (i * 0xD1342543DE82EF95)) >> 40) + 0.5) / 2^24        (64-bit wrap-around)
+    u_i  = ((mix(key ^ (i * 0xD1342543DE82EF95)) >> 41) + 0.5) / 2^23        (64-bit wrap-around; exact in float32, inside (0, 1))
 
 so a request's tokens do not depend on what else is in the batch or on how its prompt was cut
 (the reference draws from the global generator, sample.py:115-128).

@@ -5,9 +5,9 @@ Run once, by hand, where the reference checkout is available:
     python tests/golden/make_reference_golden.py /path/to/MiniInfer
 
 It builds ``miniinfer.models.fused_qwen3.Qwen3ForCausalLM`` in float32 from a tiny configuration,
-loads random weights drawn from a seeded CPU generator (the draw is repeated by
-tests/test_plain.py), runs one whole sequence and stores the token ids, the logits at every
-position and a checksum of the weights.
+loads random weights drawn from a seeded CPU generator, runs one whole sequence and stores the
+token ids, the logits at every position, and the weights themselves (under ``w:<tensor name>``; they
+are small), so that tests/test_plain.py does not depend on what a torch build draws from a seed.
 
 The reference's forward needs a GPU in three places; each is replaced by the same formula in torch,
 and the attention library by the reference's own dense grouped attention:
@@ -127,7 +127,7 @@ def main(ref_root: str) -> None:
     assert logits.shape == (T, cfg["vocab_size"]), logits.shape
     np.savez_compressed(os.path.join(HERE, f"reference_logits_{tag}.npz"), ids=ids.numpy().astype(np.int32),
                         logits=logits.float().numpy(), weight_checksum=np.float64(checksum(sd)),
-                        seed=np.int64(seed))
+                        seed=np.int64(seed), **{f"w:{k}": v.numpy() for k, v in sd.items()})
     print(tag, logits.shape, float(logits.abs().max()))
 
 

@@ -256,7 +256,13 @@ def uniform_for(seed: int, counter: int, index: int) -> float:
   """The uniform number in (0, 1) that belongs to (seed, output index, vocabulary index)."""
   key = _mix64((seed & ((1 << 64) - 1)) ^ _mix64(counter + 0x9E3779B97F4A7C15))
   bits = _mix64(key ^ ((index * 0xD1342543DE82EF95) & ((1 << 64) - 1)))
-  return ((bits >> 40) + 0.5) * (1.0 / (1 << 24))
+  return uniform_from_bits(bits)
+
+
+def uniform_from_bits(bits: int) -> float:
+  """The top 23 bits of a 64-bit hash as a number strictly inside (0, 1): (n + 0.5) / 2^23 has 24
+  significant bits, so float32 holds it exactly and the largest value is 1 - 2^-24, not 1."""
+  return ((bits >> 41) + 0.5) * (1.0 / (1 << 23))
 
 
 def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: float) -> torch.Tensor:

@@ -66,37 +66,54 @@ def portions(reqs: Dict[str, List[int]], sizes: Sequence[int] = (13, 7, 2, 29, 3
 
 
 def mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int, max_live: int = 4, decode_tail: int = 6,
-          granule: int = 64) -> List[dict]:
+          granule: int = 64, preempt: bool = False) -> List[dict]:
   """Up to ``max_live`` requests at a time: portions of some beside single tokens of others, some left
   out of a step now and then, a new request starting as soon as one has ended and its room
-  (``granule``-rounded) is free again - so that pages are used again."""
+  (``granule``-rounded) is free again - so that pages are used again.
+
+  ``preempt``: every request of more than eight tokens is, once, ended mid-way (what a scheduler does
+  when pages run out: everything the request holds is given back), waits behind the next request, and
+  comes back under the same id with all the tokens it had been fed as ONE portion, then goes on
+  where it was.  The logits of its second life must be those of its first at every position."""
   rng = random.Random(seed)
-  waiting = list(reqs.items())
+  prng = random.Random(seed + 1000)           # draws of its own, so that preempt=False gives the traces it always gave
+  waiting = [(rid, ids, 0) for rid, ids in reqs.items()]
   live: Dict[str, dict] = {}
+  cut_at = {rid: prng.randint(max(2, len(ids) // 3), len(ids) - 2) for rid, ids in reqs.items() if preempt and len(ids) > 8}
   trace, step = [], 0
   while waiting or live:
     held = sum(round_up(len(v["ids"]), granule) for v in live.values())
     while waiting and len(live) < max_live and held + round_up(len(waiting[0][1]), granule) <= max_tokens:
-      rid, ids = waiting.pop(0)
-      live[rid] = {"ids": ids, "pos": 0}
+      rid, ids, resume = waiting.pop(0)
+      live[rid] = {"ids": ids, "pos": 0, "resume": resume}
       held += round_up(len(ids), granule)
     assert live, "max_tokens is too small for the next request"
-    entries, end = [], []
+    entries, end, again = [], [], []
     chosen = [rid for rid in live if rng.random() < 0.8] or [next(iter(live))]
     for rid in chosen:
       st = live[rid]
       left = len(st["ids"]) - st["pos"]
-      if left <= decode_tail:
+      if st["resume"]:
+        n, st["resume"] = st["resume"], 0       # the second life starts with everything fed so far, as one portion
+      elif left <= decode_tail:
         n = 1
       else:
         n = min(left - decode_tail, rng.choice((2, 3, 5, 8, 13, 21, 40)))
+      if rid in cut_at and st["pos"] < cut_at[rid] < st["pos"] + n:
+        n = cut_at[rid] - st["pos"]
       toks = st["ids"][st["pos"]:st["pos"] + n]
-      entries.append({"id": rid, "tokens": toks, "want": list(range(n)) if rng.random() < 0.8 else [n - 1]})
+      entries.append({"id": rid, "tokens": toks, "want": list(range(n)) if rng.random() < 0.8 or n > 64 else [n - 1]})
       st["pos"] += n
       if st["pos"] == len(st["ids"]):
         end.append(rid)
+      elif cut_at.get(rid) == st["pos"]:
+        del cut_at[rid]
+        end.append(rid)
+        again.append((rid, st["ids"], st["pos"]))
     for rid in end:
       del live[rid]
+    # a preempted request waits behind the next one in line, so that its pages are taken meanwhile
+    waiting[1:1] = again
     trace.append({"step": step, "entries": entries, "end": end})
     step += 1
   return trace
@@ -105,19 +122,27 @@ def mixed(reqs: Dict[str, List[int]], max_tokens: int, seed: int, max_live: int 
 # ------------------------------------------------------------------------------ running and comparing
 
 
-def collect(trace: List[dict], outputs: Dict[int, np.ndarray]) -> Dict[Tuple[str, int], np.ndarray]:
-  """(request, position) -> logits row, from the per-step outputs."""
+def collect(trace: List[dict], outputs: Dict[int, np.ndarray]) -> Dict[tuple, np.ndarray]:
+  """(request, position) -> logits row, from the per-step outputs.  A request that was ended and came
+  back under the same id starts again at position 0; rows of its later lives are kept under
+  (request, position, life) beside those of the first."""
   pos: Dict[str, int] = {}
-  got: Dict[Tuple[str, int], np.ndarray] = {}
+  life: Dict[str, int] = {}
+  got: Dict[tuple, np.ndarray] = {}
   for rec in trace:
     rows = outputs.get(rec["step"])
     r = 0
     for e in rec["entries"]:
       start = pos.get(e["id"], 0)
+      n = life.get(e["id"], 0)
       for w in e["want"]:
-        got[(e["id"], start + w)] = rows[r]
+        got[(e["id"], start + w) if n == 0 else (e["id"], start + w, n)] = rows[r]
         r += 1
       pos[e["id"]] = start + len(e["tokens"])
+    for rid in rec.get("end", []):
+      if rid in pos:
+        del pos[rid]
+        life[rid] = life.get(rid, 0) + 1
     assert rows is None or r == rows.shape[0]
   return got
 
@@ -141,7 +166,8 @@ def compare(got: Dict[Tuple[str, int], np.ndarray], ref: Dict[str, torch.Tensor]
   """Every wanted row against the plain implementation; says where the first wrong row is."""
   worst = 0.0
   assert got, "nothing was compared"
-  for (rid, p), row in sorted(got.items()):
+  for key, row in sorted(got.items()):
+    rid, p = key[0], key[1]
     r = ref[rid][p].numpy()
     d = float(np.abs(row - r).max())
     worst = max(worst, d)

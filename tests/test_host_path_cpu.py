@@ -28,8 +28,9 @@ def test_every_cut_gives_the_plain_logits(cpu_kernels, model_dirs, tag, page):
   ref = rc.reference_logits(d, reqs)
   budget = 4 * rc.round_up(max(LENGTHS[tag]), page)
   for name, trace in (("whole", rc.whole(reqs)), ("tail", rc.tail_one_by_one(reqs)), ("portions", rc.portions(reqs)),
-                      ("mixed", rc.mixed(reqs, budget // 2, seed=1, granule=page))):
-    runner = make_runner(d, page, budget if name != "mixed" else budget // 2)
+                      ("mixed", rc.mixed(reqs, budget // 2, seed=1, granule=page)),
+                      ("preempted", rc.mixed(reqs, budget // 2, seed=2, granule=page, preempt=True))):
+    runner = make_runner(d, page, budget if name not in ("mixed", "preempted") else budget // 2)
     got = rc.run_in_process(runner, trace)
     rc.compare(got, ref, 2e-5, f"{tag}/{name}")
     runner.cache.check_invariants()

@@ -48,18 +48,20 @@ def runner_for(model_dir, dtype, max_tokens, page):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("tag", ["A", "B", "C", "D"])
-@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "preempted"])
 def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
   d = model_dirs(tag)
   page = PAGES[tag]
   reqs = rc.make_requests(ALL[tag]["vocab_size"], LENGTHS[tag], seed=5)
   ref = reference(d, tag, reqs)
   longest = rc.round_up(max(LENGTHS[tag]), page)
-  if cut == "mixed":
+  if cut in ("mixed", "preempted"):
     # room for the longest request plus a little: requests must wait for pages that others give back
     budget = longest + 2 * rc.round_up(70, page)
-    trace = rc.mixed(reqs, budget, seed=1, granule=page)
+    trace = rc.mixed(reqs, budget, seed=1, granule=page, preempt=cut == "preempted")
     assert max(len(r["entries"]) for r in trace) >= 2
+    if cut == "preempted":     # requests are ended mid-way and come back as prompt + what they had been fed
+      assert sum(len(r["end"]) for r in trace) >= 2 * len(reqs) - 2
   else:
     budget = longest
     trace = {"whole": rc.whole, "tail": rc.tail_one_by_one, "portions": rc.portions}[cut](reqs)
@@ -67,6 +69,13 @@ def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
   got = rc.run_in_process(runner, trace)
   margin = 1e-3 if dtype == "float32" else None
   rc.compare(got, ref, tolerance(dtype, ref), f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
+  if cut == "preempted":
+    second = [k for k in got if len(k) == 3]
+    assert len(second) > len(reqs)
+    if dtype == "float32":       # the second life of a request gives the bits of the first
+      for rid, p, _ in second:
+        if (rid, p) in got:
+          assert np.array_equal(got[(rid, p)], got[(rid, p, 1)]), (rid, p)
   runner.cache.check_invariants()
   assert runner.cache.free_pages() == [g.num_pages for g in runner.cache.paged_groups]
 

@@ -139,7 +139,7 @@ def gumbel_scores(logits_row, temperature, top_k, top_p, seed, counter):
     last = int((before < top_p).nonzero().max())
     z = torch.where(pr >= sp[last], z, torch.full_like(z, float("-inf")))
   key = _mix64((seed & _M) ^ _mix64(counter + 0x9E3779B97F4A7C15))
-  u = torch.tensor([((_mix64(key ^ ((i * 0xD1342543DE82EF95) & _M)) >> 40) + 0.5) / (1 << 24) for i in range(V)],
+  u = torch.tensor([((_mix64(key ^ ((i * 0xD1342543DE82EF95) & _M)) >> 41) + 0.5) / (1 << 23) for i in range(V)],
                    dtype=torch.float64)
   return z - torch.log(-torch.log(u))
 
