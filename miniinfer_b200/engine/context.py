@@ -9,8 +9,6 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..kernels.ops import AttentionBatch
-
 
 class Workspace:
   """Named activation buffers that keep their address from step to step, so that a captured step
@@ -67,7 +65,11 @@ class StepContext:
   ``positions[t]``, ``token_item[t]``: per token; ``q_start/q_len/ctx_len/seq_slot[b]``: per item;
   ``slot_mapping[g][t]`` and ``block_tables[g]``: per group of paged layers; ``state_slots`` is
   ``seq_slot`` (the row of a request in every per-request state tensor); ``host`` keeps the same
-  numbers as Python lists for parts that loop on the host."""
+  numbers as Python lists for parts that loop on the host (such a part sets ``reads_step_on_host``).
+  ``work[name]`` is the device view of a work list that a part declared (``Part.step_work``) and
+  ``work_key[name]`` its key, the host-side numbers the part's launches may depend on; ``shared`` is
+  a scratch dictionary for what the layers of one step want to make once and share; ``captured``
+  says that the step is being recorded into a CUDA graph (or run to prepare that)."""
 
   def __init__(self, dtype: torch.dtype, device, ws: Workspace):
     self.dtype = dtype
@@ -85,9 +87,12 @@ class StepContext:
     self.logit_rows: Optional[torch.Tensor] = None
     self.slot_mapping: List[torch.Tensor] = []
     self.block_tables: List[torch.Tensor] = []
-    self.attn: Optional[AttentionBatch] = None
     self.host: Dict[str, list] = {}
     self.extra: Dict[str, torch.Tensor] = {}
+    self.work: Dict[str, torch.Tensor] = {}
+    self.work_key: Dict[str, tuple] = {}
+    self.shared: Dict[str, object] = {}
+    self.captured = False
 
   @property
   def state_slots(self) -> torch.Tensor:

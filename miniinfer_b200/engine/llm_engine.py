@@ -219,7 +219,7 @@ class LLMEngine:
     R = len(sampling_reqs)
     dev, _ = self._token_buffers(max(R, 1))
     toks_dev = self.runner.step_and_sample(items, extras, Sampler.sample, dev, use_graphs=not self.config.enforce_eager,
-                                           ids_on_device=ids_on_device)
+                                           ids_on_device=ids_on_device, sampling_pad=Sampler.PAD_ROWS)
     self.stats["h2d_bytes"] += self.runner.last_h2d_bytes
     self.stats["launches"] += self.runner.last_launches
     self.stats["steps"] += 1

@@ -17,6 +17,16 @@ token ids from a device buffer - the tokens the step before has sampled - so tha
 have read them yet.  Any other step (a prompt portion, a mixed step) is recorded as a graph of its
 own once its shape has been seen twice, and replayed when that shape comes again
 (``_shape_step``); kernel by kernel a step is bound by the host's time per launch.
+
+Recording a graph touches nothing of the live requests: the run that prepares the recording works on
+a step of the same shape whose items all sit in the padding slot and the dummy page, and the real
+step then runs once, as the first replay.  So a step's tokens pass through the model exactly once
+whether or not it is the step that records, which mixers with per-request state updated in place
+rely on.
+
+What a part's kernels need per step beyond the common description - attention's lists of decode
+items and prefill tiles, say - the part declares (``Part.step_work``); the step function knows no
+part's tiling.
 """
 
 from __future__ import annotations
@@ -30,13 +40,12 @@ import torch
 
 from ..cache.manager import KVCacheManager, OutOfPages
 from ..kernels import ops
-from ..kernels.ops import AttentionBatch
 from ..models.spec import ModelSpec
+from ..parts.base import HostStep, StepWork
 from .context import StepContext, Workspace
 
-PREFILL_TILE = 64   # query rows of one prefill-attention tile
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-GRAPH_CONTEXT_STEP = 1024   # a captured decode step serves contexts up to a multiple of this
+DECODE_GRAPHS_KEPT = 12     # graphs of decode-only steps that are kept (each holds buffers of its own, logits included)
 STEP_GRAPHS_KEPT = 8        # graphs of steps other than decode-only ones (prompt portions, mixed steps) that are kept
 STEP_GRAPH_AFTER = 2        # a step of a shape is recorded once that shape has been seen this many times ...
 STEP_GRAPH_WINDOW = 64      # ... no more than this many steps apart: recording costs about twenty steps' worth of host
@@ -126,7 +135,7 @@ class _DecodeGraph:
     self.logits: Optional[torch.Tensor] = None
     self.tokens: Optional[torch.Tensor] = None
     self.launches = 0
-    self.max_ctx_len = 0
+    self.work_keys: Dict[str, tuple] = {}
     # the description of a step with no live entry (all padding) and where each array lies in it
     self.template: Optional[np.ndarray] = None
     self.offsets: Dict[str, Tuple[int, int]] = {}
@@ -152,10 +161,18 @@ class ModelRunner:
       else:
         self.layer_caches.append(cache.layer_cache(run.cache_of, writes=False))
     self.meta = _MetaBuffers(self.device)
-    # a part that reads the step on the host would have its decisions frozen into a recorded graph
     parts = spec.all_parts() if hasattr(spec, "all_parts") else []
+    # sizes that a part's kernels cannot take are refused here, before any step
+    for p in parts:
+      p.validate(dtype)
+    # the work lists the parts declare, one of each name
+    self.work: "OrderedDict[str, StepWork]" = OrderedDict()
+    for p in parts:
+      for w in p.step_work():
+        self.work.setdefault(w.name, w)
+    # a part that reads the step on the host would have its decisions frozen into a recorded graph
     self.graphs_allowed = not any(getattr(p, "reads_step_on_host", False) for p in parts)
-    self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+    self._graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
     # steps of any other kind, by shape (see _shape_key): how often seen, and the graphs of the repeated ones
     self._shape_seen: Dict[tuple, Tuple[int, int]] = {}      # shape -> (times seen, step it was last seen at)
     self._shape_steps = 0
@@ -225,15 +242,19 @@ class ModelRunner:
     a["ctx_len"] = start_np + q_len
     a["seq_slot"] = np.array([cache.slot_of(it.req_id) for it in items], dtype=np.int32)
     a["logit_rows"] = np.array([q_start[b] + w for b, it in enumerate(items) for w in it.want], dtype=np.int32)
-    a["decode_items"] = np.array([b for b in range(B) if q_len[b] == 1], dtype=np.int32)
-    a["prefill_tiles"] = np.array([(b, o) for b in range(B) if q_len[b] > 1
-                                   for o in range(0, int(q_len[b]), PREFILL_TILE)], dtype=np.int32).reshape(-1)
+    host = HostStep(q_len, start_np, cache.max_model_len)
+    for name, w in self.work.items():
+      a[f"work:{name}"] = np.asarray(w.build(host), dtype=np.int32).reshape(-1)
     for k, v in (extras or {}).items():
       a[f"extra:{k}"] = np.asarray(v, dtype=np.int32)
     return a
 
+  def _work_keys(self, q_len: np.ndarray, start: np.ndarray) -> Dict[str, tuple]:
+    host = HostStep(q_len, start, self.cache.max_model_len)
+    return {name: tuple(w.key(host)) for name, w in self.work.items()}
+
   def _context(self, a: "OrderedDict[str, np.ndarray]", offsets: Dict[str, Tuple[int, int]], dev: torch.Tensor,
-               ws: Workspace, max_ctx_len: Optional[int] = None) -> StepContext:
+               ws: Workspace, work_keys: Optional[Dict[str, tuple]] = None, captured: bool = False) -> StepContext:
     def view(name):
       o, n = offsets[name]
       return dev[o:o + n]
@@ -251,12 +272,9 @@ class ModelRunner:
                 "start": (a["ctx_len"] - a["q_len"]).tolist(), "seq_slot": a["seq_slot"].tolist(),
                 "logit_rows": a["logit_rows"].tolist()}
     ctx.extra = {k[len("extra:"):]: view(k) for k in a if k.startswith("extra:")}
-    ctx.attn = AttentionBatch(
-      token_item=ctx.token_item, positions=ctx.positions, seq_slot=ctx.seq_slot, q_start=ctx.q_start,
-      q_len=ctx.q_len, ctx_len=ctx.ctx_len, num_tokens=ctx.num_tokens, num_items=ctx.num_items,
-      prefill_tiles=view("prefill_tiles").view(-1, 2), num_prefill_tiles=len(a["prefill_tiles"]) // 2,
-      decode_items=view("decode_items"), num_decode=len(a["decode_items"]),
-      max_ctx_len=max_ctx_len if max_ctx_len is not None else int(a["ctx_len"].max()), scratch=ws)
+    ctx.work = {k[len("work:"):]: view(k) for k in a if k.startswith("work:")}
+    ctx.work_key = work_keys if work_keys is not None else self._work_keys(a["q_len"], a["ctx_len"] - a["q_len"])
+    ctx.captured = captured
     return ctx
 
   def prepare(self, items: Sequence[StepItem], extras: Optional[dict] = None) -> StepContext:
@@ -305,24 +323,15 @@ class ModelRunner:
 
   # ------------------------------------------------------------------ steps of a repeated shape, from CUDA graphs
 
-  def _shape_key(self, items: Sequence[StepItem], starts: Sequence[int], sampled: bool) -> tuple:
-    """What the launches of a step depend on: the counts of tokens, items, prefill tiles, decode
-    items and wanted rows, the context class of the decode items (their split-KV grid), and whether
-    the sampler runs.  Everything else about the step is in the description on the device."""
-    T = B = tiles = n_dec = R = 0
-    longest = 0
-    for it, st in zip(items, starts):
-      n = len(it.tokens)
-      T += n
-      B += 1
-      R += len(it.want)
-      if n == 1:
-        n_dec += 1
-        longest = max(longest, st + 1)
-      else:
-        tiles += -(-n // PREFILL_TILE)
-    ctx_class = min(self.cache.max_model_len, -(-longest // GRAPH_CONTEXT_STEP) * GRAPH_CONTEXT_STEP) if n_dec else 0
-    return (T, B, tiles, n_dec, R, ctx_class, sampled)
+  def _shape_key(self, items: Sequence[StepItem], starts: Sequence[int], sampled: bool) -> Tuple[tuple, Dict[str, tuple]]:
+    """What the launches of a step depend on: the counts of tokens, items and wanted rows, whether
+    the sampler runs, and the keys of the work lists that the parts declare (for attention: the
+    numbers of decode items and prefill tiles and the class of the longest decode context, which
+    sizes the split-KV grid).  Everything else about the step is in the description on the device."""
+    q_len = np.array([len(it.tokens) for it in items], dtype=np.int32)
+    keys = self._work_keys(q_len, np.array(starts, dtype=np.int32))
+    R = sum(len(it.want) for it in items)
+    return (int(q_len.sum()), len(items), R, sampled) + tuple(keys.values()), keys
 
   def _shape_step(self, items: Sequence[StepItem], extras: Optional[dict], sample_fn) -> Optional[_DecodeGraph]:
     """Runs the step from a CUDA graph if a step of its shape has been recorded, records it if the
@@ -334,7 +343,7 @@ class ModelRunner:
     self._shape_steps += 1
     if not (self.graphs_allowed and self.device.type == "cuda"):
       return None
-    key = self._shape_key(items, starts, sample_fn is not None)
+    key, work_keys = self._shape_key(items, starts, sample_fn is not None)
     g = self._step_graphs.get(key)
     if g is None:
       seen, last = self._shape_seen.get(key, (0, 0))
@@ -348,20 +357,19 @@ class ModelRunner:
       arrays = self._describe(items, starts, extras)
       if g is None:
         g = _DecodeGraph(len(items), self.device)
-        g.max_ctx_len = key[5]
+        g.work_keys = work_keys
         g.offsets, g.total = g.meta.layout(arrays)
-        g.meta.upload(arrays)
         self.cache.sync()
-        self._capture(g, arrays, g.offsets, sample_fn, rows=key[4])
+        self._capture(g, arrays, g.offsets, sample_fn, rows=key[2])
         self._step_graphs[key] = g
         while len(self._step_graphs) > STEP_GRAPHS_KEPT:
           self._step_graphs.popitem(last=False)
       else:
         self._step_graphs.move_to_end(key)
-        offsets = g.meta.upload(arrays, fixed_capacity=True)
-        if offsets != g.offsets:
-          raise RuntimeError("a step's description does not have the layout its shape was recorded with")
-        self.cache.sync()
+      offsets = g.meta.upload(arrays, fixed_capacity=True)
+      if offsets != g.offsets:
+        raise RuntimeError("a step's description does not have the layout its shape was recorded with")
+      self.cache.sync()
       self.last_h2d_bytes = g.meta.bytes_copied
       g.graph.replay()
       self.last_launches = g.launches
@@ -409,9 +417,12 @@ class ModelRunner:
   def step_and_sample(self, items: Sequence[StepItem], sampling: Dict[str, np.ndarray],
                       sample_fn: Callable[..., None],
                       tokens_out: torch.Tensor, use_graphs: bool = True,
-                      ids_on_device: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      ids_on_device: Optional[torch.Tensor] = None,
+                      sampling_pad: Optional[Dict[str, np.ndarray]] = None) -> torch.Tensor:
     """Runs the step and samples one token for each wanted row into ``tokens_out`` (int32, device).
-    ``sampling``: packed per-row options (``Sampler.pack``).  Returns the tokens' device view.
+    ``sampling``: packed per-row options (``Sampler.pack``).  ``sampling_pad``: for each option the
+    words of a row that samples harmlessly, for the padding rows of a captured decode step (default:
+    zero words).  Returns the tokens' device view.
     A step of decode tokens only, each wanting its one row, is replayed from a CUDA graph; for such
     a step ``ids_on_device`` (int32, one per item) may give the tokens instead of the items: the
     tokens a step before has sampled and the host has not read yet."""
@@ -420,7 +431,7 @@ class ModelRunner:
     if ids_on_device is not None and bucket is None:
       raise ValueError("tokens on the device are taken by graph decode steps only")
     if bucket is not None:
-      return self._graph_step(items, sampling, sample_fn, tokens_out, bucket, ids_on_device)
+      return self._graph_step(items, sampling, sample_fn, tokens_out, bucket, ids_on_device, sampling_pad)
     if use_graphs and R:
       g = self._shape_step(items, sampling, sample_fn)      # a step of a repeated shape: forward pass and sampler from one graph
       if g is not None:
@@ -440,9 +451,12 @@ class ModelRunner:
     self.last_launches = ops.launch_count() - before
     return tokens_out[:R]
 
-  def _padded(self, a: "OrderedDict[str, np.ndarray]", bucket: int) -> "OrderedDict[str, np.ndarray]":
+  def _padded(self, a: "OrderedDict[str, np.ndarray]", bucket: int, sampling_pad: Optional[Dict[str, np.ndarray]] = None
+              ) -> "OrderedDict[str, np.ndarray]":
     """Fills a decode-only description up to ``bucket`` entries.  The extra entries belong to the
-    padding slot, whose block table points at the dummy page: they read one key there and write there."""
+    padding slot, whose block table points at the dummy page: they read one key there and write
+    there; their state rows are the padding slot's.  Work lists are made anew for the padded step;
+    the sampler's options get the rows their owner declared harmless (zero words otherwise)."""
     B = len(a["q_len"])
     n = bucket - B
 
@@ -453,43 +467,55 @@ class ModelRunner:
     for k, v in a.items():
       if k in ("ids", "positions") or k.startswith("slot_mapping"):
         out[k] = pad(v, 0)
-      elif k in ("token_item", "q_start", "logit_rows", "decode_items"):
+      elif k in ("token_item", "q_start", "logit_rows"):
         out[k] = np.arange(bucket, dtype=np.int32)
       elif k in ("q_len", "ctx_len"):
         out[k] = pad(v, 1)
       elif k == "seq_slot":
         out[k] = pad(v, self.cache.pad_slot)
-      elif k == "prefill_tiles":
-        out[k] = v
-      elif k == "extra:top_p":
-        out[k] = np.concatenate([v, np.full(n, 1.0, dtype=np.float32).view(np.int32)])
-      elif k in ("extra:seed", "extra:counter"):
-        out[k] = pad(v, 0, 2 * n)   # 64-bit values, two words each
+      elif k.startswith("work:"):
+        out[k] = v                                  # replaced below, once the padded numbers are known
       elif k.startswith("extra:"):
-        out[k] = pad(v, 0)          # temperature 0: the padding rows take the arg-max
+        width = len(v) // B if B else None          # words per row
+        row = (sampling_pad or {}).get(k[len("extra:"):])
+        if row is None:
+          row = np.zeros(width if width is not None else 1, dtype=np.int32)
+        out[k] = np.concatenate([v, np.tile(np.asarray(row, dtype=np.int32), n)])
       else:
         raise KeyError(k)
+    host = HostStep(out["q_len"], out["ctx_len"] - out["q_len"], self.cache.max_model_len)
+    for name, w in self.work.items():
+      out[f"work:{name}"] = np.asarray(w.build(host), dtype=np.int32).reshape(-1)
     return out
 
-  def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int, ids_on_device=None) -> torch.Tensor:
+  def _graph_step(self, items, sampling, sample_fn, tokens_out, bucket: int, ids_on_device=None, sampling_pad=None) -> torch.Tensor:
     starts = self._check_and_reserve(items)
     self._shape_steps += 1
     B = len(items)
     try:
-      # the split-KV grid is part of the capture: one graph per (bucket, context class)
-      longest = max(starts) + 1
-      ctx_class = min(self.cache.max_model_len, -(-longest // GRAPH_CONTEXT_STEP) * GRAPH_CONTEXT_STEP)
-      g = self._graphs.get((bucket, ctx_class))
+      # what the captured launches depend on (for attention: the split-KV grid, sized from the class of the
+      # longest context) is part of the graph's identity: one graph per (bucket, keys of the work lists)
+      q_len = np.ones(bucket, dtype=np.int32)
+      start_np = np.zeros(bucket, dtype=np.int32)
+      start_np[:B] = starts
+      work_keys = self._work_keys(q_len, start_np)
+      key = (bucket,) + tuple(work_keys.values())
+      g = self._graphs.get(key)
       if g is None:
-        g = self._graphs[(bucket, ctx_class)] = _DecodeGraph(bucket, self.device)
-        g.max_ctx_len = ctx_class
+        g = self._graphs[key] = _DecodeGraph(bucket, self.device)
+        g.work_keys = work_keys
+        while len(self._graphs) > DECODE_GRAPHS_KEPT:
+          self._graphs.popitem(last=False)          # the least recently used graph goes, with its buffers
+      else:
+        self._graphs.move_to_end(key)
       if g.graph is None:
-        arrays = self._decode_layout(g, self._describe(items, starts, sampling))
-        g.meta.upload(arrays)
+        described = self._describe(items, starts, sampling)
+        arrays = self._decode_layout(g, described, sampling_pad)
         self.cache.sync()
         self._capture(g, arrays, g.offsets, sample_fn)
+        g.meta.upload(arrays, fixed_capacity=True)
       else:
-        self._fill_decode(g, items, starts, sampling)
+        self._fill_decode(g, items, starts, sampling, q_len, start_np)
         self.cache.sync()
       self.last_h2d_bytes = g.meta.bytes_copied
       if ids_on_device is not None:
@@ -505,11 +531,17 @@ class ModelRunner:
     self._finish(items, True)
     return g.tokens[:B]
 
-  def _decode_layout(self, g: _DecodeGraph, described: "OrderedDict[str, np.ndarray]") -> "OrderedDict[str, np.ndarray]":
+  def _decode_layout(self, g: _DecodeGraph, described: "OrderedDict[str, np.ndarray]", sampling_pad=None
+                     ) -> "OrderedDict[str, np.ndarray]":
     """Fixes where each array of a decode-only step lies in the graph's buffers and keeps the
     description of a step without live entries; returns ``described`` padded to the bucket."""
-    arrays = self._padded(described, g.bucket)
-    empty = self._padded(OrderedDict((k, v[:0]) for k, v in described.items()), g.bucket)
+    arrays = self._padded(described, g.bucket, sampling_pad)
+    B = len(described["q_len"])
+    widths = {k: len(v) // B for k, v in described.items() if k.startswith("extra:")}
+    empty_in = OrderedDict((k, v[:0]) for k, v in described.items())
+    pad_rows = {k[len("extra:"):]: np.asarray((sampling_pad or {}).get(k[len("extra:"):], np.zeros(w, dtype=np.int32)), dtype=np.int32)
+                for k, w in widths.items()}
+    empty = self._padded(empty_in, g.bucket, pad_rows)
     g.offsets, g.total = g.meta.layout(arrays)
     g.template = np.zeros(g.total, dtype=np.int32)
     for k, v in empty.items():
@@ -517,7 +549,7 @@ class ModelRunner:
       g.template[o:o + n] = v
     return arrays
 
-  def _fill_decode(self, g: _DecodeGraph, items, starts, sampling) -> None:
+  def _fill_decode(self, g: _DecodeGraph, items, starts, sampling, q_len: np.ndarray, start_np: np.ndarray) -> None:
     """A decode-only step written straight into the graph's staging array: the entries that differ
     from step to step (token, position, cache slot, length, request slot, sampling options) over the
     all-padding description.  Gives the same words as ``_padded(_describe(...))``."""
@@ -541,25 +573,47 @@ class ModelRunner:
       put(f"slot_mapping{gi}", [cache.slot_at(it.req_id, gi, s) for it, s in zip(items, starts)])
     for k, v in sampling.items():
       put(f"extra:{k}", v if v.dtype == np.int32 else v.view(np.int32))
+    for name, w in self.work.items():
+      if w.per_step:          # a list that depends on more than the bucket is made anew from the padded step's numbers
+        put(f"work:{name}", np.asarray(w.build(HostStep(q_len, start_np, cache.max_model_len)), dtype=np.int32).reshape(-1))
     g.meta.send(g.total)
+
+  def _neutral(self, arrays: "OrderedDict[str, np.ndarray]") -> "OrderedDict[str, np.ndarray]":
+    """A step of the same shape that belongs to nobody: every item sits in the padding slot (whose
+    block table points at the dummy page and whose state rows are scratch), every token is token 0
+    and is stored in the dummy page.  Lengths, positions and work lists stay, so the same kernels
+    run with the same grids."""
+    out: "OrderedDict[str, np.ndarray]" = OrderedDict()
+    for k, v in arrays.items():
+      if k == "ids" or k.startswith("slot_mapping"):
+        out[k] = np.zeros_like(v)
+      elif k == "seq_slot":
+        out[k] = np.full_like(v, self.cache.pad_slot)
+      else:
+        out[k] = v
+    return out
 
   def _capture(self, g: _DecodeGraph, arrays, offsets, sample_fn, rows: Optional[int] = None) -> None:
     """Records forward pass (and sampler, if given) over the graph's own buffers.  ``rows``: sampled
-    rows (default: one per entry of the bucket)."""
-    # every length of the context class must be served by the captured launch: size the split-KV grid for it
-    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, max_ctx_len=g.max_ctx_len if g.max_ctx_len else None)
+    rows (default: one per entry of the bucket).
+
+    Nothing of the live requests is touched: the run that sizes the workspace, configures the kernels
+    and makes the libraries load what they will launch (nothing may be loaded while a graph is
+    recorded) works on a step of the same shape in the padding slot and the dummy page.  The caller
+    uploads the real description afterwards and replays the graph once, so the step's tokens pass
+    through the model exactly once - which a mixer that updates per-request state in place needs."""
+    g.meta.upload(self._neutral(arrays))
+    g.ctx = self._context(arrays, offsets, g.meta.dev, g.ws, work_keys=g.work_keys, captured=True)
     g.tokens = torch.zeros(max(g.bucket if rows is None else rows, 1), dtype=torch.int32, device=self.device)
 
     def run():
+      g.ctx.shared.clear()
       g.logits = self.forward(g.ctx)
       if sample_fn is not None and g.logits.shape[0] > 0:
         sample_fn(g.logits, g.ctx.extra, g.tokens[:g.logits.shape[0]], g.ws)
 
-    # The first run sizes the workspace, configures the kernels and makes the libraries load what
-    # they will launch (nothing may be loaded while a graph is recorded): it takes the same paths
-    # as the recording.
     with ops.recording_graph():
-      run()
+      run()                                  # takes the same paths as the recording
       torch.cuda.current_stream().synchronize()
       g.ws.frozen = True
       before = ops.launch_count()

@@ -21,6 +21,7 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
+PREFILL_TILE = 64     # query rows of one tile of the prefill attention kernels
 SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
 SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
 GEMM_TC_MIN_M = 1280  # from here the tcgen05 gate-up product with SwiGLU beats cuBLAS + activation (measured on B200
@@ -419,7 +420,9 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
-    use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 16 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
+    # more than 8 query heads per kv head: the TMA kernel would walk an item's tiles twice and hand a stage back only
+    # in the second pass, which cannot work once an item has more tiles than there are stages - the cp.async kernel takes those
+    use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")
     if use_tma:
       # the TMA kernel deals 64-key tiles out evenly; a (request, kv head) is cut into at most as many
       # pieces as it has tiles, and no more than there are blocks

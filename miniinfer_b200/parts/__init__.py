@@ -1,4 +1,5 @@
-from .base import Block, FeedForward, Mixer, Norm, ParamSpec, Part, Piece, PositionEncoding, whole
+from .base import (Block, FeedForward, HostStep, Mixer, Norm, ParamSpec, Part, Piece, PositionEncoding, StepWork,
+                   whole)
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .feedforward import SwiGLUFeedForward

@@ -16,6 +16,11 @@ Interfaces (see the concrete parts for examples):
 ``PositionEncoding`` gives mixers what they need to encode positions (``rotary_table()``), and may
                    act on the hidden state after the embedding (``apply_to_hidden``).
 ``Block``          ``forward(resid, pending, ctx, cache) -> pending``: the arrangement of the above.
+
+Two more things any part may state: ``validate(dtype)`` refuses, when the engine is built, the sizes
+its kernels cannot take; ``step_work()`` declares int32 work lists (``StepWork``) that its kernels
+need for every step - the step function makes them on the host, uploads them with the rest of the
+step's description and hands them to the part in ``ctx.work``.
 """
 
 from __future__ import annotations
@@ -23,6 +28,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.specs import CacheSpec
@@ -56,6 +62,53 @@ def whole(file_name: str, shape: Sequence[int]) -> List[Piece]:
   return [Piece(file_name, 0, tuple(shape))]
 
 
+class HostStep:
+  """The numbers of a step as the host knows them, for the makers of work lists: for every item its
+  number of new tokens ``q_len`` and its length before the step ``start`` (int32 arrays)."""
+
+  def __init__(self, q_len: np.ndarray, start: np.ndarray, max_model_len: int):
+    self.q_len = q_len
+    self.start = start
+    self.max_model_len = max_model_len
+
+  @property
+  def num_items(self) -> int:
+    return len(self.q_len)
+
+  def decode_items(self) -> np.ndarray:
+    """Indices of the items that bring exactly one token."""
+    return np.flatnonzero(self.q_len == 1).astype(np.int32)
+
+  def longest_decode_context(self) -> int:
+    """The largest length, this step's token included, among the items that bring one token (0: none)."""
+    one = self.q_len == 1
+    return int((self.start[one] + 1).max()) if one.any() else 0
+
+  def context_class(self, length: int, step: int) -> int:
+    """``length`` rounded up to a multiple of ``step``, no more than the longest request allowed."""
+    return min(self.max_model_len, -(-length // step) * step) if length else 0
+
+
+class StepWork:
+  """An int32 work list that a part's kernels need for each step.
+
+  ``name`` identifies the list: parts that declare a list of the same name share it (it is made once
+  per step).  ``build(step)`` returns the array.  ``key(step)`` returns what the part's launches
+  depend on beyond the array's contents on the device - its length as a rule, and any bound that
+  sizes a grid; steps with equal keys may be replayed from one recorded CUDA graph, and the key is
+  handed to the part as ``ctx.work_key[name]``.  ``per_step``: set it if, for steps of single tokens
+  only, the array depends on more than the number of items (it is then made anew for every step)."""
+
+  name = ""
+  per_step = False
+
+  def build(self, step: HostStep) -> np.ndarray:
+    raise NotImplementedError
+
+  def key(self, step: HostStep) -> tuple:
+    return (len(self.build(step)),)
+
+
 class Part:
   """Base of all parts.  ``name`` is the prefix of the part's tensors in a weights file.
 
@@ -80,6 +133,14 @@ class Part:
       setattr(self, k, v)
 
   def sub_parts(self) -> List["Part"]:
+    return []
+
+  def validate(self, dtype: torch.dtype) -> None:
+    """Raises ``ValueError`` if the part's kernels cannot take its sizes in this compute dtype.  Called
+    once when the engine is built, so that a configuration is refused before any step runs."""
+
+  def step_work(self) -> List["StepWork"]:
+    """The work lists this part needs for every step (default: none)."""
     return []
 
 

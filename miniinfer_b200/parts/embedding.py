@@ -46,6 +46,11 @@ class LMHead(Part):
     shape = (self.vocab_size, self.hidden_size)
     return {"weight": ParamSpec(shape, "matrix", [whole(f"{self.name}.weight", shape)])}
 
+  def validate(self, dtype: torch.dtype) -> None:
+    if dtype == torch.bfloat16 and self.hidden_size % 8:
+      raise ValueError(f"{self.name}: hidden_size={self.hidden_size} must be a multiple of 8 in bfloat16 "
+                       f"(rows are read 16 bytes at a time)")
+
   def table(self) -> torch.Tensor:
     return self.tied_to.weight if self.tied_to is not None else self.weight
 

@@ -28,6 +28,12 @@ class SwiGLUFeedForward(FeedForward):
       "down": ParamSpec((H, I), "matrix", [whole(f"{self.name}.down_proj.weight", (H, I))]),
     }
 
+  def validate(self, dtype: torch.dtype) -> None:
+    if dtype == torch.bfloat16:
+      for what, k in (("hidden_size", self.hidden_size), ("intermediate_size", self.intermediate_size)):
+        if k % 8:
+          raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
+
   def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
     T = x.shape[0]
     act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)

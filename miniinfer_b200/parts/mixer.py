@@ -9,13 +9,48 @@ projection.  Head counts, head size, scale, eps and window are constructor argum
 
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
+import numpy as np
 import torch
 
 from ..cache.specs import CacheSpec, PagedKVSpec
 from ..kernels import ops
-from .base import Mixer, ParamSpec, Piece, PositionEncoding, whole
+from ..kernels.ops import AttentionBatch
+from .base import HostStep, Mixer, ParamSpec, Piece, PositionEncoding, StepWork, whole
+
+DECODE_CONTEXT_STEP = 1024   # the split-KV grid of a step is sized for its longest context rounded up to this
+
+
+class DecodeItems(StepWork):
+  """The items that bring one token: the split-KV decode kernel works through these.  Its grid is
+  sized from their number and from a bound on their context lengths, so both are the list's key."""
+
+  name = "attention_decode_items"
+
+  def build(self, step: HostStep) -> np.ndarray:
+    return step.decode_items()
+
+  def key(self, step: HostStep) -> tuple:
+    return (int((step.q_len == 1).sum()), step.context_class(step.longest_decode_context(), DECODE_CONTEXT_STEP))
+
+
+class PrefillTiles(StepWork):
+  """(item, first row) of every tile of ``ops.PREFILL_TILE`` query rows of the items that bring
+  several tokens: one block of the prefill attention kernel per tile and head."""
+
+  name = "attention_prefill_tiles"
+
+  def build(self, step: HostStep) -> np.ndarray:
+    pairs = [(b, o) for b in np.flatnonzero(step.q_len > 1) for o in range(0, int(step.q_len[b]), ops.PREFILL_TILE)]
+    return np.array(pairs, dtype=np.int32).reshape(-1)
+
+  def key(self, step: HostStep) -> tuple:
+    n = step.q_len[step.q_len > 1]
+    return (int((-(-n // ops.PREFILL_TILE)).sum()),)
+
+
+_WORK = [DecodeItems(), PrefillTiles()]
 
 
 class AttentionMixer(Mixer):
@@ -53,6 +88,37 @@ class AttentionMixer(Mixer):
       specs["k_norm"] = ParamSpec((hd,), "vector", [whole(f"{n}.k_norm.weight", (hd,))], init="ones_noise")
     return specs
 
+  def validate(self, dtype: torch.dtype) -> None:
+    hd, H = self.head_dim, self.hidden_size
+    if hd % 4 or not (4 <= hd <= 256):
+      raise ValueError(f"{self.name}: head_dim={hd} is not supported: the attention kernels take multiples of 4 up to 256 "
+                       f"(multiples of 16 run on the tensor cores in bfloat16)")
+    if dtype == torch.bfloat16:
+      for what, k in (("hidden_size", H), ("num_attention_heads * head_dim", self.num_heads * hd),
+                      ("(num_attention_heads + 2 * num_key_value_heads) * head_dim", (self.num_heads + 2 * self.num_kv_heads) * hd)):
+        if k % 8:
+          raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
+    rotary = getattr(self.position, "rotary_dim", None)
+    if rotary is not None and rotary > hd:
+      raise ValueError(f"{self.name}: the rotary encoding covers {rotary} values, more than head_dim={hd}")
+
+  def step_work(self) -> List[StepWork]:
+    return _WORK
+
+  @staticmethod
+  def _batch(ctx) -> AttentionBatch:
+    """The step as the attention kernels take it; made once per step and shared by all layers."""
+    batch = ctx.shared.get("attention_batch")
+    if batch is None:
+      dec, tiles = ctx.work[DecodeItems.name], ctx.work[PrefillTiles.name]
+      batch = AttentionBatch(
+        token_item=ctx.token_item, positions=ctx.positions, seq_slot=ctx.seq_slot, q_start=ctx.q_start, q_len=ctx.q_len,
+        ctx_len=ctx.ctx_len, num_tokens=ctx.num_tokens, num_items=ctx.num_items,
+        prefill_tiles=tiles.view(-1, 2), num_prefill_tiles=tiles.shape[0] // 2, decode_items=dec, num_decode=dec.shape[0],
+        max_ctx_len=max(1, ctx.work_key[DecodeItems.name][1]), scratch=ctx.ws)
+      ctx.shared["attention_batch"] = batch
+    return batch
+
   def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
     T = x.shape[0]
     nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
@@ -68,7 +134,7 @@ class AttentionMixer(Mixer):
                            cache.tensor if cache.writes else None, nh, nkv, hd,
                            self.qk_norm_eps if self.qk_norm_eps is not None else 1.0)
     attn = ctx.ws.buffer("attn_out", (T, nh * hd), ctx.dtype)
-    ops.attention(attn, qkv, cache.tensor, ctx.block_tables[cache.group], ctx.attn, nh, nkv, hd,
+    ops.attention(attn, qkv, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), nh, nkv, hd,
                   self.scale, self.window)
     out = ctx.ws.buffer("mixer_out", (T, self.hidden_size), ctx.dtype)
     ops.linear(out, attn, self.o)

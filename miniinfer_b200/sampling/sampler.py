@@ -34,6 +34,10 @@ class Sampler:
   """Packs the per-row options into int32 words (for the step's single host-to-device copy) and
   launches the kernel."""
 
+  # a row of options that samples harmlessly (temperature 0: the arg-max, nothing filtered): what the padding
+  # rows of a captured decode step get; options not named here are padded with zero words
+  PAD_ROWS: Dict[str, np.ndarray] = {"top_p": np.array([1.0], dtype=np.float32).view(np.int32)}
+
   @staticmethod
   def pack(params: Sequence[SamplingParams], seeds: Sequence[int], counters: Sequence[int]) -> Dict[str, np.ndarray]:
     R = len(params)

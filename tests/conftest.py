@@ -50,7 +50,7 @@ def model_dirs(tmp_path_factory):
     key = (tag, dtype, seed)
     if key not in made:
       d = tmp_path_factory.mktemp(f"tiny_{tag}_{dtype}")
-      s = seed if seed is not None else {"A": 1, "B": 2, "C": 3, "D": 4, "E": 5}[tag]
+      s = seed if seed is not None else {"A": 1, "B": 2, "C": 3, "D": 4, "E": 5, "F": 6, "R": 7}[tag]
       write_random_model(dict(ALL[tag]), str(d), seed=s, dtype=getattr(torch, dtype))
       made[key] = str(d)
     return made[key]

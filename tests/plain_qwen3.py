@@ -196,8 +196,10 @@ def lm_head_weight(weights: Dict[str, torch.Tensor]) -> torch.Tensor:
 
 def forward(weights: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int],
             run_list: Optional[List[Tuple[int, Optional[int]]]] = None,
-            dtype: torch.dtype = torch.float32) -> torch.Tensor:
-  """Logits [T, V] of one whole sequence (miniinfer/models/fused_qwen3.py:243-259,344).
+            dtype: torch.dtype = torch.float32, rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+  """Logits [T, V] of one whole sequence (miniinfer/models/fused_qwen3.py:243-259,344); with
+  ``rows``, only at those positions (the reference keeps the last row of a sequence,
+  fused_qwen3.py:317-334): the layers still run on the whole sequence.
 
   The block is pre-norm with the residual carried beside the hidden state
   (fused_qwen3.py:175-196): ``res = h (+ res)``; ``x = norm1(res)``; ``a = attn(x)``;
@@ -232,6 +234,8 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int],
     h = swiglu_mlp(x, weights, p)
   if h is not None:
     res = h + res
+  if rows is not None:
+    res = res[torch.as_tensor(list(rows), dtype=torch.long)]
   x = rms_norm(res, _w(weights, "model.norm.weight"), eps)
   return (x @ lm_head_weight(weights).t()).float()
 
@@ -303,10 +307,32 @@ def generate(weights: Dict[str, torch.Tensor], cfg: dict, prompt: Sequence[int],
   ids = list(prompt)
   out: List[int] = []
   for n in range(max_tokens):
-    logits = forward(weights, cfg, ids)[-1]
+    logits = forward(weights, cfg, ids, rows=[len(ids) - 1])[0]
     tok, _ = sample_token(logits, temperature, top_k, top_p, seed, n)
     out.append(tok)
     ids.append(tok)
     if eos is not None and tok in eos:
       break
   return out
+
+
+def check_greedy_tokens(weights: Dict[str, torch.Tensor], cfg: dict, prompt: Sequence[int], tokens: Sequence[int],
+                        margin: float) -> int:
+  """Whether ``tokens`` are a greedy continuation of ``prompt``, by ONE pass over prompt + tokens:
+  each token must be the arg-max of the logits at the position before it, or lie within ``margin`` of
+  the largest logit there (a choice that rounding may turn).  If every token is the arg-max, this is
+  what ``generate`` gives token by token, since equal prefixes give equal logits.  Returns how many
+  tokens were the arg-max itself."""
+  ids = list(prompt) + list(tokens)
+  P, n = len(prompt), len(tokens)
+  logits = forward(weights, cfg, ids[:-1], rows=range(P - 1, P - 1 + n))
+  exact = 0
+  for i, tok in enumerate(tokens):
+    row = logits[i]
+    best = int(row.argmax())
+    if tok == best:
+      exact += 1
+      continue
+    gap = float(row[best] - row[tok])
+    assert gap <= margin, f"output token {i}: engine chose {tok} (logit {float(row[tok]):.5f}), plain chooses {best} ({float(row[best]):.5f}): gap {gap:.2e} > {margin:.1e}"
+  return exact

@@ -7,6 +7,7 @@ A trace is a list of records as ``bin/trace_run`` reads them:
 
 from __future__ import annotations
 
+import os
 import random
 from typing import Dict, List, Sequence, Tuple
 
@@ -179,3 +180,13 @@ def compare(got: Dict[Tuple[str, int], np.ndarray], ref: Dict[str, torch.Tensor]
       if top2[1] - top2[0] > check_argmax_margin:
         assert int(row.argmax()) == int(r.argmax()), f"{what}: request {rid} position {p}: another greedy token"
   return worst
+
+
+def log_worst(what: str, worst: float, ref: Dict[str, torch.Tensor]) -> None:
+  """With MINIINFER_B200_DIFF_LOG=<file> the largest difference of every comparison is appended there,
+  beside the largest reference logit: the record from which the bfloat16 bounds of the tests are set."""
+  path = os.environ.get("MINIINFER_B200_DIFF_LOG")
+  if path:
+    top = max(float(v.abs().max()) for v in ref.values())
+    with open(path, "a") as f:
+      f.write(f"{what} worst_abs_diff={worst:.6f} max_abs_logit={top:.4f}\n")

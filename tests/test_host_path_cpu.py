@@ -150,15 +150,17 @@ def test_decode_description_written_in_place_equals_the_general_one(cpu_kernels,
     items = [StepItem(rid, [7 + step + i], (0,)) for i, rid in enumerate(rids)]
     packed = Sampler.pack(params[:len(rids)], [11, 2 ** 40 + 5, 3][:len(rids)], [step] * len(rids))
     starts = run._check_and_reserve(items)
-    general = run._padded(run._describe(items, starts, packed), 4)
+    general = run._padded(run._describe(items, starts, packed), 4, Sampler.PAD_ROWS)
     if g.template is None:
-      run._decode_layout(g, run._describe(items, starts, packed))
+      run._decode_layout(g, run._describe(items, starts, packed), Sampler.PAD_ROWS)
     want = np.zeros(g.total, dtype=np.int32)
     for k, v in general.items():
       o, n = g.offsets[k]
       assert n == len(v)
       want[o:o + n] = v
-    run._fill_decode(g, items, starts, packed)
+    start_np = np.zeros(4, dtype=np.int32)
+    start_np[:len(starts)] = starts
+    run._fill_decode(g, items, starts, packed, np.ones(4, dtype=np.int32), start_np)
     assert np.array_equal(g.meta.host.numpy()[:g.total], want), (step, rids)
     run._finish(items, True)
   for rid in lengths:

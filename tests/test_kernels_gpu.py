@@ -193,6 +193,20 @@ def test_attention_over_pages(ops, mode, case):
   assert (out.float() - want.float()).abs().max() < (2e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("nh,nkv", [(16, 1), (32, 4), (24, 2)])
+def test_decode_attention_many_requests_long_contexts_wide_groups(ops, nh, nkv):
+  """Sixteen, eight and twelve query heads per kv head, 40 requests of 2048 and more tokens: every block of
+  the decode kernels gets many key tiles.  No bounded wait may run out (the call raises if one does)."""
+  items = [(2048 + 37 * i, 1) for i in range(40)]
+  qkv, kv, bt, batch = make_attention_case(items, nh, nkv, 128, 64, torch.bfloat16, seed=3, num_slots=48)
+  out = torch.full((len(items), nh * 128), float("nan"), dtype=torch.bfloat16, device=DEV)
+  want = torch.empty_like(out)
+  ops.attention(out, qkv, kv, bt, batch, nh, nkv, 128, 128 ** -0.5, None)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, 128, 128 ** -0.5, None)
+  assert torch.isfinite(out.float()).all()
+  assert (out.float() - want.float()).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
   """Random data would hide a key that is skipped: make one key's score stand out."""

@@ -1,0 +1,113 @@
+"""The engine at the layer sizes the benchmark times - Qwen3-0.6B's hidden 1024, 16 query and 8 kv heads
+of 128, intermediate 3072, vocabulary 151936, tied head, pages of 64 tokens - with 2 of its 28 layers,
+against the plain implementation: the logits under every way of cutting the requests into steps, in
+float32 and in bfloat16; generation with more live requests than the few-row kernels take (the decode
+steps then go through the library product inside CUDA graphs); and generation over prompts of about a
+thousand tokens, whose decode graphs pass from one context class into the next."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import replay_cases as rc
+from gpu_helpers import DEV
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+
+CFG = ALL["R"]
+V = CFG["vocab_size"]
+LENGTHS = (33, 130, 200, 65)
+PAGE = 64
+
+# float32: the bound the engine is built for.  bfloat16: three times the largest difference seen on a B200 for
+# this model over all cuts (0.011: logits of size 3, two layers, every activation rounded to 8 bits of mantissa).
+BOUND = {"float32": 1e-4, "bfloat16": 0.08}
+
+_made = {}
+
+
+def weights_and_reference(model_dir):
+  if "ref" not in _made:
+    w, c = plain.read_weights(model_dir), plain.read_config(model_dir)
+    reqs = rc.make_requests(V, LENGTHS, seed=5)
+    _made.update(w=w, c=c, reqs=reqs, ref={rid: plain.forward(w, c, ids) for rid, ids in reqs.items()})
+  return _made["w"], _made["c"], _made["reqs"], _made["ref"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_cut_gives_the_plain_logits_at_real_layer_sizes(model_dirs, dtype):
+  from miniinfer_b200.engine.replay import TraceRunner
+  d = model_dirs("R")
+  w, c, reqs, ref = weights_and_reference(d)
+  longest = rc.round_up(max(LENGTHS), PAGE)
+  few = longest + 2 * rc.round_up(70, PAGE)
+  cuts = [("whole", rc.whole(reqs), longest), ("tail", rc.tail_one_by_one(reqs), longest),
+          ("portions", rc.portions(reqs), longest), ("mixed", rc.mixed(reqs, few, seed=1, granule=PAGE), few),
+          ("preempted", rc.mixed(reqs, few, seed=2, granule=PAGE, preempt=True), few)]
+  first = None
+  for name, trace, budget in cuts:
+    runner = TraceRunner(d, dtype, budget, device=DEV, page_size=PAGE)
+    got = rc.run_in_process(runner, trace)
+    margin = 1e-3 if dtype == "float32" else 2 * BOUND[dtype]
+    worst = rc.compare(got, ref, BOUND[dtype], f"0.6B sizes/{dtype}/{name}", check_argmax_margin=margin)
+    rc.log_worst(f"R/{dtype}/{name}", worst, ref)
+    runner.runner.check_status()
+    runner.cache.check_invariants()
+    assert runner.cache.free_pages() == [g.num_pages for g in runner.cache.paged_groups]
+    if dtype == "float32" and DEV != "cpu":       # the 32-bit kernels give the same bits under every cut
+      if first is None:
+        first = got
+      else:
+        for key, row in got.items():
+          if key[:2] in first:
+            assert np.array_equal(row, first[key[:2]]), (name, key)
+    del runner
+    if DEV != "cpu":
+      torch.cuda.empty_cache()
+
+
+def test_more_live_requests_than_the_few_row_kernels_take(model_dirs):
+  """24 requests decode together in bfloat16: 24 rows are more than the few-row kernels' 16, so every
+  product of these decode steps is the library's, recorded into the decode graph.  Every token is the
+  plain implementation's greedy choice, or within the bfloat16 bound of it."""
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  d = model_dirs("R")
+  w, c, _, _ = weights_and_reference(d)
+  lens = [20 + 7 * i for i in range(24)]
+  prompts = list(rc.make_requests(V, lens, seed=9).values())
+  eng = LLMEngine(d, dtype="bfloat16", device=DEV, page_size=PAGE, num_pages=24 * 4 + 8, max_num_seqs=24,
+                  max_model_len=256, max_num_batched_tokens=2048)
+  outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+  if DEV != "cpu":
+    assert eng.stats["decode_tokens"] >= 24 * 10 and eng.runner.num_graphs() >= 1
+    assert any(key[0] == 24 for key in eng.runner._graphs), "no decode graph of 24 rows was recorded"
+  exact = 0
+  for p, o in zip(prompts, outs):
+    assert len(o["token_ids"]) == 12
+    exact += plain.check_greedy_tokens(w, c, p, o["token_ids"], margin=2 * BOUND["bfloat16"])
+  assert exact >= 0.9 * 24 * 12, f"only {exact} of {24 * 12} tokens are the plain arg-max"
+  eng.runner.check_status()
+  assert eng.cache.free_pages() == [24 * 4 + 8]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_across_a_context_class(model_dirs, dtype):
+  """Prompts of 1000 and 970 tokens, 60 tokens generated each: decoding starts in the class of contexts
+  up to 1024 tokens and passes into the next, whose graph has a split-KV grid of its own.  float32: the
+  tokens are the plain implementation's; bfloat16: they are, or lie within the bound of its choice."""
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  d = model_dirs("R")
+  w, c, _, _ = weights_and_reference(d)
+  prompts = list(rc.make_requests(V, (1000, 970), seed=11).values())
+  eng = LLMEngine(d, dtype=dtype, device=DEV, page_size=PAGE, num_pages=2 * 17 + 4, max_num_seqs=2,
+                  max_model_len=2048, max_num_batched_tokens=2048)
+  outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=60))
+  if DEV != "cpu":
+    classes = sorted({key[1][1] for key in eng.runner._graphs})      # the decode work list's key: (rows, context class)
+    assert classes == [1024, 2048], classes
+  for p, o in zip(prompts, outs):
+    assert len(o["token_ids"]) == 60
+    exact = plain.check_greedy_tokens(w, c, p, o["token_ids"], margin=2e-4 if dtype == "float32" else 2 * BOUND["bfloat16"])
+    assert exact >= (58 if dtype == "float32" else 50)
+  eng.runner.check_status()

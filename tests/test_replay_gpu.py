@@ -19,8 +19,8 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LENGTHS = {"A": (5, 17, 33, 100, 64, 128, 41, 65), "B": (1, 9, 40, 71, 130, 65, 256, 2), "C": (90, 33, 150, 64, 7, 300, 129),
-           "D": (130, 70, 300, 64, 200, 65, 257)}
-PAGES = {"A": 16, "B": 8, "C": 64, "D": 64}
+           "D": (130, 70, 300, 64, 200, 65, 257), "F": (130, 70, 300, 64, 200, 65, 257)}
+PAGES = {"A": 16, "B": 8, "C": 64, "D": 64, "F": 64}
 
 # float32: the bound the engine is built for.  bfloat16: 8 bits of mantissa; activations are rounded
 # about six times per layer, the errors add like a random walk over at most four layers and the
@@ -47,7 +47,7 @@ def runner_for(model_dir, dtype, max_tokens, page):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D", "F"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "preempted"])
 def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
   d = model_dirs(tag)
@@ -68,7 +68,8 @@ def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
   runner = runner_for(d, dtype, budget, page)
   got = rc.run_in_process(runner, trace)
   margin = 1e-3 if dtype == "float32" else None
-  rc.compare(got, ref, tolerance(dtype, ref), f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
+  worst = rc.compare(got, ref, tolerance(dtype, ref), f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
+  rc.log_worst(f"{tag}/{dtype}/{cut}", worst, ref)
   if cut == "preempted":
     second = [k for k in got if len(k) == 3]
     assert len(second) > len(reqs)

@@ -40,4 +40,18 @@ TINY_E = dict(
   rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=2048, tie_word_embeddings=True,
   attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# eight query heads per kv head (the grouping of the Qwen3-32B shape, 64 / 8) with head size 128 on a narrow model
+TINY_F = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=264,
+  num_attention_heads=16, num_key_value_heads=2, head_dim=128, intermediate_size=520, vocab_size=1003,
+  rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=1024, tie_word_embeddings=False,
+  attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
+
+# the layer sizes of Qwen3-0.6B (the shape the benchmark times), two of its 28 layers
+QWEN3_06B_2_OF_28_LAYERS = dict(
+  architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=1024,
+  num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936,
+  rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=4096, tie_word_embeddings=True,
+  attention_bias=False, use_sliding_window=False, hidden_act="silu", initializer_range=0.02)
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "R": QWEN3_06B_2_OF_28_LAYERS}
