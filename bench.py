@@ -16,6 +16,13 @@ One JSON line is printed:
   roofline   bytes the decode step must read (every weight once + the cache of the live requests)
              divided by its time, against the measured HBM copy bandwidth
   points     decode tokens/s at batch 1 and 64
+  kernels    the dominant kernels of the decode step (the matrix products that stream the weights, the
+             attention kernel that streams the cache) and of the prefill step (the matrix products, the
+             attention kernel): microseconds per step from CUPTI kernel records of a few further steps,
+             the bytes or FLOPs they account for, and the rate that follows against the measured peak
+
+``--shape 8b`` / ``--shape 32b`` run the same measurement at the layer sizes of Qwen3-8B (36 layers) and
+Qwen3-32B (64 layers, 4096-token contexts, max_model_len 8192).
 """
 import argparse
 import json
@@ -35,7 +42,11 @@ MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_
 # other shapes for --shape: what differs from MODEL
 SHAPES = {"0.6b": {},
           "8b": dict(num_hidden_layers=36, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-                     intermediate_size=12288, tie_word_embeddings=False)}
+                     intermediate_size=12288, tie_word_embeddings=False),
+          "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                      intermediate_size=25600, tie_word_embeddings=False)}
+SHAPE_CONTEXT = {"32b": 4096}          # tokens each request holds when decoding starts, where it is not 2048
+SHAPE_MAX_MODEL_LEN = {"32b": 8192}
 CONTEXT = 2048
 GENERATED = 256
 MAX_MODEL_LEN = 4096
@@ -156,7 +167,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int) -> dict:
   def one():
     extras = Sampler.pack(params, list(range(batch)), [n[0]] * batch)
     items = [StepItem(r, [t], (0,)) for r, t in zip(rids, last)]
-    engine.runner.step_and_sample(items, extras, Sampler.sample, tokens_dev)
+    engine.runner.step_and_sample(items, extras, Sampler.sample, tokens_dev, sampling_pad=Sampler.PAD_ROWS)
     n[0] += 1
 
   for _ in range(max(warmup, 3)):
@@ -292,6 +303,98 @@ def _table_of(prof, steps: int, title: str) -> str:
   return "\n".join(lines)
 
 
+def _kernel_times(fn, steps: int) -> dict:
+  """Kernel name -> microseconds per step, from CUPTI records of `steps` calls of fn."""
+  import torch
+  from torch.profiler import ProfilerActivity, profile
+  with profile(activities=[ProfilerActivity.CUDA]) as prof:
+    for i in range(steps):
+      fn(i)
+    torch.cuda.synchronize()
+  out = {}
+  for ev in prof.key_averages():
+    t = getattr(ev, "device_time_total", 0.0) or getattr(ev, "cuda_time_total", 0.0)
+    if t > 0:
+      out[ev.key] = t / steps
+  return out
+
+
+def _group(times: dict) -> dict:
+  """Sums the kernels of a step by what they do."""
+  import re
+  g = {"own_products": 0.0, "library_products": 0.0, "attention": 0.0, "other": 0.0}
+  for name, us in times.items():
+    if "gemm_skinny" in name or "gemm_tc_kernel" in name:
+      g["own_products"] += us
+    elif re.search(r"decode_tma_kernel|decode_split_kernel|decode_merge|attention_prefill", name):
+      g["attention"] += us
+    elif "anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I):
+      g["library_products"] += us
+    elif not name.startswith("Memcpy") and not name.startswith("Memset"):
+      g["other"] += us
+  return g
+
+
+def kernel_rates(engine, batch: int, cfg: dict, layers: int, pk: dict, steps: int = 4) -> dict:
+  """The dominant kernels of a decode step and of a prefill step with the rates they reach: the products
+  stream every weight once (decode) or do the step's matrix FLOPs (prefill); the attention kernel streams
+  the cache of the live requests (decode) or does the causal attention FLOPs (prefill)."""
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  mb = model_bytes(cfg, layers)
+  rids = fill_context(engine, batch, CONTEXT, seed=1000 + batch)
+  params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+  tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+  def decode(i):
+    extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+    engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev,
+                                  sampling_pad=Sampler.PAD_ROWS)
+
+  for i in range(4):
+    decode(i)
+  torch.cuda.synchronize()
+  d = _group(_kernel_times(lambda i: decode(10 + i), steps))
+  for r in rids:
+    engine.cache.release_request(r)
+  prod_us = d["own_products"] + d["library_products"]
+  kv_bytes = batch * (CONTEXT + 4 + steps / 2.0) * mb["kv_per_token"]
+  out = {"source": f"CUPTI kernel records of {steps} further steps", "decode": {
+    "products": {"us": round(prod_us, 1), "bytes": int(mb["weights"]), "GB/s": round(mb["weights"] / prod_us / 1e3, 1),
+                 "frac": round(mb["weights"] / prod_us / 1e3 / pk["hbm_gbs"], 4), "own_share": round(d["own_products"] / max(prod_us, 1e-9), 3)},
+    "attention": {"us": round(d["attention"], 1), "bytes": int(kv_bytes), "GB/s": round(kv_bytes / d["attention"] / 1e3, 1),
+                  "frac": round(kv_bytes / d["attention"] / 1e3 / pk["hbm_gbs"], 4)},
+    "other_us": round(d["other"], 1)}}
+
+  g = torch.Generator().manual_seed(7)
+  V = engine.model_config.vocab_size
+
+  def whole(i):
+    rid = f"rates{i}"
+    engine.cache.admit(rid)
+    engine.runner.step([StepItem(rid, torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist(), (PREFILL_TOKENS - 1,))])
+    engine.cache.release_request(rid)
+
+  for i in range(2):
+    whole(i)
+  torch.cuda.synchronize()
+  p = _group(_kernel_times(lambda i: whole(10 + i), 2))
+  H, I, Vv = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+  nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+  T = PREFILL_TOKENS
+  gemm_flops = 2.0 * T * ((nh + 2 * nkv) * hd * H + H * nh * hd + 2 * I * H + H * I) * layers + 2.0 * Vv * H
+  attn_flops = layers * 2.0 * 2.0 * nh * hd * (T * (T + 1) / 2)
+  prod_us = p["own_products"] + p["library_products"]
+  out["prefill"] = {
+    "products": {"us": round(prod_us, 1), "TFLOP": round(gemm_flops / 1e12, 4), "TFLOP/s": round(gemm_flops / prod_us / 1e6, 1),
+                 "frac": round(gemm_flops / prod_us / 1e6 / pk["bf16_tflops"], 4), "own_share": round(p["own_products"] / max(prod_us, 1e-9), 3)},
+    "attention": {"us": round(p["attention"], 1), "TFLOP": round(attn_flops / 1e12, 4), "TFLOP/s": round(attn_flops / p["attention"] / 1e6, 1),
+                  "frac": round(attn_flops / p["attention"] / 1e6 / pk["bf16_tflops"], 4)},
+    "other_us": round(p["other"], 1)}
+  return out
+
+
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
   """A continuous batch through `LLMEngine.generate`: prompts of 128 .. 2048 uniform random tokens, `outputs`
   generated tokens each, prompts cut under a budget of 2048 tokens a step.  Run twice; the second run
@@ -340,7 +443,8 @@ def main() -> int:
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")
   ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
-  ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when decoding starts")
+  ap.add_argument("--context", type=int, default=None, help="tokens each request holds when decoding starts (default 2048; 32b: 4096)")
+  ap.add_argument("--skip-kernels", action="store_true", help="leave out the per-kernel rates")
   ap.add_argument("--skip-points", action="store_true")
   ap.add_argument("--mixed", action="store_true",
                   help="run a continuous batch of 64 requests through LLMEngine.generate, print its throughput and exit")
@@ -363,7 +467,8 @@ def main() -> int:
   warmup = max(args.warmup, 3)
   # room for the tokens that the timed steps generate, whatever --steps says
   global GENERATED, MAX_MODEL_LEN
-  CONTEXT = args.context
+  CONTEXT = args.context if args.context is not None else SHAPE_CONTEXT.get(args.shape, CONTEXT)
+  MAX_MODEL_LEN = max(MAX_MODEL_LEN, SHAPE_MAX_MODEL_LEN.get(args.shape, 0))
   GENERATED = max(GENERATED, warmup + args.steps + args.batch * -(-CONTEXT // PREFILL_TOKENS) + 64)
   MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
   cfg["max_position_embeddings"] = max(cfg.get("max_position_embeddings", 0), MAX_MODEL_LEN)
@@ -383,6 +488,7 @@ def main() -> int:
     e2e = time_e2e(engine, args.batch, args.steps, warmup)
     pre = time_prefill(engine)
     clock_info = clocks.stop()
+    rates = None if args.skip_kernels else kernel_rates(engine, args.batch, cfg, args.layers, pk)
     points = {}
     if not args.skip_points:
       for b in (1, 64):
@@ -416,6 +522,7 @@ def main() -> int:
     "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                  "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
     "points": points,
+    "kernels": rates,
     "clocks": clock_info,
   }
   print(json.dumps(line))

@@ -95,3 +95,31 @@ def test_engine_config():
     EngineConfig.from_kwargs("/m", dtype="float16")
   with pytest.raises(TypeError):
     EngineConfig.from_kwargs("/m", max_model_len=5, max_context_len=6)
+
+
+def test_sizes_the_kernels_cannot_take_are_refused_when_the_engine_is_built(tmp_path):
+  """head_dim 6 is a valid Qwen3 configuration for config.json, but no attention kernel takes it; a
+  hidden size of 36 cannot be read 16 bytes at a time in bfloat16.  Both are refused with the
+  offending size in the message when the step function is built, before any step."""
+  import torch
+  from miniinfer_b200.cache import KVCacheManager
+  from miniinfer_b200.config import build_model_spec
+  from miniinfer_b200.config.model_config import Qwen3Config
+  from miniinfer_b200.engine import ModelRunner
+  from tiny_configs import TINY_A
+
+  def runner(cfg, dtype):
+    spec = build_model_spec(Qwen3Config.from_dict(cfg))
+    cache = KVCacheManager(spec.cache_layer_specs(), 16, 4, 2, 64, dtype, "cpu")
+    return ModelRunner(spec, cache, dtype, "cpu")
+
+  with pytest.raises(ValueError, match="head_dim=6"):
+    runner(dict(TINY_A, head_dim=6), torch.float32)
+  with pytest.raises(ValueError, match="head_dim=260"):
+    runner(dict(TINY_A, head_dim=260), torch.bfloat16)
+  with pytest.raises(ValueError, match="hidden_size=36"):
+    runner(dict(TINY_A, hidden_size=36), torch.bfloat16)
+  with pytest.raises(ValueError, match="intermediate_size=100"):
+    runner(dict(TINY_A, intermediate_size=100), torch.bfloat16)
+  runner(dict(TINY_A, hidden_size=36, intermediate_size=100), torch.float32)      # the 32-bit kernels take both
+  runner(dict(TINY_A, head_dim=20), torch.bfloat16)                               # a head size of 20 runs on the general kernel

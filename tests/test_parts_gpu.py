@@ -33,7 +33,7 @@ def context_for(mixers, rope, dtype, T, page_size=16, start=0):
   from miniinfer_b200.models import LayerRun
   blocks = [SimpleNamespace(mixer_part=lambda m=m: m) for m in mixers]
   spec = SimpleNamespace(position_encodings=[rope] if rope else [], run_list=[LayerRun(i) for i in range(len(mixers))],
-                         blocks=blocks, config=SimpleNamespace(vocab_size=10))
+                         blocks=blocks, config=SimpleNamespace(vocab_size=10), all_parts=lambda: list(mixers))
   cache = KVCacheManager([m.cache_spec() for m in mixers], page_size, 40, 2, 512, dtype, DEV)
   runner = ModelRunner(spec, cache, dtype, DEV)
   cache.admit("x")

@@ -20,9 +20,9 @@ V = CFG["vocab_size"]
 LENGTHS = (33, 130, 200, 65)
 PAGE = 64
 
-# float32: the bound the engine is built for.  bfloat16: three times the largest difference seen on a B200 for
-# this model over all cuts (0.011: logits of size 3, two layers, every activation rounded to 8 bits of mantissa).
-BOUND = {"float32": 1e-4, "bfloat16": 0.08}
+# float32: the bound the engine is built for (seen on a B200: 1.0e-5).  bfloat16: two and a half times the largest
+# difference seen on a B200 for this model over all cuts (0.0383 among 65 million logits of size up to 3.7: 1 %).
+BOUND = {"float32": 1e-4, "bfloat16": 0.095 if DEV != "cpu" else 0.2}
 
 _made = {}
 

@@ -22,12 +22,19 @@ LENGTHS = {"A": (5, 17, 33, 100, 64, 128, 41, 65), "B": (1, 9, 40, 71, 130, 65, 
            "D": (130, 70, 300, 64, 200, 65, 257), "F": (130, 70, 300, 64, 200, 65, 257)}
 PAGES = {"A": 16, "B": 8, "C": 64, "D": 64, "F": 64}
 
-# float32: the bound the engine is built for.  bfloat16: 8 bits of mantissa; activations are rounded
-# about six times per layer, the errors add like a random walk over at most four layers and the
-# logits are of order one: 5 * sqrt(24) * 2^-9 = 0.05 of the largest logit bounds what rounding can do.
-def tolerance(dtype: str, ref) -> float:
+# float32: the bound the engine is built for.  bfloat16: for each configuration two and a half times the largest
+# difference seen on a B200 over all cuts (whole 0.0029 / 0.0049 / 0.0046 / 0.0041 / 0.0093 for A, B, C, D, F; the other
+# cuts differ from that in the fourth decimal), so that a slip of one layer's cache - which changes logits by
+# tenths - cannot hide under it.  Where the plain implementation's best logit leads the second by more than
+# twice the bound, the engine's arg-max must be the same.
+BF16_BOUND = {"A": 0.0072, "B": 0.0122, "C": 0.0116, "D": 0.0103, "E": None, "F": 0.0232}
+
+
+def tolerance(dtype: str, ref, tag: str = None) -> float:
   if dtype == "float32":
     return 1e-4
+  if BF16_BOUND.get(tag) is not None and DEV != "cpu":      # the bounds are those of the CUDA kernels, not of the CPU statements
+    return BF16_BOUND[tag]
   return 0.05 * max(float(v.abs().max()) for v in ref.values())
 
 
@@ -67,8 +74,9 @@ def test_every_cut_gives_the_plain_logits(model_dirs, dtype, tag, cut):
     trace = {"whole": rc.whole, "tail": rc.tail_one_by_one, "portions": rc.portions}[cut](reqs)
   runner = runner_for(d, dtype, budget, page)
   got = rc.run_in_process(runner, trace)
-  margin = 1e-3 if dtype == "float32" else None
-  worst = rc.compare(got, ref, tolerance(dtype, ref), f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
+  bound = tolerance(dtype, ref, tag)
+  margin = 1e-3 if dtype == "float32" else 2 * bound
+  worst = rc.compare(got, ref, bound, f"{tag}/{dtype}/{cut}", check_argmax_margin=margin)
   rc.log_worst(f"{tag}/{dtype}/{cut}", worst, ref)
   if cut == "preempted":
     second = [k for k in got if len(k) == 3]
@@ -94,11 +102,11 @@ def test_steps_of_more_than_a_thousand_tokens(model_dirs, dtype):
     from miniinfer_b200.kernels import ops
     assert 1400 >= ops.GEMM_TC_MIN_M
   got = rc.run_in_process(runner, rc.whole(reqs))
-  rc.compare(got, ref, tolerance(dtype, ref), f"E/{dtype}/whole")
+  rc.log_worst(f"E/{dtype}/whole", rc.compare(got, ref, tolerance(dtype, ref, "E"), f"E/{dtype}/whole"), ref)
   if dtype == "bfloat16":       # the kernel leaves its status word in the workspace: it has run
     assert ("gemm_tc_status", torch.int32) in runner.runner.ws._bufs
   got = rc.run_in_process(runner, rc.portions(reqs, sizes=(1300, 64, 2, 150)))
-  rc.compare(got, ref, tolerance(dtype, ref), f"E/{dtype}/portions")
+  rc.log_worst(f"E/{dtype}/portions", rc.compare(got, ref, tolerance(dtype, ref, "E"), f"E/{dtype}/portions"), ref)
   runner.runner.check_status()
   runner.cache.check_invariants()
 
@@ -113,9 +121,9 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
   runner = runner_for(d, dtype, 448, 64)
   got = rc.run_in_process(runner, trace)
   assert len(got) == 400
-  rc.compare(got, ref, tolerance(dtype, ref), f"C/{dtype}/decode-400")
+  rc.log_worst(f"C/{dtype}/decode-400", rc.compare(got, ref, tolerance(dtype, ref, "C"), f"C/{dtype}/decode-400"), ref)
   first = {k: v for k, v in got.items() if k[1] < 4}
-  rc.compare(first, ref, tolerance(dtype, ref), f"C/{dtype}/first-tokens")
+  rc.compare(first, ref, tolerance(dtype, ref, "C"), f"C/{dtype}/first-tokens")
 
 
 def test_float32_logits_do_not_depend_on_the_cut_at_all(model_dirs):
@@ -182,4 +190,4 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
     if wanted:
       outputs[r["step"]] = np.fromfile(out / f"{r['step']}.f32", dtype="<f4").reshape(wanted, 256)
   ref = reference(d, "A", reqs)
-  rc.compare(rc.collect(trace, outputs), ref, tolerance(dtype, ref), f"trace_run/{dtype}")
+  rc.compare(rc.collect(trace, outputs), ref, tolerance(dtype, ref, "A"), f"trace_run/{dtype}")
