@@ -25,6 +25,7 @@ One JSON line is printed:
 Qwen3-32B (64 layers, 4096-token contexts, max_model_len 8192).
 """
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -425,11 +426,136 @@ def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> di
   return res
 
 
-def reference_arm() -> int:
-  print(json.dumps({"impl": "reference", "unavailable": (
-    "the reference installs (pip --no-deps into baseline/_ref) but cannot be imported as installed: its pyproject "
-    "places the sub-packages at top level without a 'miniinfer' package and leaves out kernels/, and its engine needs "
-    "a tokenizer and a checkpoint from the hub, which cannot be fetched offline")}))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _write_reference_model(cfg: dict, out_dir: str, seed: int = 0) -> None:
+  """A model folder the reference can load, made without this repository's package: config.json,
+  model.safetensors with the tensor names of the Qwen3 checkpoints (random N(0, 0.02) matrices, norm
+  weights near one) and a word-level tokenizer of the configuration's vocabulary size."""
+  import torch
+  from safetensors.torch import save_file
+  from tokenizers import Tokenizer, models, pre_tokenizers
+  os.makedirs(out_dir, exist_ok=True)
+  with open(os.path.join(out_dir, "config.json"), "w") as f:
+    json.dump(dict(cfg, torch_dtype="bfloat16", hidden_act="silu", attention_bias=False, use_sliding_window=False,
+                   bos_token_id=0, eos_token_id=1), f)
+  g = torch.Generator().manual_seed(seed)
+  H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+  nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+  mat = lambda *s: (torch.randn(*s, generator=g) * 0.02).to(torch.bfloat16)
+  vec = lambda n: (1 + 0.1 * torch.randn(n, generator=g)).to(torch.bfloat16)
+  sd = {"model.embed_tokens.weight": mat(V, H), "model.norm.weight": vec(H)}
+  for i in range(cfg["num_hidden_layers"]):
+    p = f"model.layers.{i}"
+    sd.update({f"{p}.input_layernorm.weight": vec(H), f"{p}.post_attention_layernorm.weight": vec(H),
+               f"{p}.self_attn.q_proj.weight": mat(nh * hd, H), f"{p}.self_attn.k_proj.weight": mat(nkv * hd, H),
+               f"{p}.self_attn.v_proj.weight": mat(nkv * hd, H), f"{p}.self_attn.o_proj.weight": mat(H, nh * hd),
+               f"{p}.self_attn.q_norm.weight": vec(hd), f"{p}.self_attn.k_norm.weight": vec(hd),
+               f"{p}.mlp.gate_proj.weight": mat(I, H), f"{p}.mlp.up_proj.weight": mat(I, H), f"{p}.mlp.down_proj.weight": mat(H, I)})
+  if not cfg.get("tie_word_embeddings"):
+    sd["lm_head.weight"] = mat(V, H)
+  save_file(sd, os.path.join(out_dir, "model.safetensors"))
+  vocab = {"<bos>": 0, "<eos>": 1, "<unk>": 2}
+  for i in range(3, V):
+    vocab[f"t{i}"] = i
+  tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+  tok.pre_tokenizer = pre_tokenizers.Whitespace()
+  tok.save(os.path.join(out_dir, "tokenizer.json"))
+  with open(os.path.join(out_dir, "tokenizer_config.json"), "w") as f:
+    json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "bos_token": "<bos>", "eos_token": "<eos>", "unk_token": "<unk>",
+               "pad_token": "<eos>", "model_max_length": cfg["max_position_embeddings"]}, f)
+
+
+def reference_child(args) -> int:
+  """Runs in a process of its own, with nothing of this repository's package imported: the reference as
+  installed under baseline/_ref (its sub-packages lie there at top level, so the name ``miniinfer`` is
+  bound to that folder), its own ``LLMEngine.generate`` with token-id prompts, as its benchmark does
+  (benchmark/bench_miniinfer.py:28-58).  Decode tokens a second: two runs that differ only in the number
+  of generated tokens, (tokens of the longer - tokens of the shorter) / (time of the longer - the shorter)."""
+  import types
+  pkg = types.ModuleType("miniinfer")
+  pkg.__path__ = [REF_DIR]
+  sys.modules["miniinfer"] = pkg
+  sys.path.insert(0, REF_DIR)
+  os.environ.update(HF_HUB_OFFLINE="1", TRANSFORMERS_OFFLINE="1")
+  import torch
+  from miniinfer.engine.llm_engine import LLMEngine
+  from miniinfer.utils.sampling_params import SamplingParams
+  cfg = dict(MODEL, **SHAPES[args.shape])
+  if args.layers:
+    cfg["num_hidden_layers"] = args.layers
+  context = args.context if args.context is not None else SHAPE_CONTEXT.get(args.shape, CONTEXT)
+  steps, warmup, batch = args.steps, max(args.warmup, 3), args.batch
+  with tempfile.TemporaryDirectory() as d:
+    _write_reference_model(cfg, d)
+    # no dtype is passed: the reference's engine builds its model in float16 whatever it is asked for
+    # (miniinfer/engine/model_runner.py:66-68, models/fused_qwen3.py:272), and its cache must match
+    engine = LLMEngine(model=d, use_multiprocess=False, max_num_seqs=max(batch, 8),
+                       max_context_len=max(MAX_MODEL_LEN, SHAPE_MAX_MODEL_LEN.get(args.shape, 0)), page_size=PAGE * 4,
+                       enable_prefix_cache=False, debug=False)
+    engine.start()
+    g = torch.Generator().manual_seed(1)
+    V = cfg["vocab_size"]
+
+    def run(n_tokens: int) -> float:
+      prompts = [torch.randint(3, V, (context,), generator=g).tolist() for _ in range(batch)]
+      sp = SamplingParams(temperature=0.6, ignore_eos=True, max_tokens=n_tokens)
+      torch.cuda.synchronize()
+      t0 = time.perf_counter()
+      outs = engine.generate(prompts=prompts, sampling_params=sp, use_tqdm=False)
+      torch.cuda.synchronize()
+      dt = time.perf_counter() - t0
+      assert all(len(o["token_ids"]) == n_tokens for o in outs), "the reference generated another number of tokens"
+      return dt
+
+    run(warmup + 4)                      # loads kernels, records its CUDA graphs
+    clocks = ClockSampler()
+    clocks.start()
+    short = min(run(4) for _ in range(2))
+    long_ = min(run(4 + steps) for _ in range(2))
+    clock_info = clocks.stop()
+    engine.stop()
+  ms = 1000.0 * (long_ - short) / steps
+  value = batch * 1000.0 / ms
+  print(json.dumps({
+    "metric": f"decode tok/s at batch {batch} (Qwen3-{args.shape.upper()} shape, {context}-token contexts)",
+    "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+    "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (the reference's own; same width as bf16)", "impl": "reference",
+    "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
+    "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": cfg["num_hidden_layers"], "global_batch": batch, "seq_len": context,
+               "page_size": PAGE * 4, "attention_backend": "the reference's default", "parallelism": "single GPU",
+               "timing": "LLMEngine.generate end to end, host tokens in and out; (time of 4+K tokens - time of 4 tokens) / K"},
+    "e2e": {"value": round(value, 1), "unit": "tok/s", "ms_per_step": round(ms, 4)},
+    "clocks": clock_info}))
+  return 0
+
+
+def reference_arm(args) -> int:
+  """The reference's own engine on the same shape, batch, context and step count, in a child process.
+  If it cannot be imported or run, one line says which import or call failed."""
+  if not os.path.isdir(REF_DIR):
+    print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref does not exist: the reference was not installed here"}))
+    return 0
+  cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-child", "--steps", str(args.steps), "--warmup", str(args.warmup),
+         "--batch", str(args.batch), "--shape", args.shape]
+  if args.layers:
+    cmd += ["--layers", str(args.layers)]
+  if args.context is not None:
+    cmd += ["--context", str(args.context)]
+  try:
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+  except subprocess.TimeoutExpired:
+    print(json.dumps({"impl": "reference", "unavailable": "the reference's engine did not finish within 25 minutes"}))
+    return 0
+  lines = [l for l in proc.stdout.splitlines() if l.startswith("{") and '"impl": "reference"' in l]
+  if proc.returncode == 0 and lines:
+    print(lines[-1])
+    return 0
+  err = [l.strip() for l in (proc.stderr or "").splitlines() if l.strip()]
+  why = err[-1] if err else f"exit code {proc.returncode} without a message"
+  where = next((l for l in reversed(err) if l.startswith("File ") and "_ref" in l), "")
+  print(json.dumps({"impl": "reference", "unavailable": f"the reference's own code failed: {why[:300]} {where[:200]}".strip()}))
   return 0
 
 
@@ -439,7 +565,7 @@ def main() -> int:
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child"])
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")
   ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
@@ -452,7 +578,9 @@ def main() -> int:
                   help="print the device time of each kernel of a decode step (default) or a prefill step and exit")
   args = ap.parse_args()
   if args.impl == "reference":
-    return reference_arm()
+    return reference_arm(args)
+  if args.impl == "reference-child":
+    return reference_child(args)
   MODEL.update(SHAPES[args.shape])
   shape_name = f"Qwen3-{args.shape.upper()} shape"
   if args.layers is None:
@@ -492,7 +620,9 @@ def main() -> int:
     points = {}
     if not args.skip_points:
       for b in (1, 64):
+        engine.stop()
         del engine
+        gc.collect()
         torch.cuda.empty_cache()
         engine = build_engine(d, b)
         points[f"decode_b{b}"] = round(time_decode(engine, b, args.steps, warmup)["tok_s"], 1)
@@ -502,7 +632,7 @@ def main() -> int:
   achieved = step_bytes / (dec["ms"] * 1e-3) / 1e9
   flops = prefill_flops(cfg, args.layers, PREFILL_TOKENS)
   line = {
-    "metric": f"decode tok/s at batch {args.batch} ({shape_name}, {CONTEXT}-token contexts, bf16)",
+    "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.shape.upper()} shape, {CONTEXT}-token contexts)",
     "value": round(dec["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
     "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
     "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids", "impl": "ours",

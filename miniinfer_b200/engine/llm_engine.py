@@ -111,7 +111,11 @@ class LLMEngine:
     return self
 
   def stop(self) -> None:
-    pass
+    """Lets go of what the kernel wrappers keep per weight and cache tensor, so that this engine's memory
+    is free once the engine itself is dropped (the reference's stop ends its worker processes,
+    miniinfer/engine/llm_engine.py:1284-1299; this engine has none)."""
+    from ..kernels import ops
+    ops.forget_tensors()
 
   def __enter__(self) -> "LLMEngine":
     return self.start()

@@ -497,6 +497,14 @@ def _qkv_tensor_map(lib, qkv: torch.Tensor):
   return m
 
 
+def forget_tensors() -> None:
+  """Drops what this module keeps per tensor address (transposed views of weights, TMA descriptors of cache
+  layers and QKV buffers).  The views keep the weights' memory alive: an engine that is done calls this so
+  that its memory can go back to the device."""
+  _transposed_views.clear()
+  _tensor_maps.clear()
+
+
 def device_status(ws) -> int:
   """The status words that kernels with bounded waits set when a wait ran out (0: all well)."""
   code = 0
