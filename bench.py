@@ -361,7 +361,7 @@ def kernel_rates(engine, batch: int, cfg: dict, layers: int, pk: dict, steps: in
     engine.cache.release_request(r)
   prod_us = d["own_products"] + d["library_products"]
   kv_bytes = batch * (CONTEXT + 4 + steps / 2.0) * mb["kv_per_token"]
-  out = {"source": f"CUPTI kernel records of {steps} further steps", "decode": {
+  out = {"source": f"CUPTI kernel records of {steps} further steps in a process of its own, dependent launch off", "decode": {
     "products": {"us": round(prod_us, 1), "bytes": int(mb["weights"]), "GB/s": round(mb["weights"] / prod_us / 1e3, 1),
                  "frac": round(mb["weights"] / prod_us / 1e3 / pk["hbm_gbs"], 4), "own_share": round(d["own_products"] / max(prod_us, 1e-9), 3)},
     "attention": {"us": round(d["attention"], 1), "bytes": int(kv_bytes), "GB/s": round(kv_bytes / d["attention"] / 1e3, 1),
@@ -565,7 +565,7 @@ def main() -> int:
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child"])
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child"])
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")
   ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
@@ -609,6 +609,9 @@ def main() -> int:
     if args.kernel_table:
       print(kernel_table(build_engine(d, args.batch), args.batch, mode=args.kernel_table))
       return 0
+    if args.impl == "kernels-child":
+      print(json.dumps({"kernels": kernel_rates(build_engine(d, args.batch), args.batch, cfg, args.layers, pk)}))
+      return 0
     clocks = ClockSampler()
     engine = build_engine(d, args.batch)
     clocks.start()
@@ -616,7 +619,6 @@ def main() -> int:
     e2e = time_e2e(engine, args.batch, args.steps, warmup)
     pre = time_prefill(engine)
     clock_info = clocks.stop()
-    rates = None if args.skip_kernels else kernel_rates(engine, args.batch, cfg, args.layers, pk)
     points = {}
     if not args.skip_points:
       for b in (1, 64):
@@ -626,6 +628,20 @@ def main() -> int:
         torch.cuda.empty_cache()
         engine = build_engine(d, b)
         points[f"decode_b{b}"] = round(time_decode(engine, b, args.steps, warmup)["tok_s"], 1)
+
+    # Per-kernel times come from a process of its own with dependent launch off: with it on, a kernel is placed
+    # while its predecessor runs and the time it spends waiting there would count as its own.
+    rates = None
+    if not args.skip_kernels:
+      engine.stop()
+      del engine
+      gc.collect()
+      torch.cuda.empty_cache()
+      cmd = [sys.executable, os.path.abspath(__file__), "--impl", "kernels-child", "--shape", args.shape, "--batch", str(args.batch),
+             "--layers", str(args.layers), "--context", str(CONTEXT)]
+      proc = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ, MINIINFER_B200_PDL="0"))
+      found = [l for l in proc.stdout.splitlines() if l.startswith('{"kernels"')]
+      rates = json.loads(found[-1])["kernels"] if found else {"unavailable": (proc.stderr or "no output").strip().splitlines()[-1][:200]}
 
   mb = model_bytes(cfg, args.layers)
   step_bytes = mb["weights"] + args.batch * dec["mean_ctx"] * mb["kv_per_token"]

@@ -29,7 +29,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-Xptxas", "-v"]
 
-COMMON_SOURCES = ["common.cu", "embedding.cu", "norm.cu", "gemm_f32.cu", "gemm_skinny.cu",
+COMMON_SOURCES = ["common.cu", "embedding.cu", "norm.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_skinny_fused.cu",
                   "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu", "gemm_cublas.cu", "gemm_tc.cu"]
 COMMON_LIBS = ["cublas"]
 ATTENTION_SOURCES = ["attention_prefill.cu", "attention_decode.cu", "attention_decode_tma.cu", "attention_prefill_tc.cu"]
@@ -68,9 +68,26 @@ def build_dir() -> str:
     return alt
 
 
+def _with_headers(sources: Sequence[str]) -> List[str]:
+  """The sources and the headers of this folder that they include, directly or through one another."""
+  seen: List[str] = []
+  todo = list(sources)
+  while todo:
+    name = todo.pop()
+    if name in seen or not os.path.exists(os.path.join(CSRC, name)):
+      continue
+    seen.append(name)
+    with open(os.path.join(CSRC, name), "r", encoding="utf-8") as f:
+      for line in f:
+        line = line.strip()
+        if line.startswith("#include \""):
+          todo.append(line.split("\"")[1])
+  return sorted(seen)
+
+
 def _digest(sources: Sequence[str], defines: Dict[str, str]) -> str:
   h = hashlib.sha256()
-  names = sorted(set(list(sources) + [f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]))
+  names = _with_headers(sources)
   for name in names:
     h.update(name.encode())
     with open(os.path.join(CSRC, name), "rb") as f:

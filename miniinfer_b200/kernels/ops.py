@@ -226,6 +226,45 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
                                         _stream()))
 
 
+def fuses_few_rows(x_rows: int, dtype: torch.dtype) -> bool:
+  """Whether a step of ``x_rows`` rows takes the few-row products with the norm and the residual add fused to them."""
+  return dtype == torch.bfloat16 and 0 < x_rows <= SKINNY_BEST_M and os.environ.get("MINIINFER_B200_FUSE_FEW_ROWS", "1") != "0"
+
+
+def linear_normed(out: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor) -> None:
+  """out[M, N] = rmsnorm(resid)[M, K] @ w[N, K]^T for up to 16 rows: the norm in the product's prologue.
+  resid float32, w and out bfloat16; the normalised rows are rounded to bfloat16 once, as ``add_rmsnorm`` rounds them."""
+  M, K = resid.shape
+  N = w.shape[0]
+  if w.shape[1] != K or out.shape != (M, N) or norm_weight.shape != (K,):
+    raise KernelError(f"linear_normed: shapes do not match: resid {tuple(resid.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  lib = common_lib()
+  _check(lib, lib.mi_gemm_skinny_norm_bf16(_ptr(out, torch.bfloat16), _ptr(resid, torch.float32), _ptr(norm_weight, torch.float32),
+                                           ctypes.c_float(eps), _ptr(w, torch.bfloat16), M, N, K, N, _stream()))
+
+
+def linear_swiglu_normed(out: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor) -> None:
+  """out[M, I] = silu(n @ w[:I]^T) * (n @ w[I:]^T) with n = rmsnorm(resid), for up to 16 rows, in one kernel."""
+  M, K = resid.shape
+  I = out.shape[1]
+  if w.shape != (2 * I, K) or out.shape[0] != M or norm_weight.shape != (K,):
+    raise KernelError(f"linear_swiglu_normed: shapes do not match: resid {tuple(resid.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  lib = common_lib()
+  _check(lib, lib.mi_gemm_skinny_norm_swiglu_bf16(_ptr(out, torch.bfloat16), _ptr(resid, torch.float32), _ptr(norm_weight, torch.float32),
+                                                  ctypes.c_float(eps), _ptr(w, torch.bfloat16), M, I, K, I, _stream()))
+
+
+def linear_add(resid: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+  """resid[M, N] += bfloat16(x[M, K] @ w[N, K]^T) for up to 16 rows: the residual add in the product's epilogue.
+  The product is rounded to bfloat16 before it is added, as it is when a bfloat16 product is handed to ``add_rmsnorm``."""
+  M, K = x.shape
+  N = w.shape[0]
+  if w.shape[1] != K or resid.shape != (M, N):
+    raise KernelError(f"linear_add: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, resid {tuple(resid.shape)}")
+  lib = common_lib()
+  _check(lib, lib.mi_gemm_skinny_add_f32(_ptr(resid, torch.float32), _ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), M, N, K, N, _stream()))
+
+
 def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
                        cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
                        slot_mapping: Optional[torch.Tensor], kv_layer: Optional[torch.Tensor],

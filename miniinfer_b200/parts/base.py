@@ -145,6 +145,11 @@ class Part:
 
 
 class Norm(Part):
+  def as_rms(self) -> Optional[Tuple[torch.Tensor, float]]:
+    """(weight, eps) if this norm is a plain RMSNorm, ``weight * x * rsqrt(mean(x^2) + eps)``, which a part
+    that follows it may then compute itself (``takes_residual``); None otherwise."""
+    return None
+
   def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
     raise NotImplementedError
 
@@ -174,9 +179,26 @@ class Mixer(Part):
   def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
     raise NotImplementedError
 
+  def takes_residual(self, norm: "Norm", ctx) -> bool:
+    """Whether, for this step, the mixer would rather work on the residual stream itself: apply ``norm``
+    in its first kernel and add its output into the residual in its last (``forward_on_residual``).  An
+    option a part may offer where it saves launches; the default is the plain ``forward``."""
+    return False
+
+  def forward_on_residual(self, resid: torch.Tensor, norm: "Norm", ctx, cache) -> None:
+    """resid += mixer(norm(resid)), in place."""
+    raise NotImplementedError
+
 
 class FeedForward(Part):
   def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+  def takes_residual(self, norm: "Norm", ctx) -> bool:
+    return False
+
+  def forward_on_residual(self, resid: torch.Tensor, norm: "Norm", ctx) -> None:
+    """resid += feed_forward(norm(resid)), in place."""
     raise NotImplementedError
 
 

@@ -30,7 +30,16 @@ class PreNormBlock(Block):
     return self.mixer
 
   def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx, cache) -> Optional[torch.Tensor]:
-    x = self.mixer_norm.add_norm(resid, pending, ctx)
-    a = self.mixer.forward(x, ctx, cache)
+    # A part may offer to work on the residual stream itself - its norm in its first kernel, the add of its
+    # output in its last (for a step of few rows: fewer launches).  Then nothing is pending behind it.
+    if pending is None and self.mixer.takes_residual(self.mixer_norm, ctx):
+      self.mixer.forward_on_residual(resid, self.mixer_norm, ctx, cache)
+      a = None
+    else:
+      x = self.mixer_norm.add_norm(resid, pending, ctx)
+      a = self.mixer.forward(x, ctx, cache)
+    if a is None and self.ffn.takes_residual(self.ffn_norm, ctx):
+      self.ffn.forward_on_residual(resid, self.ffn_norm, ctx)
+      return None
     x = self.ffn_norm.add_norm(resid, a, ctx)
     return self.ffn.forward(x, ctx)

@@ -34,6 +34,16 @@ class SwiGLUFeedForward(FeedForward):
         if k % 8:
           raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
 
+  def takes_residual(self, norm, ctx) -> bool:
+    return norm.as_rms() is not None and ops.fuses_few_rows(ctx.num_tokens, ctx.dtype)
+
+  def forward_on_residual(self, resid: torch.Tensor, norm, ctx) -> None:
+    """Two kernels: norm + gate-and-up product + SwiGLU, then the down product + residual add."""
+    weight, eps = norm.as_rms()
+    act = ctx.ws.buffer("ffn_act", (resid.shape[0], self.intermediate_size), ctx.dtype)
+    ops.linear_swiglu_normed(act, resid, weight, eps, self.gate_up)
+    ops.linear_add(resid, act, self.down)
+
   def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
     T = x.shape[0]
     act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)

@@ -119,13 +119,34 @@ class AttentionMixer(Mixer):
       ctx.shared["attention_batch"] = batch
     return batch
 
+  def takes_residual(self, norm, ctx) -> bool:
+    return norm.as_rms() is not None and ops.fuses_few_rows(ctx.num_tokens, ctx.dtype)
+
+  def forward_on_residual(self, resid: torch.Tensor, norm, ctx, cache) -> None:
+    """The norm in the QKV product's prologue, the residual add in the output product's epilogue."""
+    weight, eps = norm.as_rms()
+    nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+    qkv = ctx.ws.buffer("qkv", (resid.shape[0], (nh + 2 * nkv) * hd), ctx.dtype)
+    ops.linear_normed(qkv, resid, weight, eps, self.qkv)
+    attn = self._attend(qkv, ctx, cache)
+    ops.linear_add(resid, attn, self.o)
+
   def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
     T = x.shape[0]
     nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
-    if cache.kind != "paged":
-      raise RuntimeError(f"{self.name}: attention needs a paged cache, got {cache.kind!r}")
     qkv = ctx.ws.buffer("qkv", (T, (nh + 2 * nkv) * hd), ctx.dtype)
     ops.linear(qkv, x, self.qkv)
+    attn = self._attend(qkv, ctx, cache)
+    out = ctx.ws.buffer("mixer_out", (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, attn, self.o)
+    return out
+
+  def _attend(self, qkv: torch.Tensor, ctx, cache) -> torch.Tensor:
+    """From the fused QKV rows to the attention output rows: QK norm, rotation, cache store, attention."""
+    T = qkv.shape[0]
+    nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+    if cache.kind != "paged":
+      raise RuntimeError(f"{self.name}: attention needs a paged cache, got {cache.kind!r}")
     table = self.position.rotary_table() if self.position is not None else None
     qn = self.q_norm if self.qk_norm_eps is not None else None
     kn = self.k_norm if self.qk_norm_eps is not None else None
@@ -136,6 +157,4 @@ class AttentionMixer(Mixer):
     attn = ctx.ws.buffer("attn_out", (T, nh * hd), ctx.dtype)
     ops.attention(attn, qkv, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), nh, nkv, hd,
                   self.scale, self.window)
-    out = ctx.ws.buffer("mixer_out", (T, self.hidden_size), ctx.dtype)
-    ops.linear(out, attn, self.o)
-    return out
+    return attn

@@ -24,6 +24,9 @@ class RMSNorm(Norm):
   def param_specs(self) -> Dict[str, ParamSpec]:
     return {"weight": ParamSpec((self.dim,), "vector", [whole(f"{self.name}.weight", (self.dim,))], init="ones_noise")}
 
+  def as_rms(self):
+    return self.weight, self.eps
+
   def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
     out = ctx.ws.buffer("normed", (resid.shape[0], self.dim), ctx.dtype)
     ops.add_rmsnorm(out, resid, delta, self.weight, self.eps, None, True)

@@ -316,6 +316,70 @@ def test_linear_swiglu(ops, I, K):
   assert torch.allclose(out32, torch.nn.functional.silu(g[:, :I]) * g[:, I:], atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("N,K", [(24, 64), (4096, 1024), (1000, 136), (1024, 3072), (6144, 4096), (5000, 520), (8, 8)])
+def test_few_row_products_with_the_norm_and_the_residual_add_fused(ops, N, K):
+  """The decode step's fused products against their statements (norm kernel, then product; product, then
+  add): the values agree to bfloat16 rounding, a row's value does not depend on the other rows, and the
+  residual rows beyond M are not touched."""
+  w = rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+  wn = 1 + 0.1 * rnd(K, seed=3)
+  resid_k = rnd(16, K, seed=4, scale=2.0)
+  xs = rnd(16, K, dtype=torch.bfloat16, seed=1)
+  first_norm = first_add = None
+  for M in (16, 8, 1, 5, 11):
+    # norm in the prologue
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    want = torch.empty_like(out)
+    ops.linear_normed(out, resid_k[:M].contiguous(), wn, 1e-6, w)
+    ref.linear_normed(want, resid_k[:M].contiguous(), wn, 1e-6, w)
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), ("norm", M, err)
+    if first_norm is None:
+      first_norm = out
+    else:
+      assert torch.equal(out, first_norm[:M]), "a row's value must not depend on the other rows"
+    # against the unfused kernels: the same products of the same rounded activations
+    normed = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(normed, resid_k[:M].clone(), None, wn, 1e-6, None, False)
+    two = torch.empty_like(out)
+    ops.linear(two, normed, w)
+    assert (out.float() - two.float()).abs().max().item() <= 1e-2 * max(1.0, want.float().abs().max().item())
+    # residual add in the epilogue
+    resid = rnd(16, N, seed=6)
+    got = resid.clone()
+    ops.linear_add(got[:M], xs[:M].contiguous(), w)
+    want32 = resid.clone()
+    ref.linear_add(want32[:M], xs[:M].contiguous(), w)
+    assert torch.equal(got[M:], resid[M:])
+    scale = max(1.0, (xs[:M].float() @ w.float().t()).abs().max().item())
+    assert (got - want32).abs().max().item() <= 1e-2 * scale, ("add", M)
+    if first_add is None:
+      first_add = got
+    else:
+      assert torch.equal(got[:M], first_add[:M])
+
+
+@pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (12288, 4096), (7, 8)])
+def test_few_row_gate_and_up_product_with_the_norm_fused(ops, I, K):
+  w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.08)
+  wn = 1 + 0.1 * rnd(K, seed=3)
+  resid = rnd(16, K, seed=4, scale=2.0)
+  first = None
+  for M in (16, 8, 3):
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    want = torch.empty_like(out)
+    ops.linear_swiglu_normed(out, resid[:M].contiguous(), wn, 1e-5, w)
+    ref.linear_swiglu_normed(want, resid[:M].contiguous(), wn, 1e-5, w)
+    err = (out.float() - want.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), (M, err)
+    if first is None:
+      first = out
+    else:
+      assert torch.equal(out, first[:M])
+  with pytest.raises(ops.KernelError, match="0..16"):
+    ops.linear_swiglu_normed(torch.empty(17, I, dtype=torch.bfloat16, device=DEV), rnd(17, K), wn, 1e-5, w)
+
+
 @pytest.mark.parametrize("mode", ["2", "1"])          # blocks in pairs, blocks alone
 @pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (200, 72), (128, 4096)])
 def test_linear_swiglu_many_rows(ops, I, K, mode, monkeypatch):

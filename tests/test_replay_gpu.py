@@ -103,7 +103,7 @@ def test_steps_of_more_than_a_thousand_tokens(model_dirs, dtype):
     assert 1400 >= ops.GEMM_TC_MIN_M
   got = rc.run_in_process(runner, rc.whole(reqs))
   rc.log_worst(f"E/{dtype}/whole", rc.compare(got, ref, tolerance(dtype, ref, "E"), f"E/{dtype}/whole"), ref)
-  if dtype == "bfloat16":       # the kernel leaves its status word in the workspace: it has run
+  if dtype == "bfloat16" and DEV != "cpu":       # the kernel leaves its status word in the workspace: it has run
     assert ("gemm_tc_status", torch.int32) in runner.runner.ws._bufs
   got = rc.run_in_process(runner, rc.portions(reqs, sizes=(1300, 64, 2, 150)))
   rc.log_worst(f"E/{dtype}/portions", rc.compare(got, ref, tolerance(dtype, ref, "E"), f"E/{dtype}/portions"), ref)

@@ -39,6 +39,23 @@ def linear(out, x, w, force_skinny=False):
   out.copy_((x.float() @ w.float().t()).to(out.dtype))
 
 
+def _rms(resid, weight, eps):
+  x = resid.float()
+  return (weight * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))).to(torch.bfloat16)
+
+
+def linear_normed(out, resid, norm_weight, eps, w):
+  linear(out, _rms(resid, norm_weight, eps), w)
+
+
+def linear_swiglu_normed(out, resid, norm_weight, eps, w):
+  linear_swiglu(out, _rms(resid, norm_weight, eps), w, None)
+
+
+def linear_add(resid, x, w):
+  resid.add_((x.float() @ w.float().t()).to(torch.bfloat16).float())
+
+
 def qk_norm_rope_store(qkv, q_weight, k_weight, cos_sin, positions, slot_mapping, kv_layer,
                        num_heads, num_kv_heads, head_dim, eps):
   T = qkv.shape[0]
@@ -159,5 +176,6 @@ def install(monkeypatch) -> None:
   """Puts the statements above in place of the CUDA kernels (CPU tests of the host-side logic)."""
   from miniinfer_b200.kernels import ops
 
-  for name in ("embedding", "add_rmsnorm", "linear", "linear_swiglu", "qk_norm_rope_store", "attention", "silu_mul", "sample"):
+  for name in ("embedding", "add_rmsnorm", "linear", "linear_swiglu", "qk_norm_rope_store", "attention", "silu_mul", "sample",
+               "linear_normed", "linear_swiglu_normed", "linear_add"):
     monkeypatch.setattr(ops, name, globals()[name])
