@@ -327,7 +327,7 @@ def _group(times: dict) -> dict:
   for name, us in times.items():
     if "gemm_skinny" in name or "gemm_tc_kernel" in name:
       g["own_products"] += us
-    elif re.search(r"decode_tma_kernel|decode_split_kernel|decode_merge|attention_prefill", name):
+    elif re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill", name):
       g["attention"] += us
     elif "anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I):
       g["library_products"] += us

@@ -32,7 +32,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 COMMON_SOURCES = ["common.cu", "embedding.cu", "norm.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_skinny_fused.cu",
                   "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu", "gemm_cublas.cu", "gemm_tc.cu"]
 COMMON_LIBS = ["cublas"]
-ATTENTION_SOURCES = ["attention_prefill.cu", "attention_decode.cu", "attention_decode_tma.cu", "attention_prefill_tc.cu"]
+ATTENTION_SOURCES = ["attention_prefill.cu", "attention_decode.cu", "attention_decode_tma.cu", "attention_prefill_tc.cu",
+                     "attention_decode_cluster.cu"]
 
 _lock = threading.Lock()
 
@@ -156,8 +157,20 @@ def build_attention(head_dim: int) -> str:
   return build_library(f"attn_hd{head_dim}", ATTENTION_SOURCES, {"MI_HEAD_DIM": str(head_dim)})
 
 
-def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 128)) -> List[str]:
+def build_all(head_dims: Sequence[int] = (16, 32, 48, 64, 80, 128, 256), remove_stale: bool = True) -> List[str]:
+  """Builds the common library and the attention library of every head size in ``head_dims``.  Libraries
+  of other source versions (another hash in the name) and their compiler logs are then removed from the
+  build folder, so that it holds one build."""
   paths = [build_common()]
   for hd in head_dims:
     paths.append(build_attention(hd))
+  if remove_stale:
+    keep = {os.path.basename(p)[:-3] for p in paths}
+    bdir = os.path.dirname(paths[0])
+    for name in os.listdir(bdir):
+      if name.startswith("libmi_") and not any(name.startswith(k) for k in keep):
+        try:
+          os.remove(os.path.join(bdir, name))
+        except OSError:
+          pass
   return paths

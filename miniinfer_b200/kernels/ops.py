@@ -227,8 +227,12 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
 
 
 def fuses_few_rows(x_rows: int, dtype: torch.dtype) -> bool:
-  """Whether a step of ``x_rows`` rows takes the few-row products with the norm and the residual add fused to them."""
-  return dtype == torch.bfloat16 and 0 < x_rows <= SKINNY_BEST_M and os.environ.get("MINIINFER_B200_FUSE_FEW_ROWS", "1") != "0"
+  """Whether a step of ``x_rows`` rows takes the few-row products with the norm and the residual add fused to them
+  (six launches per layer instead of eight).  Off unless MINIINFER_B200_FUSE_FEW_ROWS=1: measured on B200 (Qwen3-0.6B
+  shape, decode at batch 8) the fused step takes 1.31 ms against 1.12 ms.  The norm kernels between the products
+  are where, under dependent launch, the next product's blocks get onto the SMs and fetch their weights; a product
+  that follows a product directly finds the SMs' registers taken until its predecessor has ended."""
+  return dtype == torch.bfloat16 and 0 < x_rows <= SKINNY_BEST_M and os.environ.get("MINIINFER_B200_FUSE_FEW_ROWS", "0") == "1"
 
 
 def linear_normed(out: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: torch.Tensor) -> None:
@@ -417,8 +421,6 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
 
 
 DECODE_CHUNKS = (512, 256, 128, 64)
-
-
 def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
   """Keys per block of the cp.async split-KV decode kernel: the longest chunk that still gives every
   SM about two blocks, so that a small batch is spread over the whole GPU."""
@@ -429,6 +431,41 @@ def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim:
     if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
       return c
   return DECODE_CHUNKS[-1]
+
+
+_cluster_fit: Dict[tuple, int] = {}
+
+
+def decode_cluster_size(lib, head_dim: int, num_decode: int, num_kv_heads: int, span: int) -> int:
+  """Blocks per (request, kv head) for the cluster-scheduled decode kernel (attention_decode_cluster.cu), or 0 if
+  the step should take the persistent kernel instead.  The largest cluster (16, 8, 4, 2, 1 blocks) that leaves a
+  block at least one 64-key tile and whose clusters - one per (request, kv head) - can all be on the GPU at once:
+  a second round of clusters would double the kernel's time.  (Measured on B200, 8 kv heads of 128, 2048-token
+  contexts: 1 / 2 / 4 / 8 / 16 requests are fastest with clusters of 8 / 4 / 4 / 2 / 1, which is what this rule
+  picks; decode steps take 0.74 / 0.79 / 0.83 / 0.99 / 1.34 ms against 0.92 / 0.92 / 0.99 / 1.12 / 1.55 ms with
+  the persistent kernel.)  Blocks with more than 64 tiles each, or more (request, kv head) pairs than fit at once,
+  stream better from the persistent kernel, which deals the tiles out evenly over the SMs."""
+  tiles = -(-span // 64) + 1
+
+  def fit(c: int) -> int:
+    key = (head_dim, c, -(-tiles // c))
+    n = _cluster_fit.get(key)
+    if n is None:
+      n = _cluster_fit[key] = int(lib.mi_attention_decode_cluster_fit(c, -(-tiles // c)))
+    return n
+
+  forced = os.environ.get("MINIINFER_B200_DECODE_CLUSTER")
+  if forced is not None:
+    c = int(forced)
+    return c if c and fit(c) > 0 else 0
+  pairs = num_decode * num_kv_heads
+  for c in (16, 8, 4, 2, 1):
+    if c <= tiles and -(-tiles // c) <= DECODE_CLUSTER_MAX_TILES_PER_BLOCK and pairs <= fit(c):
+      return c
+  return 0
+
+
+DECODE_CLUSTER_MAX_TILES_PER_BLOCK = 64
 
 
 def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, win, page_size) -> None:
@@ -459,6 +496,21 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
+    tma_shapes = hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
+    cluster = decode_cluster_size(lib, hd, batch.num_decode, nkv, span) if (tma_shapes and G <= 8) else 0
+    if cluster:
+      if batch.scratch is not None:
+        status = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv + 1, torch.int32)[:1]
+      else:
+        status = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+      _check(lib, lib.mi_attention_decode_cluster(
+        _ptr(out), _ptr(qkv), qkv.shape[1], _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+        _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
+        _ptr(batch.seq_slot, torch.int32), _ptr(status, torch.int32), batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win,
+        cluster, batch.max_ctx_len, _stream()))
+      if batch.scratch is None and int(status[0]) != 0:
+        raise KernelError("attention_decode_cluster: a bounded wait on a copy barrier ran out")
+      return
     # more than 8 query heads per kv head: the TMA kernel would walk an item's tiles twice and hand a stage back only
     # in the second pass, which cannot work once an item has more tiles than there are stages - the cp.async kernel takes those
     use_tma = (hd % 64 == 0 and page_size % 64 == 0 and G <= 8 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0")

@@ -65,6 +65,26 @@ def test_greedy_generation_bfloat16_follows_plain_where_the_choice_is_clear(mode
     assert len(o["token_ids"]) == 8
 
 
+def test_decode_with_the_norm_and_the_residual_add_fused_to_the_products(model_dirs, monkeypatch):
+  """The optional decode path of six launches per layer (MINIINFER_B200_FUSE_FEW_ROWS=1): every token is the
+  plain implementation's greedy choice or within the bfloat16 bound of it, for a model with head size 64
+  (TMA and cluster attention kernels) and one with head size 16."""
+  from miniinfer_b200 import SamplingParams
+  monkeypatch.setenv("MINIINFER_B200_FUSE_FEW_ROWS", "1")
+  for tag, page, bound in (("D", 64, 0.0103), ("A", 16, 0.0072)):
+    d = model_dirs(tag)
+    eng = engine(d, "bfloat16", page_size=page, num_pages=40, max_num_seqs=4, max_model_len=256)
+    prompts = list(rc.make_requests(eng.model_config.vocab_size, (70, 5, 33), seed=3).values())
+    w, c = plain.read_weights(d), plain.read_config(d)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+    launches = eng.runner.last_launches
+    exact = sum(plain.check_greedy_tokens(w, c, p, o["token_ids"], margin=2 * bound) for p, o in zip(prompts, outs))
+    assert exact >= 30
+    if DEV != "cpu":
+      L = eng.model_config.num_hidden_layers
+      assert launches <= 6 * L + 5, launches        # the last step was a decode step: six launches per layer
+
+
 def test_preemption_on_the_gpu_keeps_the_tokens(model_dirs):
   from miniinfer_b200 import SamplingParams
   d = model_dirs("A")

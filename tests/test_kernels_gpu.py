@@ -207,6 +207,25 @@ def test_decode_attention_many_requests_long_contexts_wide_groups(ops, nh, nkv):
   assert (out.float() - want.float()).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, None), (8, 1, 64, None), (3, 3, 128, 700), (4, 2, 256, None)])
+def test_decode_attention_in_clusters(ops, monkeypatch, cluster, nh, nkv, hd, window):
+  """The cluster-scheduled decode kernel at every cluster size, on requests from one token to several
+  thousand: with one block per (request, kv head) a block has far more tiles than its ring has stages, so
+  every stage is used many times; with sixteen most blocks of the short requests have no tile at all."""
+  monkeypatch.setenv("MINIINFER_B200_DECODE_CLUSTER", str(cluster))
+  items = [(3000, 1), (1, 1), (64, 1), (65, 1), (1500, 1), (700, 1), (2049, 1)]
+  qkv, kv, bt, batch = make_attention_case(items, nh, nkv, hd, 64, torch.bfloat16, seed=cluster, num_slots=8)
+  out = torch.full((len(items), nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+  want = torch.empty_like(out)
+  for _ in range(3):                                   # the same launch again: nothing is left behind between launches
+    out.fill_(float("nan"))
+    ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  assert torch.isfinite(out.float()).all()
+  assert (out.float() - want.float()).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
   """Random data would hide a key that is skipped: make one key's score stand out."""
