@@ -439,7 +439,7 @@ _cluster_fit: Dict[tuple, int] = {}
 def decode_cluster_size(lib, head_dim: int, num_decode: int, num_kv_heads: int, span: int) -> int:
   """Blocks per (request, kv head) for the cluster-scheduled decode kernel (attention_decode_cluster.cu), or 0 if
   the step should take the persistent kernel instead.  The largest cluster (16, 8, 4, 2, 1 blocks) that leaves a
-  block at least one 64-key tile and whose clusters - one per (request, kv head) - can all be on the GPU at once:
+  block at least one 64-key tile (6 is tried as well: two requests are a little faster with it) and whose clusters - one per (request, kv head) - can all be on the GPU at once:
   a second round of clusters would double the kernel's time.  (Measured on B200, 8 kv heads of 128, 2048-token
   contexts: 1 / 2 / 4 / 8 / 16 requests are fastest with clusters of 8 / 4 / 4 / 2 / 1, which is what this rule
   picks; decode steps take 0.74 / 0.79 / 0.83 / 0.99 / 1.34 ms against 0.92 / 0.92 / 0.99 / 1.12 / 1.55 ms with
@@ -459,7 +459,7 @@ def decode_cluster_size(lib, head_dim: int, num_decode: int, num_kv_heads: int, 
     c = int(forced)
     return c if c and fit(c) > 0 else 0
   pairs = num_decode * num_kv_heads
-  for c in (16, 8, 4, 2, 1):
+  for c in (16, 8, 6, 4, 2, 1):
     if c <= tiles and -(-tiles // c) <= DECODE_CLUSTER_MAX_TILES_PER_BLOCK and pairs <= fit(c):
       return c
   return 0
