@@ -79,7 +79,7 @@ constexpr int TMEM_COLS = 512;
 // output accumulator (head size columns).
 constexpr int S_COL = 0, O_COL = 256;                  // stream s: S at S_COL + 128 s, O at O_COL + 128 s
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + STREAMS * (TPR + 1)) * BM * sizeof(float);
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float);
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
@@ -228,29 +228,53 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// What a block works on at a time: 128 query rows that share one kv head, and the key tiles they see.
+struct Work {
+  int item, o, head0, kvh, rows_tok, start, p_first, p_last, lo_last, t_begin, n, row0;
+  const int* bt;
+  bool skip;
+};
+
+// Work number w of the step, longest first: all head groups of the last 64-token tile, then of the tile
+// before, ...  (Later tiles of a request see more keys.)
+__device__ __forceinline__ Work work_of(const Args& a, int w) {
+  Work k;
+  const int X = a.nh / a.hpt;
+  const int tile = a.n_tiles - 1 - w / X;
+  k.item = a.tiles[2 * tile];
+  k.o = a.tiles[2 * tile + 1];
+  k.skip = a.hpt == 1 && (k.o & 64);                      // the work of the tile before covers these 64 tokens too
+  const int G = a.nh / a.nkv;
+  k.head0 = (w % X) * a.hpt;
+  k.kvh = k.head0 / G;
+  const int qlen = a.q_len[k.item], ctx = a.ctx_len[k.item];
+  k.start = ctx - qlen;                                   // position of the item's first new token
+  const int tok_per_block = BM / a.hpt;
+  k.rows_tok = min(tok_per_block, qlen - k.o);            // tokens of this work that exist
+  k.p_first = k.start + k.o;
+  k.p_last = k.start + k.o + k.rows_tok - 1;
+  const int lo_first = a.window > 0 ? max(0, k.p_first - a.window + 1) : 0;
+  k.lo_last = a.window > 0 ? max(0, k.p_last - a.window + 1) : 0;
+  k.t_begin = lo_first / BN;
+  k.n = k.p_last / BN - k.t_begin + 1;                    // key tiles to walk
+  k.row0 = a.q_start[k.item] + k.o;                       // the first row in the step
+  k.bt = a.block_table + (size_t)a.seq_slot[k.item] * a.bt_stride;
+  return k;
+}
+
+// The i-th work of block b of `blocks`: the works are dealt out in rounds, back and forth (0 .. blocks-1,
+// then blocks-1 .. 0, ...), so that the block that got the longest work of one round gets the shortest of
+// the next.  Returns -1 past the end.
+__device__ __forceinline__ int nth_work(int i, int b, int blocks, int total) {
+  const int w = i * blocks + ((i & 1) ? blocks - 1 - b : b);
+  return w < total ? w : -1;
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
   mi::grid_dependency_sync();
-  // ---- which rows and which keys (uniform over the block)
-  // Blocks start in the order of x, then y: all heads of the last tile first, then the tile before.
-  // Later tiles of a request see more keys, so the long blocks start first and the short ones fill up.
-  const int tile = a.n_tiles - 1 - (int)blockIdx.y;
-  const int item = a.tiles[2 * tile], o = a.tiles[2 * tile + 1];
-  if (a.hpt == 1 && (o & 64)) return;                     // the block of the tile before covers these 64 tokens too
-  const int G = a.nh / a.nkv;
-  const int head0 = (int)blockIdx.x * a.hpt;
-  const int kvh = head0 / G;
-  const int qlen = a.q_len[item], ctx = a.ctx_len[item];
-  const int start = ctx - qlen;                           // position of the item's first new token
-  const int tok_per_block = BM / a.hpt;
-  const int rows_tok = min(tok_per_block, qlen - o);      // tokens of this block that exist
-  const int p_first = start + o, p_last = start + o + rows_tok - 1;
-  const int lo_first = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
-  const int lo_last = a.window > 0 ? max(0, p_last - a.window + 1) : 0;
-  const int t_begin = lo_first / BN;
-  const int n = p_last / BN - t_begin + 1;                // key tiles to walk
-  const int row0 = a.q_start[item] + o;                   // the block's first row in the step
-  const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
+  const int total_work = (a.nh / a.hpt) * a.n_tiles;
+  const int blocks = (int)gridDim.x, me = (int)blockIdx.x;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -265,15 +289,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   uint64_t* s_full = v_empty + STAGES;                    // [stream]: S of the stream's tile is computed
   uint64_t* p_full = s_full + STREAMS;                    // [stream]: its P is written
   uint64_t* o_full = p_full + STREAMS;                    // [stream]: its P V is added to the output row
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + STREAMS);
+  uint64_t* q_empty = o_full + STREAMS;                   // the work's last S is computed: the Q rows may be replaced
+  uint64_t* o_free = q_empty + 1;                         // the work's output rows are read: the next work's P V may overwrite them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* xch = reinterpret_cast<float*>(bars + 32);       // [stream][2][TPR][BM]: the maxima the threads of a row tell each other
-  float* fin_l = xch + 2 * STREAMS * TPR * BM;            // [stream][TPR][BM]: at the end, each thread's sum
-  float* fin_m = fin_l + STREAMS * TPR * BM;              // [stream][BM]: and each stream's maximum
+  float* fin_l = xch + 2 * STREAMS * TPR * BM;            // [2][stream][TPR][BM]: at the end of a work, each thread's sum
+  float* fin_m = fin_l + 2 * STREAMS * TPR * BM;          // [2][stream][BM]: and each stream's maximum (two works take turns)
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(o_free, SOFTMAX_WARPS * 32);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -294,38 +322,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // A block is persistent: it takes one work after the other.  The barriers' phases run on across works -
+  // every role counts the works (Q), the key tiles (the K / V ring) and each stream's tiles (S, P, O) it has
+  // seen - so the copies of the next work's Q and first keys, and its first S, are under way while the
+  // softmax warps still finish the work before.
   if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
+      int gi = 0, it = 0;                                  // key tiles and works so far
+      for (int i = 0;; ++i) {
+        const int w = nth_work(i, me, blocks, total_work);
+        if (w < 0 || *abort) break;
+        const Work k = work_of(a, w);
+        if (k.skip) continue;
+        mbar_wait(q_empty, (it & 1) ^ 1, abort, a.status);   // the S products of the work before have read the Q rows
+        mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
 #pragma unroll
-      for (int rb = 0; rb < 2; ++rb) {
-        const int head = head0 + (a.hpt == 2 ? rb : 0);
-        const int y = row0 + (a.hpt == 2 ? 0 : 64 * rb);
+        for (int rb = 0; rb < 2; ++rb) {
+          const int head = k.head0 + (a.hpt == 2 ? rb : 0);
+          const int y = k.row0 + (a.hpt == 2 ? 0 : 64 * rb);
 #pragma unroll
-        for (int h = 0; h < NHALF; ++h)
-          tma_load_2d(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
-      }
-      // K of tile i goes first, then V of tile i - 1: S of the next tile never waits for a V copy
-      auto load = [&](int i, bool values) {
-        const int s = i % STAGES;
-        uint64_t* full = values ? &v_full[s] : &k_full[s];
-        mbar_wait(values ? &v_empty[s] : &k_empty[s], ((i / STAGES) & 1) ^ 1, abort, a.status);
-        unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (values ? K_BYTES : 0);
-        mbar_expect_tx(full, (uint32_t)K_BYTES);
-        const int key0 = (t_begin + i) * BN;
-#pragma unroll
-        for (int pg = 0; pg < 2; ++pg) {
-          const int key = key0 + 64 * pg;
-          const int page = bt[min(key / a.page_size, a.bt_stride - 1)];   // past the context: the dummy page, masked below
-          const int y = ((page * 2 + (values ? 1 : 0)) * a.nkv + kvh) * a.page_size + key % a.page_size;
-#pragma unroll
-          for (int h = 0; h < NHALF; ++h) tma_load_2d(dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y, full);
+          for (int h = 0; h < NHALF; ++h)
+            tma_load_2d(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
         }
-      };
-      for (int step = 0; step <= n && !*abort; ++step) {
-        if (step < n) load(step, false);
-        if (step >= 1) load(step - 1, true);
+        // K of tile i goes first, then V of tile i - 1: S of the next tile never waits for a V copy
+        auto load = [&](int li, bool values) {
+          const int g = gi + li;                           // the tile's number among all tiles of this block
+          const int s = g % STAGES;
+          uint64_t* full = values ? &v_full[s] : &k_full[s];
+          mbar_wait(values ? &v_empty[s] : &k_empty[s], ((g / STAGES) & 1) ^ 1, abort, a.status);
+          unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (values ? K_BYTES : 0);
+          mbar_expect_tx(full, (uint32_t)K_BYTES);
+          const int key0 = (k.t_begin + li) * BN;
+#pragma unroll
+          for (int pg = 0; pg < 2; ++pg) {
+            const int key = key0 + 64 * pg;
+            const int page = k.bt[min(key / a.page_size, a.bt_stride - 1)];   // past the context: the dummy page, masked below
+            const int y = ((page * 2 + (values ? 1 : 0)) * a.nkv + k.kvh) * a.page_size + key % a.page_size;
+#pragma unroll
+            for (int h = 0; h < NHALF; ++h) tma_load_2d(dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y, full);
+          }
+        };
+        for (int step = 0; step <= k.n && !*abort; ++step) {
+          if (step < k.n) load(step, false);
+          if (step >= 1) load(step - 1, true);
+        }
+        gi += k.n;
+        ++it;
       }
     }
   } else if (warp == MMA_WARP) {
@@ -334,7 +377,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
       constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
       const uint32_t q_addr = smem_u32(q_s);
-      // Tile j belongs to stream j & 1.  The products of a stream follow each other - S, (softmax,)
+      // Tile j of a work belongs to stream j & 1.  The products of a stream follow each other - S, (softmax,)
       // P V, S of its next tile, ... - and the two streams take turns, so the tensor cores have the
       // products of one stream to do while the softmax warps of the other work.  The tensor cores
       // run the products in the order they are issued: P V of a tile (which reads P from the
@@ -346,38 +389,56 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       // threads wrote P with tcgen05.st - is followed by a fence.
       const uint64_t q_desc = smem_desc(q_addr, 16, 1024);
       auto k_step = [](int ks) { return (uint64_t)((ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2); };
-      auto issue_s = [&](int i, uint32_t ready) {
-        const int s = i % STAGES, b = i & 1;
-        if (!ready) mbar_wait(&k_full[s], (i / STAGES) & 1, abort, a.status);
-        const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES), 16, 1024);
-        const uint32_t d = tmem_base + S_COL + 128 * b;
+      int gi = 0, it = 0;                                  // key tiles and works so far
+      int sb[STREAMS] = {0, 0};                            // tiles of each stream so far
+      for (int i = 0;; ++i) {
+        const int w = nth_work(i, me, blocks, total_work);
+        if (w < 0 || *abort) break;
+        const Work k = work_of(a, w);
+        if (k.skip) continue;
+        const int n = k.n;
+        auto issue_s = [&](int li, uint32_t ready) {
+          const int g = gi + li;
+          const int s = g % STAGES, b = li & 1;
+          if (!ready) mbar_wait(&k_full[s], (g / STAGES) & 1, abort, a.status);
+          const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES), 16, 1024);
+          const uint32_t d = tmem_base + S_COL + 128 * b;
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
-        tc_commit(&s_full[b]);
-        tc_commit(&k_empty[s]);
-      };
-      mbar_wait(q_full, 0, abort, a.status);
-      if (!*abort) issue_s(0, 0u);
-      if (!*abort && n > 1) issue_s(1, 0u);
-      for (int j = 0; j < n && !*abort; ++j) {
-        const int s = j % STAGES, b = j & 1;
-        const uint32_t v_ready = mbar_peek(&v_full[s], (j / STAGES) & 1);
-        const uint32_t k_ready = j + 2 < n ? mbar_peek(&k_full[(j + 2) % STAGES], ((j + 2) / STAGES) & 1) : 1u;
-        mbar_wait(&p_full[b], (j / 2) & 1, abort, a.status);
-        if (!v_ready) mbar_wait(&v_full[s], (j / STAGES) & 1, abort, a.status);
-        if (*abort) break;
-        tc_fence_after();
-        const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
-        const uint32_t p_tmem = tmem_base + S_COL + 128 * b;   // thread `ch` of a row leaves its 64 keys in its first 32 columns
+          for (int ks = 0; ks < HD / 16; ++ks)
+            tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
+          tc_commit(&s_full[b]);
+          tc_commit(&k_empty[s]);
+          if (li == n - 1) tc_commit(q_empty);             // the work's last S: the Q rows are free once it is done
+        };
+        mbar_wait(q_full, it & 1, abort, a.status);
+        if (!*abort) issue_s(0, 0u);
+        if (!*abort && n > 1) issue_s(1, 0u);
+        // the output rows in tensor memory are the work before's until its softmax warps have read them
+        if (it > 0) mbar_wait(o_free, (it - 1) & 1, abort, a.status);
+        for (int j = 0; j < n && !*abort; ++j) {
+          const int g = gi + j;
+          const int s = g % STAGES, b = j & 1;
+          const uint32_t v_ready = mbar_peek(&v_full[s], (g / STAGES) & 1);
+          const uint32_t k_ready = j + 2 < n ? mbar_peek(&k_full[(g + 2) % STAGES], ((g + 2) / STAGES) & 1) : 1u;
+          mbar_wait(&p_full[b], (sb[b] + j / 2) & 1, abort, a.status);
+          if (!v_ready) mbar_wait(&v_full[s], (g / STAGES) & 1, abort, a.status);
+          if (*abort) break;
+          tc_fence_after();
+          const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
+          const uint32_t p_tmem = tmem_base + S_COL + 128 * b;   // thread `ch` of a row leaves its 64 keys in its first 32 columns
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks)                   // 16 keys further: 2048 bytes of V
-          tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(64 * (ks >> 2) + 8 * (ks & 3)),
-                    v_desc + (uint64_t)(ks * (2048 >> 4)), IDESC_PV,
-                    (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over its tiles in tensor memory
-        tc_commit(&o_full[b]);
-        tc_commit(&v_empty[s]);
-        if (j + 2 < n) issue_s(j + 2, k_ready);
+          for (int ks = 0; ks < BN / 16; ++ks)                   // 16 keys further: 2048 bytes of V
+            tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(64 * (ks >> 2) + 8 * (ks & 3)),
+                      v_desc + (uint64_t)(ks * (2048 >> 4)), IDESC_PV,
+                      (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over the work's tiles in tensor memory
+          tc_commit(&o_full[b]);
+          tc_commit(&v_empty[s]);
+          if (j + 2 < n) issue_s(j + 2, k_ready);
+        }
+        gi += n;
+        sb[0] += (n + 1) / 2;
+        sb[1] += n / 2;
+        ++it;
       }
     }
   } else {
@@ -389,13 +450,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     // shared memory, with a barrier of the 64 threads that share the rows.
     const int q = warp & 3, ch = (warp >> 2) & 1, st = warp >> 3;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
-    const int tok = a.hpt == 2 ? (r & 63) : r;
-    const int head = head0 + (a.hpt == 2 ? (r >> 6) : 0);
-    const bool row_valid = tok < rows_tok;
-    const int pos = row_valid ? start + o + tok : p_last;
-    const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;                  // m_run: the maximum the stream's sums are taken against
     const float sc = a.scale_log2;
     auto row_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + st * 4 + q) : "memory"); };
     // o_full of the stream completes once per tile of the stream; every thread takes the phases in
@@ -410,131 +465,155 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     };
     const uint32_t s_addr = t_lane + S_COL + 128 * st + ch * COLS;
     const uint32_t o_addr = t_lane + O_COL + 128 * st + ch * (HD / 2);   // for rescaling: this thread's half of the stream's output row
-    const int n_mine = (n - st + 1) / 2;                   // tiles of this stream
+    int base = 0, it = 0;                                  // tiles of this stream and works so far
 
-    for (int k = 0; k < n_mine; ++k) {
-      const int j = 2 * k + st;
-      const int key0 = (t_begin + j) * BN + ch * COLS;     // first key of this thread's columns
-      const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
-      // (after a wait has run out the loop goes on without waiting, so that the warps of a row
-      // still meet at every row barrier; what it computes then is never stored)
-      mbar_wait(&s_full[st], k & 1, abort, a.status);
-      tc_fence_after();
-      // first pass over this thread's 64 scores: their maximum
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64 links
+    for (int i = 0;; ++i) {
+      const int w = nth_work(i, me, blocks, total_work);
+      if (w < 0) break;
+      const Work wk = work_of(a, w);
+      if (wk.skip) continue;
+      const int n = wk.n, start = wk.start, o = wk.o, rows_tok = wk.rows_tok;
+      const int p_first = wk.p_first, p_last = wk.p_last, lo_last = wk.lo_last, t_begin = wk.t_begin;
+      const int tok = a.hpt == 2 ? (r & 63) : r;
+      const int head = wk.head0 + (a.hpt == 2 ? (r >> 6) : 0);
+      const bool row_valid = tok < rows_tok;
+      const int pos = row_valid ? start + o + tok : p_last;
+      const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+      float m_run = -INFINITY, l_run = 0.f;                // m_run: the maximum the stream's sums are taken against
+      const int n_mine = (n - st + 1) / 2;                 // tiles of this stream
+
+      for (int k = 0; k < n_mine; ++k) {
+        const int j = 2 * k + st;
+        const int kk = base + k;                           // the tile's number among all tiles of this stream and block
+        const int key0 = (t_begin + j) * BN + ch * COLS;   // first key of this thread's columns
+        const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
+        // (after a wait has run out the loop goes on without waiting, so that the warps of a row
+        // still meet at every row barrier; what it computes then is never stored)
+        mbar_wait(&s_full[st], kk & 1, abort, a.status);
+        tc_fence_after();
+        // first pass over this thread's 64 scores: their maximum
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64 links
 #pragma unroll
-      for (int c = 0; c < COLS / 32; ++c) {
-        float v[32];
-        tmem_ld32(v, s_addr + 32 * c);
+        for (int c = 0; c < COLS / 32; ++c) {
+          float v[32];
+          tmem_ld32(v, s_addr + 32 * c);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + 32 * c + i;
-          if (!masked || (key >= lo_r && key <= pos)) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-        }
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      float* my_xch = xch + ((st * 2 + (k & 1)) * TPR) * BM;
-      my_xch[ch * BM + r] = mx;
-      row_sync();
-      mx = fmaxf(mx, my_xch[(ch ^ 1) * BM + r]);
-      // The sums stay relative to the old maximum while the new one is at most 2^8 above it (the
-      // exponentials then stay below 2^8, which float32 sums and bf16 P hold easily); only a larger
-      // move - the first tile, mostly - rescales the sum and the output row in tensor memory.  The
-      // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; both
-      // threads of a row see the same maxima and decide alike.
-      const float m_new = fmaxf(m_run, mx * sc);           // the scale is positive
-      const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
-      if (__any_sync(0xffffffffu, move)) {
-        const float m_next = move ? m_new : m_run;
-        const float m_to = m_next == -INFINITY ? 0.f : m_next;
-        const float alpha = move ? exp2f(m_run - m_to) : 1.f;   // 0 for a row that had no key yet
-        if (k > 0) {
-          wait_o(k - 1);                                   // the stream's products so far are in its output row
-#pragma unroll
-          for (int c = 0; c < HD / 2 / 32; ++c) {
-            float op[32];
-            tmem_ld32(op, o_addr + c * 32);
-            uint32_t w[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(op[i] * alpha);
-            tmem_st32(o_addr + c * 32, w);
+          for (int e = 0; e < 32; ++e) {
+            const int key = key0 + 32 * c + e;
+            if (!masked || (key >= lo_r && key <= pos)) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
-        l_run *= alpha;
-        m_run = m_next;
-      }
-      const float m_use = m_run == -INFINITY ? 0.f : m_run;
-      // exponentials, their sum, and P in bf16 into tensor memory, where the second product reads
-      // its A operand (lane = row, two keys to a column): this thread's 64 keys go to the first 32
-      // of its own 64 columns of S, which it has read
-      // (32 scores at a time: the first 32 are read before P overwrites the first 16 columns, and
-      // the P of the second 32 goes to the columns 16..31, read by then)
-      float part[4] = {0.f, 0.f, 0.f, 0.f};
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float* my_xch = xch + ((st * 2 + (kk & 1)) * TPR) * BM;
+        my_xch[ch * BM + r] = mx;
+        row_sync();
+        mx = fmaxf(mx, my_xch[(ch ^ 1) * BM + r]);
+        // The sums stay relative to the old maximum while the new one is at most 2^8 above it (the
+        // exponentials then stay below 2^8, which float32 sums and bf16 P hold easily); only a larger
+        // move - the first tile, mostly - rescales the sum and the output row in tensor memory.  The
+        // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; both
+        // threads of a row see the same maxima and decide alike.
+        const float m_new = fmaxf(m_run, mx * sc);         // the scale is positive
+        const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
+        if (__any_sync(0xffffffffu, move)) {
+          const float m_next = move ? m_new : m_run;
+          const float m_to = m_next == -INFINITY ? 0.f : m_next;
+          const float alpha = move ? exp2f(m_run - m_to) : 1.f;   // 0 for a row that had no key yet
+          if (k > 0) {
+            wait_o(kk - 1);                                // the stream's products so far are in its output row
 #pragma unroll
-      for (int c = 0; c < COLS / 32; ++c) {
-        float v[32];
-        tmem_ld32(v, s_addr + 32 * c);
-        uint32_t packed[16];
+            for (int c = 0; c < HD / 2 / 32; ++c) {
+              float op[32];
+              tmem_ld32(op, o_addr + c * 32);
+              uint32_t wv[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + 32 * c + i;
-          float x = fmaf(v[i], sc, -m_use);
-          if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
-          float pe;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
-          v[i] = pe;
-          part[i & 3] += pe;
+              for (int e = 0; e < 32; ++e) wv[e] = __float_as_uint(op[e] * alpha);
+              tmem_st32(o_addr + c * 32, wv);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          }
+          l_run *= alpha;
+          m_run = m_next;
         }
+        const float m_use = m_run == -INFINITY ? 0.f : m_run;
+        // exponentials, their sum, and P in bf16 into tensor memory, where the second product reads
+        // its A operand (lane = row, two keys to a column): this thread's 64 keys go to the first 32
+        // of its own 64 columns of S, which it has read
+        // (32 scores at a time: the first 32 are read before P overwrites the first 16 columns, and
+        // the P of the second 32 goes to the columns 16..31, read by then)
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 16; ++i) packed[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-        tmem_st16(s_addr + 16 * c, packed);
+        for (int c = 0; c < COLS / 32; ++c) {
+          float v[32];
+          tmem_ld32(v, s_addr + 32 * c);
+          uint32_t packed[16];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int key = key0 + 32 * c + e;
+            float x = fmaf(v[e], sc, -m_use);
+            if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
+            float pe;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
+            v[e] = pe;
+            part[e & 3] += pe;
+          }
+#pragma unroll
+          for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(v[2 * e], v[2 * e + 1]);
+          tmem_st16(s_addr + 16 * c, packed);
+        }
+        l_run += (part[0] + part[1]) + (part[2] + part[3]);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        // Every phase of o_full is taken no later than one tile after it completes (a waiter two
+        // phases behind would read the parity of the wrong phase).  The product waited for here was
+        // issued a whole tile of the stream ago.
+        if (kk > 0) wait_o(kk - 1);
+        tc_fence_before();
+        mbar_arrive(&p_full[st]);
       }
-      l_run += (part[0] + part[1]) + (part[2] + part[3]);
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      // Every phase of o_full is taken no later than one tile after it completes (a waiter two
-      // phases behind would read the parity of the wrong phase).  The product waited for here was
-      // issued a whole tile of the stream ago.
-      if (k > 0) wait_o(k - 1);
+      if (n_mine > 0) wait_o(base + n_mine - 1);
+      // ---- the two streams' sums are merged: every thread leaves its sum (and the stream's maximum)
+      // in shared memory, all softmax warps meet, and each thread finishes a quarter of the output row
+      float* fl = fin_l + (it & 1) * STREAMS * TPR * BM;
+      float* fm = fin_m + (it & 1) * STREAMS * BM;
+      fl[(st * TPR + ch) * BM + r] = l_run;
+      if (ch == 0) fm[st * BM + r] = m_run;
       tc_fence_before();
-      mbar_arrive(&p_full[st]);
-    }
-    if (n_mine > 0) wait_o(n_mine - 1);
-    // ---- the two streams' sums are merged: every thread leaves its sum (and the stream's maximum)
-    // in shared memory, all softmax warps meet, and each thread finishes a quarter of the output row
-    fin_l[(st * TPR + ch) * BM + r] = l_run;
-    if (ch == 0) fin_m[st * BM + r] = m_run;
-    tc_fence_before();
-    asm volatile("bar.sync 9, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
-    tc_fence_after();
-    const float m0 = fin_m[r], m1 = fin_m[BM + r];
-    const float m_all = fmaxf(m0, m1);
-    const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);     // a stream without tiles, or without a visible key, counts nothing
-    const float w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m_all);
-    const float l_all = (fin_l[r] + fin_l[BM + r]) * w0 + (fin_l[2 * BM + r] + fin_l[3 * BM + r]) * w1;
-    constexpr int OD = HD / 4;                             // output columns of this thread: 32 or 16
-    const int part_no = st * 2 + ch;
-    float o0[OD], o1[OD];
-    const bool has1 = n > 1;                               // the second stream has an output row only if it had a tile
-    tmem_ld(o0, t_lane + O_COL + part_no * OD);
-    if (has1) {
-      tmem_ld(o1, t_lane + O_COL + 128 + part_no * OD);
-    } else {
+      asm volatile("bar.sync 9, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
+      tc_fence_after();
+      const float m0 = fm[r], m1 = fm[BM + r];
+      const float m_all = fmaxf(m0, m1);
+      const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);     // a stream without tiles, or without a visible key, counts nothing
+      const float w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m_all);
+      const float l_all = (fl[r] + fl[BM + r]) * w0 + (fl[2 * BM + r] + fl[3 * BM + r]) * w1;
+      constexpr int OD = HD / 4;                           // output columns of this thread: 32 or 16
+      const int part_no = st * 2 + ch;
+      float o0[OD], o1[OD];
+      const bool has1 = n > 1;                             // the second stream has an output row only if it had a tile
+      tmem_ld(o0, t_lane + O_COL + part_no * OD);
+      if (has1) {
+        tmem_ld(o1, t_lane + O_COL + 128 + part_no * OD);
+      } else {
 #pragma unroll
-      for (int i = 0; i < OD; ++i) o1[i] = 0.f;
-    }
-    if (row_valid && !*abort) {
-      const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(row0 + tok) * a.nh * HD + (size_t)head * HD + part_no * OD;
-#pragma unroll
-      for (int d = 0; d < OD; d += 8) {
-        uint4 w;
-        w.x = pack_bf16(o0[d] * f0 + o1[d] * f1, o0[d + 1] * f0 + o1[d + 1] * f1);
-        w.y = pack_bf16(o0[d + 2] * f0 + o1[d + 2] * f1, o0[d + 3] * f0 + o1[d + 3] * f1);
-        w.z = pack_bf16(o0[d + 4] * f0 + o1[d + 4] * f1, o0[d + 5] * f0 + o1[d + 5] * f1);
-        w.w = pack_bf16(o0[d + 6] * f0 + o1[d + 6] * f1, o0[d + 7] * f0 + o1[d + 7] * f1);
-        *reinterpret_cast<uint4*>(dst + d) = w;
+        for (int e = 0; e < OD; ++e) o1[e] = 0.f;
       }
+      // the output rows are in registers: the next work's products may overwrite them in tensor memory
+      tc_fence_before();
+      mbar_arrive(o_free);
+      if (row_valid && !*abort) {
+        const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
+        __nv_bfloat16* dst = a.out + (size_t)(wk.row0 + tok) * a.nh * HD + (size_t)head * HD + part_no * OD;
+#pragma unroll
+        for (int d = 0; d < OD; d += 8) {
+          uint4 wv;
+          wv.x = pack_bf16(o0[d] * f0 + o1[d] * f1, o0[d + 1] * f0 + o1[d + 1] * f1);
+          wv.y = pack_bf16(o0[d + 2] * f0 + o1[d + 2] * f1, o0[d + 3] * f0 + o1[d + 3] * f1);
+          wv.z = pack_bf16(o0[d + 4] * f0 + o1[d + 4] * f1, o0[d + 5] * f0 + o1[d + 5] * f1);
+          wv.w = pack_bf16(o0[d + 6] * f0 + o1[d + 6] * f1, o0[d + 7] * f0 + o1[d + 7] * f1);
+          *reinterpret_cast<uint4*>(dst + d) = wv;
+        }
+      }
+      base += n_mine;
+      ++it;
     }
   }
   // ---- teardown: every tensor-memory access is done, then the columns go back
@@ -586,7 +665,8 @@ MI_API int mi_qkv_tensor_map(void* out_map, const void* qkv, long long rows, lon
 MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_map, const int* block_table, int bt_stride,
                                    const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
                                    const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
-                                   cudaStream_t stream) {
+                                   int num_sms, cudaStream_t stream) {
+  MI_REQUIRE(num_sms > 0, "attention_prefill_tc: num_sms");
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page_size=%d must be a multiple of 64", page_size);
   MI_REQUIRE(scale > 0.f, "attention_prefill_tc: the scale must be positive");
@@ -614,7 +694,9 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   CUtensorMap qm, km;
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));
-  mi::launch(attention_prefill_tc_kernel, dim3(nh / a.hpt, n_tiles), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
+  // persistent blocks, one per SM (a block takes all of an SM's tensor memory), no more than there is work
+  const int total_work = (nh / a.hpt) * n_tiles;
+  mi::launch(attention_prefill_tc_kernel, dim3(total_work < num_sms ? total_work : num_sms), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
   MI_LAUNCH_OK("attention_prefill_tc");
   return 0;
 }
@@ -624,7 +706,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
 MI_API int mi_attention_prefill_tc_supported() { return 0; }
 MI_API int mi_qkv_tensor_map(void*, const void*, long long, long long) { return mi_fail("qkv_tensor_map: head size %d has no tcgen05 kernel", MI_HEAD_DIM); }
 MI_API int mi_attention_prefill_tc(void*, const void*, const void*, const int*, int, const int*, int, const int*, const int*, const int*,
-                                   const int*, int*, int, int, int, float, int, cudaStream_t) {
+                                   const int*, int*, int, int, int, float, int, int, cudaStream_t) {
   return mi_fail("attention_prefill_tc: head size %d has no tcgen05 kernel", MI_HEAD_DIM);
 }
 

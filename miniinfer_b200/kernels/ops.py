@@ -484,7 +484,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(out), _qkv_tensor_map(lib, qkv), _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
-        _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _stream()))
+        _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream()))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
     else:
