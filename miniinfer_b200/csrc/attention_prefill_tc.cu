@@ -2,9 +2,13 @@
 // the kernel for head sizes 64 and 128 and page sizes that are multiples of 64.  The other sizes
 // take the mma.sync kernel of attention_prefill.cu, which computes the same thing.
 //
-// A block owns 128 query rows that share one kv head - 128 tokens of one query head, or, when the
-// number of query heads per kv head is even, 64 tokens of two neighbouring heads (so K and V are
-// read once for both) - and walks the keys the mask allows in tiles of 128:
+// A piece of work is 128 query rows that share one kv head - 128 tokens of one query head, or, when
+// the number of query heads per kv head is even, 64 tokens of two neighbouring heads (so K and V are
+// read once for both) - and the keys the mask allows, walked in tiles of 128.  Blocks are persistent,
+// one per SM (a block takes all of an SM's tensor memory): the works are dealt out longest first, in
+// rounds that go back and forth over the blocks, and a block's barriers run on from one work to the
+// next, so that the next work's Q and first keys are copied and its first S is computed while the
+// softmax warps finish the work before (2048 tokens of 16 heads: 40.1 -> 38.5 us).  Within a work:
 //   * a producer warp asks the TMA engine for the Q rows once and for K and V tile by tile (boxes
 //     of 64 rows x 64 elements, one page and one half of the head size each, written in the
 //     128-byte swizzle), two stages each, counted on mbarriers; K and V are counted apart, since
