@@ -4,7 +4,8 @@
 Option names follow the reference's scripts where it has them: ``--model``, ``--prompt``,
 ``--sampler-temp``, ``--sampler-top-p``, ``--sampler-top-k`` (main.py:9-25); ``--max-tokens``,
 ``--temperature``, ``--max-num-seqs``, ``--max-model-len`` (examples/minimal_engine.py:24-55);
-``--page-size``, ``--eager`` (benchmark/bench_miniinfer.py:16-26).  ``--temperature`` and
+``--page-size``, ``--eager`` (benchmark/bench_miniinfer.py:16-26); ``--profile FILE`` stands where the reference
+has benchmark/profile_miniinfer.py.  ``--temperature`` and
 ``--sampler-temp`` are two names of one option.
 
 Without a tokenizer in the model folder, give the prompt as token ids (``--prompt-ids 1,2,3``) or
@@ -38,6 +39,9 @@ def main(argv=None) -> int:
   p.add_argument("--page-size", type=int, default=64)
   p.add_argument("--num-pages", type=int, default=None)
   p.add_argument("--eager", action="store_true", help="no CUDA graphs for decode steps")
+  p.add_argument("--profile", metavar="FILE", default=None,
+                 help="run the generation under torch.profiler with stage ranges around the phases of a step "
+                      "(schedule, describe+launch, wait+update) and write their host times and the kernels' device times to FILE")
   p.add_argument("--random-weights", metavar="CONFIG_JSON", default=None,
                  help="write random weights for this config.json into --model first")
   args = p.parse_args(argv)
@@ -63,7 +67,12 @@ def main(argv=None) -> int:
                           top_p=args.top_p, ignore_eos=args.ignore_eos)
   t0 = time.time()
   with engine:
-    outputs = engine.generate(prompts, params)
+    if args.profile:
+      from miniinfer_b200.utils import profile_to
+      with profile_to(args.profile):
+        outputs = engine.generate(prompts, params)
+    else:
+      outputs = engine.generate(prompts, params)
   dt = time.time() - t0
   for prompt, out in zip(prompts, outputs):
     shown = prompt if isinstance(prompt, str) else f"{len(prompt)} token ids"

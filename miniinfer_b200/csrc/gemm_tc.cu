@@ -39,7 +39,7 @@
 // waits of the block, sets the status word to 4, and the block runs to its end, tensor memory freed.
 //
 // Stands where the reference calls torch.nn.functional.linear followed by its Triton silu_mul
-// kernel (miniinfer/layers/mlp.py, kernels/triton/silu_mul.py:6-42).
+// kernel (miniinfer/models/fused_qwen3.py:111-138, kernels/triton/silu_mul.py:6-42).
 #include <cuda.h>
 
 #include "common.cuh"

@@ -23,7 +23,9 @@ import torch
 from ..cache.manager import KVCacheManager
 from ..config import EngineConfig, build_model_spec, load_model_config
 from ..sampling import Sampler, SamplingParams, derive_seed
+from ..utils.crash_dump import dump_step_failure
 from ..utils.logging import get_logger
+from ..utils.stages import stage
 from ..weights import init_random_on_device, load_weights
 from .runner import ModelRunner, StepItem
 from .scheduler import Request, Scheduler, SchedulerOutput
@@ -287,8 +289,19 @@ class LLMEngine:
     nxt.num_decode_tokens = len(fl.reqs)
     return nxt
 
-  @torch.no_grad()
   def step(self) -> List[Dict[str, Any]]:
+    """One engine step (see ``_step``).  If it raises, what the engine knew - queues, cache occupancy, the
+    running requests, graphs and libraries - is logged as one structured record before the error goes on
+    (miniinfer/utils/crash_logger.py:1-239)."""
+    try:
+      return self._step()
+    except BaseException as exc:
+      if not isinstance(exc, (KeyboardInterrupt, SystemExit)):
+        dump_step_failure(exc, scheduler=self.scheduler, cache=self.cache, runner=self.runner, stage="LLMEngine.step")
+      raise
+
+  @torch.no_grad()
+  def _step(self) -> List[Dict[str, Any]]:
     """Schedules, runs and samples one step; returns the outputs of the requests that finished.
     With ``enable_overlap`` a decode step that follows a decode step of the same requests is
     launched before the tokens of the step before are read (it takes them on the device), so the
@@ -301,32 +314,39 @@ class LLMEngine:
       self._take_submitted()
     fl = self._inflight
     if fl is not None:
-      nxt = self._continuation(fl)
+      with stage("schedule"):
+        nxt = self._continuation(fl)
       if nxt is not None:
         t1 = time.perf_counter()
-        self._inflight = self._launch(nxt, ids_on_device=fl.tokens_dev)
+        with stage("describe+launch"):
+          self._inflight = self._launch(nxt, ids_on_device=fl.tokens_dev)
         t2 = time.perf_counter()
-        outs = self._finish(fl)
+        with stage("wait+update"):
+          outs = self._finish(fl)
         t3 = time.perf_counter()
         self.stats["host_schedule_s"] += t1 - t0
         self.stats["host_launch_s"] += t2 - t1
         self.stats["host_wait_s"] += t3 - t2
         return outs
-      outs = self._finish(fl)
+      with stage("wait+update"):
+        outs = self._finish(fl)
       self._inflight = None
     t0b = time.perf_counter()
-    out = self.scheduler.schedule()
+    with stage("schedule"):
+      out = self.scheduler.schedule()
     if not out.items:
       return outs
     t1 = time.perf_counter()
-    fl = self._launch(out)
+    with stage("describe+launch"):
+      fl = self._launch(out)
     t2 = time.perf_counter()
     if self.config.enable_overlap and fl.graph_decode:
       self._inflight = fl              # its tokens are read at the next call
       t3 = t4 = time.perf_counter()
     else:
       t3 = time.perf_counter()
-      outs += self._finish(fl)
+      with stage("wait+update"):
+        outs += self._finish(fl)
       t4 = time.perf_counter()
     # Host seconds by phase: deciding the step, describing and launching it, waiting for the tokens, book-keeping.
     self.stats["host_schedule_s"] += t1 - t0b

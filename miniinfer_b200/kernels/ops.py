@@ -24,8 +24,12 @@ F32, BF16 = 0, 1
 PREFILL_TILE = 64     # query rows of one tile of the prefill attention kernels
 SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
 SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
-GEMM_TC_MIN_M = 1280  # from here the tcgen05 gate-up product with SwiGLU beats cuBLAS + activation (measured on B200
-                      # at K = 1024, I = 3072 and at K = 4096, I = 12288; below, its tiles of 256 rows leave SMs idle)
+GEMM_TC_MIN_M = 1280  # from here the tcgen05 gate-up product with SwiGLU beats cuBLAS + activation whatever the weights' size
+GEMM_TC_SMALL_WEIGHTS = 32 << 20   # ... and for gate-up weights of up to this many bytes it does so from 17 rows on.  Measured
+                      # on B200, library product + activation against the fused kernel: K = 1024, I = 3072 (12.6 MB): 22 / 15 / 15 /
+                      # 22 / 30 us against 13 / 12 / 13 / 19 / 25 us at 32 / 128 / 512 / 1024 / 2048 rows; K = 4096, I = 12288
+                      # (201 MB): 41 / 46 / 83 / 156 / 206 / 307 us against 56 / 58 / 88 / 157 / 185 / 286 us at 32 / 128 / 512 /
+                      # 1024 / 1280 / 2048 rows (few rows of a large matrix: its tiles of 256 rows stream the weights slower)
 _MM_F32_OUT: Optional[bool] = None   # whether torch.mm writes float32 from bf16 operands into a given tensor
 
 
@@ -210,8 +214,8 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
       raise KernelError("linear: operands and out must be contiguous CUDA tensors")
     if K % 8 != 0:
       raise KernelError(f"linear: K={K} must be a multiple of 8 (16-byte loads of bf16 rows)")
-    if M > SKINNY_MAX_M and not _capturing and out.dtype in (torch.bfloat16, torch.float32):
-      # prefill-sized: straight to cuBLAS (a third of the host time of torch.mm); not while a graph is recorded
+    if not _capturing and out.dtype in (torch.bfloat16, torch.float32):
+      # more than 16 rows: straight to cuBLAS (a third of the host time of torch.mm); not while a graph is recorded
       _check(lib, lib.mi_gemm_cublas_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, _stream()), kernels=0)
       return
     if out.dtype == torch.bfloat16:
@@ -300,8 +304,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
                   force_tc: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
-  bfloat16 with M <= 16 or M >= 1280: one kernel, the activation in the product's epilogue (few rows: the
-  weight-streaming kernel; many: the tcgen05 kernel).  Otherwise the product into a buffer of
+  bfloat16 with M <= 16, with M >= 1280, or with gate-up weights of up to 32 MB: one kernel, the activation in the
+  product's epilogue (few rows: the weight-streaming kernel; more: the tcgen05 kernel).  Otherwise the product into a buffer of
   ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
   M, K = x.shape
   I = out.shape[1]
@@ -313,7 +317,8 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     lib = common_lib()
     _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
     return
-  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (M >= GEMM_TC_MIN_M or force_tc) and K >= 64 and K % 8 == 0 and I % 8 == 0
+  many = M >= GEMM_TC_MIN_M or force_tc or (M > SKINNY_BEST_M and 4 * I * K <= GEMM_TC_SMALL_WEIGHTS)
+  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and many and K >= 64 and K % 8 == 0 and I % 8 == 0
       and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):
     # many rows: the product on tcgen05 with the activation in its epilogue; [M, 2I] is never written
     lib = common_lib()

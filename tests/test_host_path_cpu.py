@@ -201,3 +201,51 @@ def test_stream_generate_add_requests_and_submit_request(cpu_kernels, model_dirs
   with pytest.raises(ValueError, match="mismatch"):
     eng.add_requests(prompts, [sp])
   assert eng.cache.free_pages() == [24]
+
+
+def test_a_failing_step_leaves_a_structured_record(cpu_kernels, model_dirs, caplog):
+  """When a step raises, the engine logs what it knew - queues, running requests, cache occupancy - and the
+  error goes on unchanged; the dump itself never raises, whatever it is given."""
+  import logging
+  from miniinfer_b200 import LLMEngine, SamplingParams
+  from miniinfer_b200.kernels import ops
+  from miniinfer_b200.utils import describe_step_failure, dump_step_failure, tensor_summary
+  d = model_dirs("A", "float32")
+  eng = LLMEngine(d, dtype="float32", device="cpu", page_size=16, num_pages=8, max_num_seqs=2, max_model_len=64)
+  eng.add_request([5, 6, 7], SamplingParams(temperature=0.0, max_tokens=4))
+  eng.step()
+
+  def broken(*a, **k):
+    raise ops.KernelError("a kernel refused its arguments (made up for this test)")
+
+  logging.getLogger("miniinfer_b200").propagate = True
+  with caplog.at_level(logging.ERROR, logger="miniinfer_b200"):
+    import unittest.mock as mock
+    with mock.patch.object(ops, "add_rmsnorm", broken):
+      with pytest.raises(ops.KernelError, match="made up"):
+        eng.step()
+  text = caplog.text
+  assert "a step failed" in text and "made up for this test" in text
+  assert "running" in text and "'prompt': 3" in text and "free_pages" in text
+  rec = describe_step_failure(RuntimeError("x"), scheduler=eng.scheduler, cache=eng.cache, runner=eng.runner)
+  assert rec["error"] == "RuntimeError: x" and rec["cache"]["live_requests"] == 1
+  assert dump_step_failure(RuntimeError("y"), scheduler=object(), cache=object(), runner=object(), items=[object()])["error"] == "RuntimeError: y"
+  assert "shape=(2, 3)" in tensor_summary(torch.zeros(2, 3)) and tensor_summary(None) == "None"
+
+
+def test_stage_ranges_and_the_profile_option(cpu_kernels, model_dirs, tmp_path):
+  """Stage ranges are off by default and cost nothing; with --profile the command line writes the ranges'
+  host times and the kernels' device times to a file."""
+  import main as cli
+  from miniinfer_b200.utils import stage, stages_enabled
+  assert not stages_enabled()
+  with stage("nothing"):
+    pass
+  out = tmp_path / "profile.txt"
+  code = cli.main(["--model", model_dirs("A", "float32"), "--prompt-ids", "5,17,3", "--max-tokens", "4", "--temperature", "0",
+                   "--dtype", "float32", "--device", "cpu", "--max-model-len", "64", "--page-size", "16", "--profile", str(out)])
+  assert code == 0
+  text = out.read_text()
+  for name in ("stage::schedule", "stage::describe+launch", "stage::wait+update"):
+    assert name in text
+  assert not stages_enabled()
