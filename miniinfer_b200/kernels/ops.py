@@ -24,12 +24,17 @@ F32, BF16 = 0, 1
 PREFILL_TILE = 64     # query rows of one tile of the prefill attention kernels
 SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
 SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
-GEMM_TC_MIN_M = 1280  # from here the tcgen05 gate-up product with SwiGLU beats cuBLAS + activation whatever the weights' size
-GEMM_TC_SMALL_WEIGHTS = 32 << 20   # ... and for gate-up weights of up to this many bytes it does so from 17 rows on.  Measured
-                      # on B200, library product + activation against the fused kernel: K = 1024, I = 3072 (12.6 MB): 22 / 15 / 15 /
-                      # 22 / 30 us against 13 / 12 / 13 / 19 / 25 us at 32 / 128 / 512 / 1024 / 2048 rows; K = 4096, I = 12288
-                      # (201 MB): 41 / 46 / 83 / 156 / 206 / 307 us against 56 / 58 / 88 / 157 / 185 / 286 us at 32 / 128 / 512 /
-                      # 1024 / 1280 / 2048 rows (few rows of a large matrix: its tiles of 256 rows stream the weights slower)
+# Rows from which the tcgen05 gate-up product with SwiGLU in its epilogue beats the library product followed by the
+# activation kernel.  Device times on B200 with a cold L2 (each call recorded into a CUDA graph behind a 256 MB flush),
+# library + activation against the fused kernel, at 64 / 512 / 1024 / 1280 / 2048 rows:
+#   K = 1024, I = 3072:    7.1 / 11.9 / 17.1 / 19.9 / 28.9 us   against   13.7 / 14.9 / 20.5 / 21.0 / 27.0 us
+#   K = 2048, I = 6144:   15.4 / 25.6 / 44.2 / 54.0 / 81.7 us   against   21.4 / 34.0 / 45.4 / 56.3 / 77.4 us
+#   K = 4096, I = 12288:  49.6 / 76.1 / 142 / 190 / 284 us      against   63.6 / 84.4 / 149 / 173 / 270 us
+# The fused kernel saves the pass over [M, 2I] but needs about 13 us to fill and drain its pipeline of 256-row tiles,
+# so for prompt portions and mixed steps of fewer rows the library stays (blocks that work alone on 128-row tiles,
+# MINIINFER_B200_GEMM_TC=1, are slower still).
+GEMM_TC_MIN_M = 1280        # for K >= 4096
+GEMM_TC_MIN_M_NARROW = 1792  # for narrower models
 _MM_F32_OUT: Optional[bool] = None   # whether torch.mm writes float32 from bf16 operands into a given tensor
 
 
@@ -304,8 +309,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
                   force_tc: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
-  bfloat16 with M <= 16, with M >= 1280, or with gate-up weights of up to 32 MB: one kernel, the activation in the
-  product's epilogue (few rows: the weight-streaming kernel; more: the tcgen05 kernel).  Otherwise the product into a buffer of
+  bfloat16 with M <= 16 or from 1280 rows on (1792 for K < 4096): one kernel, the activation in the product's
+  epilogue (few rows: the weight-streaming kernel; many: the tcgen05 kernel).  Otherwise the product into a buffer of
   ``workspace``, then the activation kernel (the same up to the order of the sums over K)."""
   M, K = x.shape
   I = out.shape[1]
@@ -317,7 +322,7 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     lib = common_lib()
     _check(lib, lib.mi_gemm_skinny_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _stream()))
     return
-  many = M >= GEMM_TC_MIN_M or force_tc or (M > SKINNY_BEST_M and 4 * I * K <= GEMM_TC_SMALL_WEIGHTS)
+  many = force_tc or M >= (GEMM_TC_MIN_M if K >= 4096 else GEMM_TC_MIN_M_NARROW)
   if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and many and K >= 64 and K % 8 == 0 and I % 8 == 0
       and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):
     # many rows: the product on tcgen05 with the activation in its epilogue; [M, 2I] is never written
