@@ -39,7 +39,15 @@
 // once and held in registers between the maximum and the exponentials, 44.5 us; the keys of a block
 // split over two blocks, 61 us; every other exponential as a polynomial on the FMA pipe instead
 // of the special-function unit, 45.7 us - the softmax warps wait on the latencies of tensor
-// memory and of each other, not on a pipe, and more instructions only lengthen their path.)
+// memory and of each other, not on a pipe, and more instructions only lengthen their path.
+// With persistent blocks, 38.5 us as it stands: one softmax thread per row that reads the row's 128
+// scores once and holds them in registers (four warps per stream, 200 registers a thread by
+// setmaxnreg, no exchange between threads), 96 us - half as many warps hide the latencies of
+// tensor memory and of the exponentials half as well.  Two threads per row that hold their 64
+// scores in registers between the maximum and the exponentials need about 112 registers each; the
+// block is launched with 96 for each of its 640 threads, and setmaxnreg only moves registers that the
+// block already has between its warpgroups - four softmax warpgroups at 112 and the fifth at 56
+// are more than that, and a setmaxnreg.inc that cannot be met waits for ever.  Not built.)
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
 // ends all later waits at once and sets the status word, and the block runs to its end, where the
