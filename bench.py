@@ -396,6 +396,88 @@ def kernel_rates(engine, batch: int, cfg: dict, layers: int, pk: dict, steps: in
   return out
 
 
+def kernel_case(name: str, reps: int = 3) -> str:
+  """One kernel alone on an input larger than L2, a few launches: the workload of the ncu summaries under
+  profiles/ for the kernels that a benchmark step does not reach (or reaches only at small sizes)."""
+  import torch
+  from miniinfer_b200.engine.context import Workspace
+  from miniinfer_b200.kernels import ops
+  from miniinfer_b200.kernels.ops import AttentionBatch
+  dev = torch.device("cuda:0")
+  g = torch.Generator(device=dev).manual_seed(1)
+  rnd = lambda *shape, dtype=torch.bfloat16, scale=1.0: (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+  ws = Workspace(dev)
+
+  def attention_case(dtype, page, items):
+    """items: (context length, new tokens) per request; the cache holds random keys and values."""
+    nh, nkv, hd = 16, 8, 128
+    pages_per = [-(-c // page) for c, _ in items]
+    kv = rnd(sum(pages_per) + 1, 2, nkv, page, hd, dtype=dtype)
+    bt = torch.zeros(len(items) + 1, max(pages_per) + 1, dtype=torch.int32)
+    nxt = 1
+    for b, n in enumerate(pages_per):
+      bt[b, :n] = torch.arange(nxt, nxt + n)
+      nxt += n
+    T = sum(n for _, n in items)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    q_start, pos, tok_item, row = [], [], [], 0
+    for b, (c, n) in enumerate(items):
+      q_start.append(row)
+      pos += list(range(c - n, c))
+      tok_item += [b] * n
+      row += n
+    tiles = [(b, o) for b, (c, n) in enumerate(items) if n > 1 for o in range(0, n, ops.PREFILL_TILE)]
+    dec = [b for b, (c, n) in enumerate(items) if n == 1]
+    batch = AttentionBatch(token_item=i32(tok_item), positions=i32(pos), seq_slot=i32(list(range(len(items)))), q_start=i32(q_start),
+                           q_len=i32([n for _, n in items]), ctx_len=i32([c for c, _ in items]), num_tokens=T, num_items=len(items),
+                           prefill_tiles=i32(tiles).view(-1, 2) if tiles else torch.zeros((0, 2), dtype=torch.int32, device=dev),
+                           num_prefill_tiles=len(tiles), decode_items=i32(dec) if dec else torch.zeros(0, dtype=torch.int32, device=dev),
+                           num_decode=len(dec), max_ctx_len=max(c for c, _ in items), scratch=ws)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype)
+    out = torch.empty(T, nh * hd, dtype=dtype, device=dev)
+    return lambda: ops.attention(out, qkv, kv, bt.to(dev), batch, nh, nkv, hd, hd ** -0.5, None), f"{len(items)} requests {items[:2]}.., page {page}, {dtype}"
+
+  if name == "sample":
+    R, V = 256, 151936
+    logits = rnd(R, V, dtype=torch.float32, scale=2.0)
+    f = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)
+    args = (f([(0.8, 1.0, 0.6, 0.0)[i % 4] for i in range(R)], torch.float32), f([(0, 50, 0, 0)[i % 4] for i in range(R)], torch.int32),
+            f([(1.0, 1.0, 0.9, 1.0)[i % 4] for i in range(R)], torch.float32), f(list(range(R)), torch.int64), f([3] * R, torch.int64))
+    out = torch.empty(R, dtype=torch.int32, device=dev)
+    fn, what = (lambda: ops.sample(out, logits, *args, ws)), f"{R} rows x {V} float32 logits (155 MB), a quarter each: plain temperature, top-k 50, top-p 0.9, greedy"
+  elif name == "silu_mul":
+    gu, out = rnd(8192, 2 * 12288), torch.empty(8192, 12288, dtype=torch.bfloat16, device=dev)
+    fn, what = (lambda: ops.silu_mul(out, gu)), "8192 x (2 x 12288) bf16: 403 MB in, 201 MB out"
+  elif name == "gemm_f32":
+    x, w = rnd(256, 4096, dtype=torch.float32), rnd(8192, 4096, dtype=torch.float32, scale=0.02)
+    out = torch.empty(256, 8192, device=dev)
+    fn, what = (lambda: ops.linear(out, x, w)), "float32, M = 256, N = 8192, K = 4096 (134 MB of weights, 17.2 GFLOP)"
+  elif name == "gemm_tc_plain":
+    x, w = rnd(2048, 4096), rnd(4096, 4096, scale=0.02)
+    out = torch.empty(2048, 4096, dtype=torch.bfloat16, device=dev)
+    fn, what = (lambda: ops.linear_tc(out, x, w, ws)), "bf16 plain product on tcgen05, M = 2048, N = 4096, K = 4096 (68.7 GFLOP)"
+  elif name == "attention_generic":
+    fn, what = attention_case(torch.float32, 64, [(2048, 1)] * 8 + [(2048, 512)])
+  elif name == "attention_prefill_mma":
+    fn, what = attention_case(torch.bfloat16, 16, [(2048, 2048)])           # pages of 16 tokens: not the tcgen05 kernel's
+  elif name == "attention_decode_cpasync":
+    fn, what = attention_case(torch.bfloat16, 16, [(2048 + 8 * i, 1) for i in range(64)])
+  else:
+    raise SystemExit(f"unknown kernel case {name!r}")
+  fn()
+  torch.cuda.synchronize()
+  start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  start.record()
+  for _ in range(reps):
+    fn()
+  end.record()
+  torch.cuda.synchronize()
+  return f"{name}: {what}: {1000 * start.elapsed_time(end) / reps:.1f} us per call (warm, {reps} calls back to back)"
+
+
+KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "attention_generic", "attention_prefill_mma", "attention_decode_cpasync")
+
+
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
   """A continuous batch through `LLMEngine.generate`: prompts of 128 .. 2048 uniform random tokens, `outputs`
   generated tokens each, prompts cut under a budget of 2048 tokens a step.  Run twice; the second run
@@ -574,9 +656,14 @@ def main() -> int:
   ap.add_argument("--skip-points", action="store_true")
   ap.add_argument("--mixed", action="store_true",
                   help="run a continuous batch of 64 requests through LLMEngine.generate, print its throughput and exit")
+  ap.add_argument("--kernel-case", default=None, choices=KERNEL_CASES,
+                  help="run one kernel alone on an input larger than L2 (the workload of the ncu summaries) and exit")
   ap.add_argument("--kernel-table", nargs="?", const="decode", default=None, choices=["decode", "prefill"],
                   help="print the device time of each kernel of a decode step (default) or a prefill step and exit")
   args = ap.parse_args()
+  if args.kernel_case:
+    print(kernel_case(args.kernel_case))
+    return 0
   if args.impl == "reference":
     return reference_arm(args)
   if args.impl == "reference-child":
