@@ -14,7 +14,9 @@
 // Thresholds are found exactly by a 4 x 8-bit radix walk over the order-preserving integer image
 // of z: counts per bin for top-k, probability mass per bin for top-p.  Mass is held as 64-bit
 // fixed point (exp(z - max) * 2^40, integer adds), so the walk does not depend on the order in
-// which threads add.  Entries equal to a threshold are all kept.
+// which threads add.  Entries equal to a threshold are all kept.  The histograms are kept per warp
+// and added up at the end of a pass (a row of 151936 logits: top-p 0.69 ms; 2.2 ms with one histogram that a
+// thousand threads add to with 64-bit shared-memory atomics, most of them to the same few bins).
 //
 // Two launches: (1) one block per row finds the row's threshold (rows without top-k/top-p leave at
 // once); (2) the vocabulary of each row is cut into slices, one block per (slice, row) finds the
@@ -84,20 +86,43 @@ __device__ Best block_argmax(Best mine, Best* scratch /* 32 */) {
   return scratch[0];
 }
 
+// Histograms without contention.  The top byte of the ordered image takes a handful of values for real
+// logits, so a block-wide histogram in shared memory has a thousand threads adding to three or four
+// words - and 64-bit shared-memory adds are compare-and-swap loops.  Here every warp has a histogram of
+// its own for the mass; in each step the lanes of a warp that hit the same bin find each other (match.any), one of them
+// takes the group's sum (redux) and adds it to the warp's bin with plain loads and stores - the groups of a
+// step hit different bins, and a warp's steps follow each other - and at the end of a pass the warps'
+// histograms are added up, bin by bin.  Integer sums: the result does not depend on the order.
+constexpr int WARPS_T = THREADS / 32;
+
+__device__ __forceinline__ void warp_hist_add(unsigned long long* mine /* [256] of this warp */, bool active, unsigned bin,
+                                              unsigned long long value) {
+  const unsigned live = __ballot_sync(0xffffffffu, active);
+  if (!active) return;
+  const unsigned group = __match_any_sync(live, bin);
+  // the sum of a group's values, 24 bits at a time (32 lanes of 24 bits fit a 32-bit redux)
+  const unsigned lo = __reduce_add_sync(group, (unsigned)(value & 0xffffffull));
+  const unsigned mid = __reduce_add_sync(group, (unsigned)((value >> 24) & 0xffffffull));
+  const unsigned hi = __reduce_add_sync(group, (unsigned)(value >> 48));
+  if ((threadIdx.x & 31) == __ffs(group) - 1)
+    mine[bin] += (unsigned long long)lo + ((unsigned long long)mid << 24) + ((unsigned long long)hi << 48);
+}
+
 // Launch 1: thresholds.  thr[row] = smallest ordered image that is kept (0: everything).
 __global__ void __launch_bounds__(THREADS)
 sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict__ logits,
                         const float* __restrict__ temperature, const int* __restrict__ top_k,
                         const float* __restrict__ top_p, int V) {
   mi::grid_dependency_sync();
+  extern __shared__ unsigned long long warp_hist[];          // [WARPS_T][256]
   __shared__ Best best_scratch[32];
-  __shared__ unsigned int count_hist[256];
-  __shared__ unsigned long long mass_hist[256];
+  __shared__ unsigned long long hist[256];                   // the warps' histograms added up
   __shared__ unsigned int sh_prefix;
   __shared__ unsigned long long sh_above;
-  __shared__ unsigned int sh_rank;
+  __shared__ unsigned long long sh_rank;
 
   const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* x = logits + (size_t)row * V;
   const float temp = temperature[row];
   const int k = top_k[row];
@@ -108,27 +133,70 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
     return;
   }
   uint32_t thr_k = 0u, thr_p = 0u;  // keep entries whose ordered image is >= both
+  unsigned long long* mine = warp_hist + (size_t)warp * 256;
+  const int V32 = (V + 31) / 32 * 32;                         // whole warps walk the row together (match and redux are warp-wide)
+
+  // One pass of a radix walk: the histogram, over bin = byte `shift` of the ordered image, of value(i) over the
+  // entries whose higher bytes equal `prefix` (and that `keep` lets through).  Result in hist[].
+  // Counts go to one histogram of the block with 32-bit shared-memory adds, which the hardware does itself (a
+  // row of 151936 logits, top-k: 150 us that way, 430 us through the warps' histograms).
+  auto count_pass = [&](int shift, uint32_t prefix, uint32_t mask) {
+    unsigned int* counts = reinterpret_cast<unsigned int*>(warp_hist);
+    if (threadIdx.x < 256) counts[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+      const uint32_t u = ordered(x[i] / temp);
+      if ((u & mask) == prefix) atomicAdd(&counts[(u >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) hist[threadIdx.x] = counts[threadIdx.x];
+    __syncthreads();
+  };
+  auto pass = [&](int shift, uint32_t prefix, uint32_t mask, auto value_of) {
+    for (int b = lane; b < 256; b += 32) mine[b] = 0ull;
+    __syncwarp();
+    for (int i = threadIdx.x; i < V32; i += THREADS) {
+      bool active = i < V;
+      unsigned bin = 0;
+      unsigned long long val = 0ull;
+      if (active) {
+        const float z = x[i] / temp;
+        const uint32_t u = ordered(z);
+        active = u >= thr_k && (u & mask) == prefix;
+        if (active) {
+          bin = (u >> shift) & 255u;
+          val = value_of(z);
+          active = val != 0ull;
+        }
+      }
+      warp_hist_add(mine, active, bin, val);
+      __syncwarp();
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      unsigned long long t = 0ull;
+#pragma unroll 8
+      for (int w = 0; w < WARPS_T; ++w) t += warp_hist[(size_t)w * 256 + threadIdx.x];
+      hist[threadIdx.x] = t;
+    }
+    __syncthreads();
+  };
 
   if (use_k) {
     // the k-th largest z: walk the bits from the top, keeping the rank still wanted
-    if (threadIdx.x == 0) { sh_prefix = 0u; sh_rank = (unsigned)k; }
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
-      if (threadIdx.x < 256) count_hist[threadIdx.x] = 0u;
-      __syncthreads();
+    if (threadIdx.x == 0) { sh_prefix = 0u; sh_rank = (unsigned long long)k; }
+    __syncthreads();
+    for (int ps = 0; ps < 4; ++ps) {
+      const int shift = 24 - 8 * ps;
       const uint32_t prefix = sh_prefix;
-      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-      for (int i = threadIdx.x; i < V; i += THREADS) {
-        const uint32_t u = ordered(x[i] / temp);
-        if ((u & mask) == prefix) atomicAdd(&count_hist[(u >> shift) & 255u], 1u);
-      }
-      __syncthreads();
+      const uint32_t mask = ps == 0 ? 0u : (0xffffffffu << (shift + 8));
+      count_pass(shift, prefix, mask);
       if (threadIdx.x == 0) {
-        unsigned want = sh_rank, seen = 0;
+        unsigned long long want = sh_rank, seen = 0;
         int b = 255;
         for (; b > 0; --b) {
-          if (seen + count_hist[b] >= want) break;
-          seen += count_hist[b];
+          if (seen + hist[b] >= want) break;
+          seen += hist[b];
         }
         sh_rank = want - seen;
         sh_prefix = prefix | ((uint32_t)b << shift);
@@ -148,26 +216,17 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
     }
     mx = block_argmax(Best{mx, 0}, best_scratch).v;
     if (threadIdx.x == 0) { sh_prefix = 0u; sh_above = 0ull; }
+    __syncthreads();
     unsigned long long target = 0ull;  // used by thread 0 only
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
-      if (threadIdx.x < 256) mass_hist[threadIdx.x] = 0ull;
-      __syncthreads();
+    for (int ps = 0; ps < 4; ++ps) {
+      const int shift = 24 - 8 * ps;
       const uint32_t prefix = sh_prefix;
-      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-      for (int i = threadIdx.x; i < V; i += THREADS) {
-        const float z = x[i] / temp;
-        const uint32_t u = ordered(z);
-        if (u >= thr_k && (u & mask) == prefix) {
-          const unsigned long long q = (unsigned long long)(expf(z - mx) * 1099511627776.0f);
-          if (q) atomicAdd(&mass_hist[(u >> shift) & 255u], q);
-        }
-      }
-      __syncthreads();
+      const uint32_t mask = ps == 0 ? 0u : (0xffffffffu << (shift + 8));
+      pass(shift, prefix, mask, [mx](float z) { return (unsigned long long)(expf(z - mx) * 1099511627776.0f); });
       if (threadIdx.x == 0) {
-        if (pass == 0) {
+        if (ps == 0) {
           unsigned long long total = 0ull;
-          for (int b = 0; b < 256; ++b) total += mass_hist[b];
+          for (int b = 0; b < 256; ++b) total += hist[b];
           target = (unsigned long long)((double)total * (double)p);
           if (target < 1ull) target = 1ull;
         }
@@ -175,8 +234,8 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
         unsigned long long above = sh_above;
         int b = 255;
         for (; b > 0; --b) {
-          if (above + mass_hist[b] >= target) break;
-          above += mass_hist[b];
+          if (above + hist[b] >= target) break;
+          above += hist[b];
         }
         sh_above = above;
         sh_prefix = prefix | ((uint32_t)b << shift);
@@ -186,6 +245,18 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
     thr_p = sh_prefix;
   }
   if (threadIdx.x == 0) thr_out[row] = thr_k > thr_p ? thr_k : thr_p;
+}
+
+constexpr size_t THRESHOLD_SMEM = (size_t)WARPS_T * 256 * sizeof(unsigned long long);   // 64 KB
+
+// The threshold kernel's shared memory is more than a kernel gets without asking; asked once per process.
+static int configure_threshold_kernel() {
+  static bool done = false;
+  if (done) return 0;
+  cudaError_t e = cudaFuncSetAttribute(sample_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)THRESHOLD_SMEM);
+  if (e != cudaSuccess) return mi_fail("sample: cannot get %zu bytes of shared memory: %s", THRESHOLD_SMEM, cudaGetErrorString(e));
+  done = true;
+  return 0;
 }
 
 constexpr int PICK_THREADS = 256;
@@ -270,7 +341,8 @@ MI_API int mi_sample(int* out, const float* logits, const float* temperature, co
   uint32_t* thr = (uint32_t*)scratch;
   float* part_v = (float*)scratch + R;
   int* part_i = (int*)scratch + R + (size_t)R * slices;
-  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), 0, stream, thr, logits, temperature, top_k, top_p, V);
+  if (configure_threshold_kernel()) return 1;
+  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), THRESHOLD_SMEM, stream, thr, logits, temperature, top_k, top_p, V);
   MI_LAUNCH_OK("sample thresholds");
   const int slice_len = (V + slices - 1) / slices;
   mi::launch(sample_pick_kernel, dim3(dim3(slices, R)), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr, part_v,
@@ -327,7 +399,8 @@ MI_API int mi_sample_static(int* out, const float* logits, const float* temperat
   // the arrival counters must start at zero whatever an earlier call left behind
   e = cudaMemsetAsync(arrivals, 0, sizeof(int) * R, stream);
   if (e != cudaSuccess) return mi_fail("sample_static: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
-  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), 0, stream, thr, logits, temperature, top_k, top_p, V);
+  if (configure_threshold_kernel()) return 1;
+  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), THRESHOLD_SMEM, stream, thr, logits, temperature, top_k, top_p, V);
   MI_LAUNCH_OK("sample_static thresholds");
   const int slice_len = (V + slices - 1) / slices;
   mi::launch(sample_pick_kernel, dim3(slices, R), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr,
