@@ -15,14 +15,20 @@
 // of z: counts per bin for top-k, probability mass per bin for top-p.  Mass is held as 64-bit
 // fixed point (exp(z - max) * 2^40, integer adds), so the walk does not depend on the order in
 // which threads add.  Entries equal to a threshold are all kept.  The histograms are kept per warp
-// and added up at the end of a pass (a row of 151936 logits: top-p 0.69 ms; 2.2 ms with one histogram that a
-// thousand threads add to with 64-bit shared-memory atomics, most of them to the same few bins).
+// and added up at the end of a pass, and a row is spread over a cluster of up to eight blocks (a row of 151936
+// logits: top-p 0.13 ms, top-k 0.05 ms; with one block per row and one histogram that a thousand threads add to
+// with 64-bit shared-memory atomics, most of them to the same few bins, top-p took 2.2 ms).
 //
-// Two launches: (1) one block per row finds the row's threshold (rows without top-k/top-p leave at
+// Two launches: (1) a cluster of up to eight blocks per row finds the row's threshold, each block on its part of
+// the row, the blocks' histograms added up through distributed shared memory (rows without top-k/top-p leave at
 // once); (2) the vocabulary of each row is cut into slices, one block per (slice, row) finds the
 // slice's best perturbed score, and the last block of a row to finish picks the row's best.  The
 // arg-max with its lowest-index rule is associative, so the slicing does not change the result.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -121,20 +127,37 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
   __shared__ unsigned long long sh_above;
   __shared__ unsigned long long sh_rank;
 
-  const int row = blockIdx.x;
+  // A row belongs to a cluster of C blocks (gridDim.x = C), each of which walks a C-th of the row; after a pass
+  // the blocks' histograms are added up through distributed shared memory, and every block walks the sum.
+  __shared__ float sh_max;
+  const int C = (int)gridDim.x, rank = (int)blockIdx.x;
+  const int row = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* x = logits + (size_t)row * V;
   const float temp = temperature[row];
   const int k = top_k[row];
   const float p = top_p[row];
   const bool use_k = k > 0 && k < V, use_p = p < 1.f;
-  if (!(temp > 0.f) || (!use_k && !use_p)) {
-    if (threadIdx.x == 0) thr_out[row] = 0u;
+  if (!(temp > 0.f) || (!use_k && !use_p)) {                  // the same for every block of the cluster
+    if (threadIdx.x == 0 && rank == 0) thr_out[row] = 0u;
     return;
   }
   uint32_t thr_k = 0u, thr_p = 0u;  // keep entries whose ordered image is >= both
   unsigned long long* mine = warp_hist + (size_t)warp * 256;
-  const int V32 = (V + 31) / 32 * 32;                         // whole warps walk the row together (match and redux are warp-wide)
+  const int part = ((V + C - 1) / C + 31) / 32 * 32;          // this block's part of the row: whole warps walk it together
+  const int i_begin = rank * part, i_end = min(V, i_begin + part);
+  // the sum over the cluster of what every block has in hist[] (nothing to do for a cluster of one)
+  auto cluster_sum = [&]() {
+    if (C == 1) return;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    unsigned long long t = 0ull;
+    if (threadIdx.x < 256)
+      for (int r = 0; r < C; ++r) t += cluster.map_shared_rank(hist, r)[threadIdx.x];
+    cluster.sync();                                           // everybody has read: hist may be overwritten
+    if (threadIdx.x < 256) hist[threadIdx.x] = t;
+    __syncthreads();
+  };
 
   // One pass of a radix walk: the histogram, over bin = byte `shift` of the ordered image, of value(i) over the
   // entries whose higher bytes equal `prefix` (and that `keep` lets through).  Result in hist[].
@@ -144,19 +167,20 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
     unsigned int* counts = reinterpret_cast<unsigned int*>(warp_hist);
     if (threadIdx.x < 256) counts[threadIdx.x] = 0u;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += THREADS) {
+    for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
       const uint32_t u = ordered(x[i] / temp);
       if ((u & mask) == prefix) atomicAdd(&counts[(u >> shift) & 255u], 1u);
     }
     __syncthreads();
     if (threadIdx.x < 256) hist[threadIdx.x] = counts[threadIdx.x];
     __syncthreads();
+    cluster_sum();
   };
   auto pass = [&](int shift, uint32_t prefix, uint32_t mask, auto value_of) {
     for (int b = lane; b < 256; b += 32) mine[b] = 0ull;
     __syncwarp();
-    for (int i = threadIdx.x; i < V32; i += THREADS) {
-      bool active = i < V;
+    for (int i = i_begin + threadIdx.x; i < i_begin + part; i += THREADS) {
+      bool active = i < i_end;
       unsigned bin = 0;
       unsigned long long val = 0ull;
       if (active) {
@@ -180,6 +204,7 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
       hist[threadIdx.x] = t;
     }
     __syncthreads();
+    cluster_sum();
   };
 
   if (use_k) {
@@ -210,11 +235,18 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
   if (use_p) {
     // max of the kept entries, then their total mass in fixed point
     float mx = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += THREADS) {
+    for (int i = i_begin + threadIdx.x; i < i_end; i += THREADS) {
       const float z = x[i] / temp;
       if (ordered(z) >= thr_k) mx = fmaxf(mx, z);
     }
     mx = block_argmax(Best{mx, 0}, best_scratch).v;
+    if (C > 1) {                                              // the largest of the blocks' maxima
+      cg::cluster_group cluster = cg::this_cluster();
+      if (threadIdx.x == 0) sh_max = mx;
+      cluster.sync();
+      for (int r = 0; r < C; ++r) mx = fmaxf(mx, *cluster.map_shared_rank(&sh_max, r));
+      cluster.sync();
+    }
     if (threadIdx.x == 0) { sh_prefix = 0u; sh_above = 0ull; }
     __syncthreads();
     unsigned long long target = 0ull;  // used by thread 0 only
@@ -244,7 +276,7 @@ sample_threshold_kernel(uint32_t* __restrict__ thr_out, const float* __restrict_
     }
     thr_p = sh_prefix;
   }
-  if (threadIdx.x == 0) thr_out[row] = thr_k > thr_p ? thr_k : thr_p;
+  if (threadIdx.x == 0 && rank == 0) thr_out[row] = thr_k > thr_p ? thr_k : thr_p;
 }
 
 constexpr size_t THRESHOLD_SMEM = (size_t)WARPS_T * 256 * sizeof(unsigned long long);   // 64 KB
@@ -256,6 +288,43 @@ static int configure_threshold_kernel() {
   cudaError_t e = cudaFuncSetAttribute(sample_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)THRESHOLD_SMEM);
   if (e != cudaSuccess) return mi_fail("sample: cannot get %zu bytes of shared memory: %s", THRESHOLD_SMEM, cudaGetErrorString(e));
   done = true;
+  return 0;
+}
+
+// Blocks per row of the threshold kernel: a cluster of up to 8, each block at least 8192 logits.
+static int threshold_cluster(int V) {
+  int c = 1;
+  while (c < 8 && V >= 2 * 8192 * c) c *= 2;
+  return c;
+}
+
+static int launch_thresholds(uint32_t* thr, const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                             int R, int V, cudaStream_t stream) {
+  if (configure_threshold_kernel()) return 1;
+  const int C = threshold_cluster(V);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(C, R);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = THRESHOLD_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (mi::pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (C > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = C;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sample_threshold_kernel, thr, logits, temperature, top_k, top_p, V);
+  if (e != cudaSuccess) return mi_fail("sample thresholds: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -341,9 +410,7 @@ MI_API int mi_sample(int* out, const float* logits, const float* temperature, co
   uint32_t* thr = (uint32_t*)scratch;
   float* part_v = (float*)scratch + R;
   int* part_i = (int*)scratch + R + (size_t)R * slices;
-  if (configure_threshold_kernel()) return 1;
-  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), THRESHOLD_SMEM, stream, thr, logits, temperature, top_k, top_p, V);
-  MI_LAUNCH_OK("sample thresholds");
+  if (launch_thresholds(thr, logits, temperature, top_k, top_p, R, V, stream)) return 1;
   const int slice_len = (V + slices - 1) / slices;
   mi::launch(sample_pick_kernel, dim3(dim3(slices, R)), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr, part_v,
                                                                   part_i, arrivals, V, slices, slice_len);
@@ -399,9 +466,7 @@ MI_API int mi_sample_static(int* out, const float* logits, const float* temperat
   // the arrival counters must start at zero whatever an earlier call left behind
   e = cudaMemsetAsync(arrivals, 0, sizeof(int) * R, stream);
   if (e != cudaSuccess) return mi_fail("sample_static: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
-  if (configure_threshold_kernel()) return 1;
-  mi::launch(sample_threshold_kernel, dim3(R), dim3(THREADS), THRESHOLD_SMEM, stream, thr, logits, temperature, top_k, top_p, V);
-  MI_LAUNCH_OK("sample_static thresholds");
+  if (launch_thresholds(thr, logits, temperature, top_k, top_p, R, V, stream)) return 1;
   const int slice_len = (V + slices - 1) / slices;
   mi::launch(sample_pick_kernel, dim3(slices, R), dim3(PICK_THREADS), 0, stream, out, logits, temperature, seed, counter, thr,
              part_v, part_i, arrivals, V, slices, slice_len);
