@@ -238,9 +238,10 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
 def fuses_few_rows(x_rows: int, dtype: torch.dtype) -> bool:
   """Whether a step of ``x_rows`` rows takes the few-row products with the norm and the residual add fused to them
   (six launches per layer instead of eight).  Off unless MINIINFER_B200_FUSE_FEW_ROWS=1: measured on B200 (Qwen3-0.6B
-  shape, decode at batch 8) the fused step takes 1.31 ms against 1.12 ms.  The norm kernels between the products
-  are where, under dependent launch, the next product's blocks get onto the SMs and fetch their weights; a product
-  that follows a product directly finds the SMs' registers taken until its predecessor has ended."""
+  shape) the fused decode step takes 1.05 ms against 0.99 ms at batch 8 and 0.78 against 0.74 ms at batch 1.  The
+  norm kernels between the products are where, under dependent launch, the next product's blocks get onto the SMs
+  and fetch their weights - a step from which the norm launches are simply left out is slower, not faster - while a
+  product that follows a product directly finds the SMs' registers taken until its predecessor has ended."""
   return dtype == torch.bfloat16 and 0 < x_rows <= SKINNY_BEST_M and os.environ.get("MINIINFER_B200_FUSE_FEW_ROWS", "0") == "1"
 
 
