@@ -46,10 +46,11 @@ MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaS
   if (T == 0) return 0;
   const size_t total = (size_t)T * I;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const int most = mi::sm_count() * 16;
+  const int blocks = (int)((total + threads - 1) / threads < most ? (total + threads - 1) / threads : most);
   if (dtype == MI_BF16 && I % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gu % 16) == 0) {
     const size_t total8 = total / 8;
-    const int b8 = (int)((total8 + threads - 1) / threads < 148 * 16 ? (total8 + threads - 1) / threads : 148 * 16);
+    const int b8 = (int)((total8 + threads - 1) / threads < most ? (total8 + threads - 1) / threads : most);
     mi::launch(silu_mul_bf16x8_kernel, dim3(b8), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I / 8, total8);
   } else if (dtype == MI_BF16)
     mi::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, total);

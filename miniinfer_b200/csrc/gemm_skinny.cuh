@@ -303,7 +303,7 @@ int pick_ksplit(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M
   // As few warps per group of rows as still gives every SM about two blocks: long-lived warps that
   // stream many rows keep more bytes in flight than many short-lived blocks.  A function of N and K
   // only, so that the order of the additions behind an output does not depend on the batch.
-  const int target = 296;
+  const int target = 2 * mi::sm_count();       // two blocks of 8 warps per SM
   const int cols = SWIGLU ? 8 : NT * 8;
   int ks = 1;
   while (ks < 8 && (N + (WARPS / ks) * cols - 1) / ((WARPS / ks) * cols) < target) ks *= 2;
@@ -320,7 +320,7 @@ int pick_ksplit(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M
   // each warp would walk a long stretch of K.  Sixteen warps per block halve the stretch and double
   // the bytes in flight.  Few activation rows only: the wide tiles need the registers.
   if constexpr (MT == 1) {
-    if (ks == 8 && (N + cols - 1) / cols < 148 && K >= 64 * 16)
+    if (ks == 8 && (N + cols - 1) / cols < mi::sm_count() && K >= 64 * 16)
       return launch<MT, NT, 16, HALF, TOut, SWIGLU, 16, FUSE>(out, x, w, M, N, K, ldo, stream, fa);
   }
   switch (ks) {
@@ -337,7 +337,7 @@ int dispatch16(TOut* out, const __nv_bfloat16* x, const __nv_bfloat16* w, int M,
                cudaStream_t stream, FuseArgs fa) {
   const bool wide = N >= 2048;
   const int blocks16 = (N + 15) / 16;
-  if (blocks16 > 296 && blocks16 <= 444 && K >= 512)
+  if (blocks16 > 2 * mi::sm_count() && blocks16 <= 3 * mi::sm_count() && K >= 512)
     return M <= 8 ? launch<1, 3, 8, true, TOut, false, WARPS, FUSE>(out, x, w, M, N, K, ldo, stream, fa)
                   : launch<1, 3, 8, false, TOut, false, WARPS, FUSE>(out, x, w, M, N, K, ldo, stream, fa);
   if (M <= 8) return wide ? pick_ksplit<1, 2, true, TOut, false, FUSE>(out, x, w, M, N, K, ldo, stream, fa)

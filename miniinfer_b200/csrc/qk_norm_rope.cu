@@ -351,7 +351,7 @@ MI_API int mi_qk_norm_rope_store(void* qkv, int dtype, const float* q_w, const f
     const bool aligned16 = ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)kv_layer % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0 &&
                            ((uintptr_t)q_w % 16) == 0 && ((uintptr_t)k_w % 16) == 0;
     if (hd == 128 && T > 64 && aligned16)
-      mi::launch(qk_norm_rope_store_wide128_kernel, dim3(T < 148 * 4 ? T : 148 * 4), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w,
+      mi::launch(qk_norm_rope_store_wide128_kernel, dim3(T < mi::sm_count() * 4 ? T : mi::sm_count() * 4), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w,
                  cos_sin, positions, slot_mapping, (__nv_bfloat16*)kv_layer, nh, nkv, page_size, eps, T);
     else if (hd == 128)
       mi::launch(qk_norm_rope_store_fast_kernel<128>, dim3(fast_grid), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_w, k_w, cos_sin, positions,

@@ -423,7 +423,7 @@ MI_API int mi_sample(int* out, const float* logits, const float* temperature, co
 // fixed array in the library's device image instead of memory the caller passes.
 #include "no_alloc_api.h"
 
-#define MI_SAMPLE_STATIC_WORDS 1024   /* thr[R] + best value and index per (row, slice): R + 2 * R * slices <= 256 + 2 * 296 */
+#define MI_SAMPLE_STATIC_WORDS 1024   /* thr[R] + best value and index per (row, slice): R + 2 * R * slices, with R * slices <= 384 */
 #define MI_SAMPLE_STATIC_MAX_DEVICES 64
 
 // 4 KiB of per-slice results and thresholds, then one arrival counter per row.
@@ -451,10 +451,10 @@ MI_API int mi_sample_static(int* out, const float* logits, const float* temperat
     g_sample_static_addr[device] = p;
   }
   unsigned int* base = (unsigned int*)g_sample_static_addr[device];
-  // slices of the vocabulary per row: about two blocks of the pick kernel per SM of a B200, bounded so that
+  // slices of the vocabulary per row: about two blocks of the pick kernel per SM, bounded so that
   // the results fit the fixed scratch.  Callers of mi_sample choose their own count (the engine asks for
   // more); the token is the same for any count, since the arg-max over slices is associative.
-  int slices = 296 / R;
+  int slices = (2 * mi::sm_count() < 384 ? 2 * mi::sm_count() : 384) / R;
   if (slices > 64) slices = 64;
   if (slices > (V + 1023) / 1024) slices = (V + 1023) / 1024;
   if (slices < 1) slices = 1;

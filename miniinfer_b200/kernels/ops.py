@@ -438,8 +438,9 @@ def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim:
   forced = os.environ.get("MINIINFER_B200_DECODE_CHUNK")
   if forced:
     return int(forced)
+  two_per_sm = 2 * _num_sms(torch.device("cuda", torch.cuda.current_device()))
   for c in DECODE_CHUNKS:
-    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= 296:
+    if num_decode * num_kv_heads * -(-max_ctx_len // c) >= two_per_sm:
       return c
   return DECODE_CHUNKS[-1]
 
