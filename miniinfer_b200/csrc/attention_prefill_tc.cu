@@ -47,7 +47,26 @@
 // scores in registers between the maximum and the exponentials need about 112 registers each; the
 // block is launched with 96 for each of its 640 threads, and setmaxnreg only moves registers that the
 // block already has between its warpgroups - four softmax warpgroups at 112 and the fifth at 56
-// are more than that, and a setmaxnreg.inc that cannot be met waits for ever.  Not built.)
+// are more than that, and a setmaxnreg.inc that cannot be met waits for ever.  Not built.
+// A timeline of one block (clock64 stamps of the issuing thread and of the softmax warps, 16 tiles of
+// one work) shows what binds: a stream's tile takes S (~600 cycles on the tensor cores), the softmax
+// warps' round (~2600: 1400 for the pass over the scores, where the stream's two warps per scheduler
+// share one special-function unit, 200 for the exchange of maxima, 500 to 800 for the store of P and
+// its wait, 350 for the barriers), P V (~500), and two looks at barriers in between, each of which
+// costs 350 to 600 cycles even when the barrier completed long before: while S products run, the
+// tensor cores read Q and K at the full width of shared memory, and everything else that goes to
+// shared memory queues behind them.  Two such chains, interleaved, give the ~2900 cycles a tile
+// takes; the tensor cores are busy for ~1100 of them.  The issuing thread spends a tile's time as 16
+// products (60 to 80 cycles each), five commits (55 each), a fence (100), the wait for P (600) and the
+// looks at V and the next K.  Tried against that, none faster (38.5 us as it stands): later tiles of a
+// stream in one pass over the scores (exponentials against the old maximum, redone only if the maximum
+// moves by more than 2^8: 38.6 us, and the kernel spills at its 96 registers); one arrival per warp
+// instead of per thread on the barriers the softmax warps complete (no change); the block table read
+// by the whole producer warp, 32 entries at a time (no change: the copies do not wait for those reads);
+// the barriers of the next tile looked at while this tile's products are issued (40.8 -> 41.7 us in the
+// build that could switch it: the look comes too early to find P written); an issuing thread per
+// stream (46.2 us: the two streams fall into step, both in the softmax and then both on the tensor
+// cores, instead of taking turns).)
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
 // ends all later waits at once and sets the status word, and the block runs to its end, where the
