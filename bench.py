@@ -325,7 +325,7 @@ def _group(times: dict) -> dict:
   import re
   g = {"own_products": 0.0, "library_products": 0.0, "attention": 0.0, "other": 0.0}
   for name, us in times.items():
-    if "gemm_skinny" in name or "gemm_tc_kernel" in name:
+    if "gemm_skinny" in name or "gemm_tc_kernel" in name or "gemm_stream_tc" in name:
       g["own_products"] += us
     elif re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill", name):
       g["attention"] += us

@@ -30,7 +30,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
               "-Xptxas", "-v"]
 
 COMMON_SOURCES = ["common.cu", "embedding.cu", "norm.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_skinny_fused.cu",
-                  "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu", "gemm_cublas.cu", "gemm_tc.cu"]
+                  "qk_norm_rope.cu", "attention_generic.cu", "activation.cu", "sampling.cu", "gemm_cublas.cu", "gemm_tc.cu",
+                  "gemm_stream_tc.cu"]
 COMMON_LIBS = ["cublas"]
 ATTENTION_SOURCES = ["attention_prefill.cu", "attention_decode.cu", "attention_decode_tma.cu", "attention_prefill_tc.cu",
                      "attention_decode_cluster.cu"]

@@ -194,11 +194,12 @@ def _mm_f32_out_works(device) -> bool:
   return _MM_F32_OUT
 
 
-def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bool = False) -> None:
+def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bool = False, force_stream: bool = False) -> None:
   """out[M, N] = x[M, K] @ w[N, K]^T.  float32 operands: this package's fp32 FMA kernel (out float32).
-  bfloat16 operands: its skinny tensor-core kernel for M <= 16 (out bf16 or fp32; a row's value does
-  not depend on the other rows), cuBLAS above (where the reference uses it for every product).
-  ``force_skinny``: the skinny kernel for any M (in slices of 64 rows)."""
+  bfloat16 operands: for M <= 16 the weight-streaming kernels (out bf16 or fp32; a row's value does not depend
+  on the other rows) - the tcgen05 one from ``STREAM_TC_MIN_BYTES`` of weights on, the mma.sync one below -,
+  cuBLAS above 16 rows (where the reference uses it for every product).
+  ``force_skinny``: the mma.sync kernel for any M (in slices of 64 rows); ``force_stream``: the tcgen05 one at any size."""
   M, K = x.shape
   N = w.shape[0]
   if w.shape[1] != K or out.shape != (M, N):
@@ -211,6 +212,12 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
     return
   if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
     raise KernelError(f"linear: operands must both be float32 or both bfloat16, got {x.dtype} and {w.dtype}")
+  if _streams(M, N * K, K, force_skinny, force_stream) and out.dtype in (torch.bfloat16, torch.float32):
+    parts, counters, status = _stream_workspace(lib, x.device)
+    _check(lib, lib.mi_gemm_stream_tc_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, N, _ptr(parts, torch.float32),
+                                           _ptr(counters, torch.int32), counters.numel(), parts.shape[0],
+                                           _ptr(status, torch.int32), _stream()))
+    return
   if M <= SKINNY_BEST_M or (force_skinny and M <= SKINNY_MAX_M):
     _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, N, _stream()))
     return
@@ -233,6 +240,39 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
     m1 = min(M, m0 + SKINNY_MAX_M)
     _check(lib, lib.mi_gemm_skinny_bf16(_ptr(out[m0:m1]), _dt(out), _ptr(x[m0:m1]), _ptr(w), m1 - m0, N, K, N,
                                         _stream()))
+
+
+# Few rows times a large weight matrix: from this many bytes of weights on, the tcgen05 kernel that deals the
+# matrix out to the SMs in equal stretches (gemm_stream_tc.cu); below, the mma.sync kernel (gemm_skinny.cu),
+# whose launches start and end faster.
+STREAM_TC_MIN_BYTES = 160 << 20
+STREAM_TC_MAX_TILES = 1 << 14
+_stream_ws: Dict[int, tuple] = {}
+
+
+def _streams(M: int, weight_elements: int, K: int, force_skinny: bool, force_stream: bool) -> bool:
+  if M > SKINNY_BEST_M or force_skinny or K < 64 or K % 8 != 0:
+    return False
+  mode = os.environ.get("MINIINFER_B200_GEMM_STREAM", "")
+  if mode == "0":
+    return False
+  return force_stream or mode == "1" or 2 * weight_elements >= STREAM_TC_MIN_BYTES
+
+
+def _stream_workspace(lib, device):
+  """Partial sums, tile counters and the status word of the tcgen05 streaming product, made once per device."""
+  idx = device.index if device.index is not None else torch.cuda.current_device()
+  ws = _stream_ws.get(idx)
+  if ws is None:
+    if torch.cuda.is_current_stream_capturing():
+      raise KernelError("gemm_stream_tc: its workspace must exist before a graph is recorded (run the step once before)")
+    floats, blocks = ctypes.c_longlong(0), ctypes.c_int(0)
+    _check(lib, lib.mi_gemm_stream_tc_workspace(ctypes.byref(floats), ctypes.byref(blocks)), kernels=0)
+    parts = torch.zeros((blocks.value, floats.value // blocks.value), dtype=torch.float32, device=device)
+    counters = torch.zeros(STREAM_TC_MAX_TILES, dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    ws = _stream_ws[idx] = (parts, counters, status)
+  return ws
 
 
 def fuses_few_rows(x_rows: int, dtype: torch.dtype) -> bool:
@@ -308,7 +348,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_we
 
 
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
-                  force_tc: bool = False) -> None:
+                  force_tc: bool = False, force_stream: bool = False) -> None:
   """out[M, I] = silu(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a SwiGLU feed-forward.
   bfloat16 with M <= 16 or from 1280 rows on (1792 for K < 4096): one kernel, the activation in the product's
   epilogue (few rows: the weight-streaming kernel; many: the tcgen05 kernel).  Otherwise the product into a buffer of
@@ -318,6 +358,13 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
   if w.shape != (2 * I, K) or out.shape[0] != M or out.dtype != x.dtype:
     raise KernelError(f"linear_swiglu: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
   if M == 0:
+    return
+  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _streams(M, 2 * I * K, K, force_skinny, force_stream):
+    lib = common_lib()
+    parts, counters, status = _stream_workspace(lib, x.device)
+    _check(lib, lib.mi_gemm_stream_tc_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _ptr(parts, torch.float32),
+                                                  _ptr(counters, torch.int32), counters.numel(), parts.shape[0],
+                                                  _ptr(status, torch.int32), _stream()))
     return
   if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (M <= SKINNY_BEST_M or (force_skinny and M <= SKINNY_MAX_M)):
     lib = common_lib()
@@ -615,4 +662,6 @@ def device_status(ws) -> int:
     buf = ws._bufs.get((name, torch.int32))
     if buf is not None:
       code |= int(buf[0])
+  for _, _, status in _stream_ws.values():
+    code |= int(status[0])
   return code

@@ -300,6 +300,42 @@ def test_few_rows_times_many_megabytes_of_weights(ops, N, K, swiglu):
   assert torch.equal(first[8], first[16][:8])
 
 
+@pytest.mark.parametrize("N,K,swiglu,out_dtype", [(1000, 200, False, torch.bfloat16), (128, 64, False, torch.bfloat16),
+                                                    (4096, 4096, False, torch.bfloat16), (18992, 264, False, torch.float32),
+                                                    (300, 1032, True, torch.bfloat16), (3072, 1024, True, torch.bfloat16),
+                                                    (70, 9000, False, torch.bfloat16), (8, 72, True, torch.bfloat16)])
+def test_streaming_product_on_tcgen05(ops, N, K, swiglu, out_dtype):
+  """The few-row product that deals the weight matrix out to the SMs in equal stretches (tcgen05, TMA), forced at
+  sizes below its threshold too: widths that are no multiple of its tiles and slices, stretches that cut tiles
+  (one tile for all SMs; many tiles), both outputs.  Against the statement; a row's value must not depend on the
+  other rows nor on the call; the tile counters are left at zero."""
+  w = rnd((2 if swiglu else 1) * N, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+  xs = rnd(16, K, dtype=torch.bfloat16, seed=1)
+  first = None
+  for M in (16, 1, 5, 8, 16):
+    x = xs[:M].contiguous()
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    if swiglu:
+      gu = torch.empty(M, 2 * N, dtype=torch.bfloat16, device=DEV)
+      want = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+      ref.linear(gu, x, w)
+      ref.silu_mul(want, gu)
+      ops.linear_swiglu(out, x, w, _Scratch(), force_stream=True)
+      want = want.float()
+    else:
+      want = x.float() @ w.float().t()
+      ops.linear(out, x, w, force_stream=True)
+    err = (out.float() - want).abs().max().item()
+    bound = (1e-4 if out_dtype == torch.float32 else 2e-2) * max(1.0, want.abs().max().item())
+    assert err <= bound, (M, err, bound)
+    if first is None:
+      first = out
+    else:
+      assert torch.equal(out, first[:M]), "a row's value must not depend on the other rows, nor on the call"
+  parts, counters, status = ops._stream_ws[torch.cuda.current_device()]
+  assert int(counters.abs().sum()) == 0 and int(status[0]) == 0
+
+
 @pytest.mark.parametrize("I,K", [(24, 64), (3072, 1024), (1000, 136), (7, 8), (333, 2048)])
 def test_linear_swiglu(ops, I, K):
   """The fused gate-and-up product against product + activation (which it must match up to the
