@@ -212,7 +212,7 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
     return
   if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
     raise KernelError(f"linear: operands must both be float32 or both bfloat16, got {x.dtype} and {w.dtype}")
-  if _streams(M, N * K, K, force_skinny, force_stream) and out.dtype in (torch.bfloat16, torch.float32):
+  if _streams(M, N, K, force_skinny, force_stream) and out.dtype in (torch.bfloat16, torch.float32):
     parts, counters, status = _stream_workspace(lib, x.device)
     _check(lib, lib.mi_gemm_stream_tc_bf16(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, N, _ptr(parts, torch.float32),
                                            _ptr(counters, torch.int32), counters.numel(), parts.shape[0],
@@ -242,21 +242,28 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
                                         _stream()))
 
 
-# Few rows times a large weight matrix: from this many bytes of weights on, the tcgen05 kernel that deals the
-# matrix out to the SMs in equal stretches (gemm_stream_tc.cu); below, the mma.sync kernel (gemm_skinny.cu),
-# whose launches start and end faster.
+# Few rows times a large weight matrix: the tcgen05 kernel that deals the matrix out to the SMs in equal stretches
+# (gemm_stream_tc.cu) from 160 MiB of weights on, and from 80 MiB where the matrix has more than 4096 rows; else the
+# mma.sync kernel (gemm_skinny.cu), whose launches start and end faster and whose 16-warp blocks fill the SMs in one
+# round for up to 4096 rows.  Measured on B200, 8 rows, cold weights, microseconds (tcgen05 / mma.sync):
+#   10240 x 5120 (105 MB) 23.6 / 26.1    5120 x 8192 (84 MB) 19.9 / 21.1    5120 x 25600 (262 MB) 49.2 / 64.1
+#   SwiGLU 2 x 25600 x 5120 (524 MB) 84.3 / 93.4    SwiGLU 2 x 12288 x 4096 (201 MB) 38.8 / 41.7
+#   151936 x 1024 (311 MB) 55.1 / 56.2    4096 x 12288 (101 MB) 23.1 / 19.7    6144 x 4096 (50 MB) 14.2 / 11.7
 STREAM_TC_MIN_BYTES = 160 << 20
+STREAM_TC_MIN_BYTES_MANY_ROWS = 80 << 20
 STREAM_TC_MAX_TILES = 1 << 14
 _stream_ws: Dict[int, tuple] = {}
 
 
-def _streams(M: int, weight_elements: int, K: int, force_skinny: bool, force_stream: bool) -> bool:
+def _streams(M: int, weight_rows: int, K: int, force_skinny: bool, force_stream: bool) -> bool:
   if M > SKINNY_BEST_M or force_skinny or K < 64 or K % 8 != 0:
     return False
   mode = os.environ.get("MINIINFER_B200_GEMM_STREAM", "")
   if mode == "0":
     return False
-  return force_stream or mode == "1" or 2 * weight_elements >= STREAM_TC_MIN_BYTES
+  size = 2 * weight_rows * K
+  return (force_stream or mode == "1" or size >= STREAM_TC_MIN_BYTES
+          or (size >= STREAM_TC_MIN_BYTES_MANY_ROWS and weight_rows > 4096))
 
 
 def _stream_workspace(lib, device):
@@ -359,7 +366,7 @@ def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace
     raise KernelError(f"linear_swiglu: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
   if M == 0:
     return
-  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _streams(M, 2 * I * K, K, force_skinny, force_stream):
+  if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and _streams(M, 2 * I, K, force_skinny, force_stream):
     lib = common_lib()
     parts, counters, status = _stream_workspace(lib, x.device)
     _check(lib, lib.mi_gemm_stream_tc_swiglu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _ptr(parts, torch.float32),
