@@ -456,6 +456,10 @@ def kernel_case(name: str, reps: int = 3) -> str:
     x, w = rnd(2048, 4096), rnd(4096, 4096, scale=0.02)
     out = torch.empty(2048, 4096, dtype=torch.bfloat16, device=dev)
     fn, what = (lambda: ops.linear_tc(out, x, w, ws)), "bf16 plain product on tcgen05, M = 2048, N = 4096, K = 4096 (68.7 GFLOP)"
+  elif name == "gemm_stream":
+    x, w = rnd(8, 25600), rnd(5120, 25600, scale=0.02)
+    out = torch.empty(8, 5120, dtype=torch.bfloat16, device=dev)
+    fn, what = (lambda: ops.linear(out, x, w)), "bf16 few-row product on tcgen05, M = 8, N = 5120, K = 25600 (262 MB of weights: the down product of the Qwen3-32B shape)"
   elif name == "attention_generic":
     fn, what = attention_case(torch.float32, 64, [(2048, 1)] * 8 + [(2048, 512)])
   elif name == "attention_prefill_mma":
@@ -475,7 +479,7 @@ def kernel_case(name: str, reps: int = 3) -> str:
   return f"{name}: {what}: {1000 * start.elapsed_time(end) / reps:.1f} us per call (warm, {reps} calls back to back)"
 
 
-KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "attention_generic", "attention_prefill_mma", "attention_decode_cpasync")
+KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_mma", "attention_decode_cpasync")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
