@@ -239,39 +239,42 @@ gemm_stream_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_co
   const int u_begin = stretch_begin(me, blocks, units), u_end = stretch_begin(me + 1, blocks, units);
   const Walk walk(u_begin, u_end, a.slices);
 
-  // Thread 0 is the producer: it sets the barriers up and asks for the first weights at once, before the block
-  // meets (the other warps have tensor memory to allocate and nothing to do until a slice has landed).
-  auto weights = [&](int u, int s) {
+  // Warp 0 is the producer.  Its first thread sets the barriers up, and the warp asks for the first weights at once,
+  // before the block meets (the other warps have tensor memory to allocate and nothing to do until a slice has
+  // landed) and before the predecessor in the stream is waited for (no kernel writes weights).  A slice is twelve
+  // copies - eight boxes of weights, four of activations -, each asked for by a lane of its own: one thread
+  // issuing them one after the other took 2 us for the first three slices.
+  constexpr int W_BOXES = 2 * KBOX;                        // weight boxes of a slice
+  static_assert(STAGES * W_BOXES <= 32 && STAGES * KBOX <= 32 && W_BOXES + KBOX <= 32, "a lane per copy");
+  auto weight_box = [&](int u, int s, int box) {           // box: 2 * (box of K) + (half of the rows)
     const int t = u / a.slices, k = u % a.slices;
-    unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
-    const int row_lo = SWIGLU ? t * HALF_ROWS : t * TILE_ROWS;
-    const int row_hi = SWIGLU ? a.up_row0 + t * HALF_ROWS : t * TILE_ROWS + HALF_ROWS;
-#pragma unroll
-    for (int kb = 0; kb < KBOX; ++kb) {
-      tma_load_2d(dst + kb * W_KBOX_BYTES, &w_map, k * SLICE_K + kb * BK, row_lo, &full[s]);
-      tma_load_2d(dst + kb * W_KBOX_BYTES + W_BOX_BYTES, &w_map, k * SLICE_K + kb * BK, row_hi, &full[s]);
-    }
+    const int kb = box >> 1, hi = box & 1;
+    const int row = SWIGLU ? (hi ? a.up_row0 + t * HALF_ROWS : t * HALF_ROWS) : t * TILE_ROWS + hi * HALF_ROWS;
+    tma_load_2d(stages + (size_t)s * STAGE_BYTES + kb * W_KBOX_BYTES + hi * W_BOX_BYTES, &w_map, k * SLICE_K + kb * BK, row, &full[s]);
+  };
+  auto activation_box = [&](int u, int s, int kb) {
+    const int k = u % a.slices;
+    tma_load_2d(stages + (size_t)s * STAGE_BYTES + W_STAGE_BYTES + kb * X_BOX_BYTES, &x_map, k * SLICE_K + kb * BK, 0, &full[s]);
   };
   const int early = min(STAGES, u_end - u_begin);
-  if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+  if (warp == PRODUCER_WARP) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full[s], 1);
+        mbar_init(&empty[s], 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&acc_full[i], 1);
+        mbar_init(&acc_empty[i], EPILOGUE_WARPS);
+      }
+      *abort = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      for (int i = 0; i < early; ++i) mbar_expect_tx(&full[i], (uint32_t)STAGE_BYTES);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], EPILOGUE_WARPS);
-    }
-    *abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // the first stages are empty: their weights are asked for before the predecessor in the stream is waited for
-    // (no kernel writes weights)
-    for (int i = 0; i < early; ++i) {
-      mbar_expect_tx(&full[i], (uint32_t)STAGE_BYTES);
-      weights(walk.unit(i), i);
-    }
+    __syncwarp();
+    if (lane < early * W_BOXES) weight_box(walk.unit(lane / W_BOXES), lane / W_BOXES, lane % W_BOXES);
   }
   if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -281,29 +284,24 @@ gemm_stream_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_co
 
   if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
-      auto activations = [&](int u, int s) {
-        const int k = u % a.slices;
-        unsigned char* dst = stages + (size_t)s * STAGE_BYTES + W_STAGE_BYTES;
-#pragma unroll
-        for (int kb = 0; kb < KBOX; ++kb) tma_load_2d(dst + kb * X_BOX_BYTES, &x_map, k * SLICE_K + kb * BK, 0, &full[s]);
-      };
-      dep_sync();
-      for (int i = 0; i < early; ++i) activations(walk.unit(i), i);
-      int n = 0;
-      int u0, u1;
-      for (int i = 0; walk.segment(i, u0, u1) && !*abort; ++i) {
-        for (int u = u0; u < u1 && !*abort; ++u, ++n) {
-          if (n < early) continue;
-          const int s = n % STAGES;
+    dep_sync();
+    if (lane < early * KBOX) activation_box(walk.unit(lane / KBOX), lane / KBOX, lane % KBOX);
+    int n = 0;
+    int u0, u1;
+    bool stop = false;
+    for (int i = 0; walk.segment(i, u0, u1) && !stop; ++i) {
+      for (int u = u0; u < u1; ++u, ++n) {
+        if (n < early) continue;
+        const int s = n % STAGES;
+        if (lane == 0) {
           mbar_wait(&empty[s], ((n / STAGES) & 1) ^ 1, abort, a.status);
-          mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
-          weights(u, s);
-          activations(u, s);
+          if (!*abort) mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
         }
+        stop = __shfl_sync(0xffffffffu, (int)*abort, 0) != 0;   // after a wait has run out nothing more is asked for
+        if (stop) break;
+        if (lane < W_BOXES) weight_box(u, s, lane);
+        else if (lane < W_BOXES + KBOX) activation_box(u, s, lane - W_BOXES);
       }
-    } else {
-      dep_sync();
     }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
