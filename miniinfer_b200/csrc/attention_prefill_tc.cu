@@ -303,7 +303,6 @@ __device__ __forceinline__ int nth_work(int i, int b, int blocks, int total) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
-  mi::grid_dependency_sync();
   const int total_work = (a.nh / a.hpt) * a.n_tiles;
   const int blocks = (int)gridDim.x, me = (int)blockIdx.x;
 
@@ -352,6 +351,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Up to here the block has touched nothing that a kernel writes: set up beside its predecessor in the stream, it
+  // also reads the description of its first work (the step's lists, which the host uploaded) so that the roles find
+  // it in the cache, and only then waits for the predecessor - the kernel that wrote the Q rows and the cache.
+  {
+    const int w0 = nth_work(0, me, blocks, total_work);
+    if (w0 >= 0) {
+      const Work k0 = work_of(a, w0);
+      asm volatile("" ::"r"(k0.n), "r"(k0.row0), "l"(k0.bt));
+    }
+  }
+  mi::grid_dependency_sync();
 
   // A block is persistent: it takes one work after the other.  The barriers' phases run on across works -
   // every role counts the works (Q), the key tiles (the K / V ring) and each stream's tiles (S, P, O) it has
