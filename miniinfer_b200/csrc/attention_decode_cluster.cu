@@ -38,6 +38,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "qk_rope_math.cuh"
 
 #ifndef MI_HEAD_DIM
 #error "compile with -DMI_HEAD_DIM=<head size>"
@@ -70,6 +71,14 @@ struct ClusterArgs {
   int* status;
   int nh, nkv, page_size, window, stages, max_tiles;
   float scale;
+  // The step before attention - QK norm, rotation, the new token's K and V into the cache - done here (head size 128):
+  int rope;                        // 0: the rows of q_base are normed and rotated and the cache holds the new token
+  const float* q_w;                // norm weights [HD] (null: no norm)
+  const float* k_w;
+  const float* cos_sin;            // [position][cos 0..HD/2 | sin 0..HD/2] (null: no rotation)
+  const int* slot_mapping;         // per row of the step: page * page_size + offset of the token's cache entry (null: no store)
+  __nv_bfloat16* kv_layer;         // the layer's cache, [page][2][kv head][token][HD]
+  float eps;
 };
 
 __global__ void __launch_bounds__(CTHREADS, 1)
@@ -83,8 +92,10 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
   float* red = part + GP * ROW;
   uint64_t* full = reinterpret_cast<uint64_t*>(red + CW * GP * ROW);
   uint64_t* empty = full + CMAX_STAGES;
-  int* pages = reinterpret_cast<int*>(empty + CMAX_STAGES);
+  uint64_t* patched = empty + CMAX_STAGES;                       // rope: the new token's key and value are in the last tile
+  int* pages = reinterpret_cast<int*>(patched + 1);
   volatile int* abort = pages + a.max_tiles;
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(pages + ((a.max_tiles + 4 + 3) & ~3));   // [GP][HD]: the query heads, normed and rotated here (rope)
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int C = (int)gridDim.x, r = (int)blockIdx.x, kvh = (int)blockIdx.y, e = (int)blockIdx.z;
@@ -95,6 +106,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
+    mbar_init(patched, 1);
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -112,25 +124,108 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     const int* bt = a.block_table + (size_t)a.seq_slot[item] * a.bt_stride;
     for (int i = threadIdx.x; i < nb && i < a.max_tiles; i += CTHREADS) pages[i] = bt[(j_first + (b0 + i) * BK) / a.page_size];
   }
+  // The kernel that norms and rotates q and k and stores the new token's k and v may be this kernel's work (rope):
+  // each computing warp then prepares a query head of this kv head in shared memory, and in the block that holds the
+  // request's last tile the copying warp puts the new token's key and value into that tile in shared memory once its
+  // copy has landed (whatever the cache held at that place), tells the warp that computes the tile, and writes the
+  // entry into the cache for the steps to come.
+  // The arithmetic is qk_norm_rope_store_fast_kernel's, operation for operation (qk_rope_math.cuh; a lane holds the
+  // pairs 2 l and 64 + 2 l of a head), so the step's numbers do not depend on which of the two did it.  The norm
+  // weights and the position's row of the table are read here, before the wait: no kernel writes them.
+  constexpr int HALF = HD / 2;
+  const bool rope = HD == 128 && a.rope != 0;
+  const int j = 2 * lane;
+  const float2 one = make_float2(1.f, 1.f), zero = make_float2(0.f, 0.f);
+  float2 w0 = one, w1 = one, c = one, sn = zero;             // this warp's norm weights (q, or k in the copying warp)
+  bool has_table = false;
+  if (rope) {
+    const float* w = warp == CW ? a.k_w : a.q_w;
+    if (w) {
+      w0 = *reinterpret_cast<const float2*>(w + j);
+      w1 = *reinterpret_cast<const float2*>(w + HALF + j);
+    }
+    if (a.cos_sin) {
+      const float* cs = a.cos_sin + (size_t)p * HD;
+      c = *reinterpret_cast<const float2*>(cs + j);
+      sn = *reinterpret_cast<const float2*>(cs + HALF + j);
+      has_table = true;
+    }
+  }
+  auto norm_rotate = [&](const __nv_bfloat16* x, bool normed, uint32_t& ua, uint32_t& ub) {
+    const uint32_t r0 = *reinterpret_cast<const uint32_t*>(x + j), r1 = *reinterpret_cast<const uint32_t*>(x + HALF + j);
+    float2 va = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r0));
+    float2 vb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r1));
+    if (normed) {
+      const float rstd = mi::rope_rstd(mi::warp_sum(mi::rope_sum_squares(va, vb, 0.f)), HD, a.eps);
+      va = mi::rope_scale(va, rstd, w0);
+      vb = mi::rope_scale(vb, rstd, w1);
+    }
+    if (has_table) mi::rope_rotate(va, vb, c, sn);
+    const __nv_bfloat162 oa = __floats2bfloat162_rn(va.x, va.y), ob = __floats2bfloat162_rn(vb.x, vb.y);
+    ua = *reinterpret_cast<const uint32_t*>(&oa);
+    ub = *reinterpret_cast<const uint32_t*>(&ob);
+  };
+  // this block holds the tile with position p, and the new token's entry is this kernel's to write
+  const bool patch = rope && nb > 0 && b1 == tiles && a.slot_mapping != nullptr && a.kv_layer != nullptr;
   mi::grid_dependency_sync();
   __syncthreads();
 
   if (warp == CW) {
     // ------------------------------------------------------------------ the warp that asks for the copies
-    if (lane == 0) {
-      for (int b = 0; b < nb; ++b) {
-        const int s = b % a.stages;
-        mbar_wait(&empty[s], ((b / a.stages) & 1) ^ 1, abort, a.status);
-        const int jb = j_first + (b0 + b) * BK;
-        const int y_k = ((pages[b] * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
-        const int y_v = y_k + a.nkv * a.page_size;
-        unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
+    auto ask = [&](int b) {                                  // lane 0
+      const int s = b % a.stages;
+      mbar_wait(&empty[s], ((b / a.stages) & 1) ^ 1, abort, a.status);
+      const int jb = j_first + (b0 + b) * BK;
+      const int y_k = ((pages[b] * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
+      const int y_v = y_k + a.nkv * a.page_size;
+      unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
 #pragma unroll
-        for (int x = 0; x < NBOX; ++x) {
-          tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
-          tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
-        }
+      for (int x = 0; x < NBOX; ++x) {
+        tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
+        tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+      }
+    };
+    int asked = 0;
+    if (lane == 0)
+      for (; asked < nb && asked < a.stages; ++asked) ask(asked);     // the ring is empty: no wait in here
+    const int slot = patch ? a.slot_mapping[row] : -1;
+    uint32_t ka = 0u, kb = 0u, va = 0u, vb = 0u;               // this lane's pairs of the new key (normed, rotated) and value
+    if (patch && slot >= 0) {
+      const __nv_bfloat16* qkv_row = a.q_base + (size_t)row * a.q_stride;
+      const __nv_bfloat16* xv = qkv_row + (size_t)(a.nh + a.nkv + kvh) * HD;
+      va = *reinterpret_cast<const uint32_t*>(xv + j);
+      vb = *reinterpret_cast<const uint32_t*>(xv + HALF + j);
+      norm_rotate(qkv_row + (size_t)(a.nh + kvh) * HD, a.k_w != nullptr, ka, kb);
+    }
+    if (lane == 0)
+      for (; asked < nb; ++asked) ask(asked);
+    if (patch) {
+      // The lanes meet here: a lane that looked at the last tile's barrier before lane 0 had asked for that tile could
+      // take an earlier use of the stage - two phases back, the same parity - for it.
+      __syncwarp();
+      if (slot >= 0) {
+        const int last = nb - 1, s = last % a.stages;
+        mbar_wait(&full[s], (last / a.stages) & 1, abort, a.status);   // the last tile has landed
+        const uint32_t kt = smem_u32(stage0 + (size_t)s * STAGE_BYTES);
+        const int rp = p - (j_first + (b0 + last) * BK);       // the new token's row of the tile
+        const uint32_t in_chunk = (uint32_t)((lane & 3) * 4);
+        auto put = [](uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); };
+        put(tile_addr(kt, rp, lane >> 2) + in_chunk, ka);
+        put(tile_addr(kt, rp, 8 + (lane >> 2)) + in_chunk, kb);
+        put(tile_addr(kt + TILE_BYTES, rp, lane >> 2) + in_chunk, va);
+        put(tile_addr(kt + TILE_BYTES, rp, 8 + (lane >> 2)) + in_chunk, vb);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(patched);
+      if (slot >= 0) {
+        const size_t page = slot / a.page_size, off = slot % a.page_size;
+        __nv_bfloat16* dk = a.kv_layer + (((page * 2 + 0) * a.nkv + kvh) * a.page_size + off) * HD;
+        __nv_bfloat16* dv = a.kv_layer + (((page * 2 + 1) * a.nkv + kvh) * a.page_size + off) * HD;
+        *reinterpret_cast<uint32_t*>(dk + j) = ka;
+        *reinterpret_cast<uint32_t*>(dk + HALF + j) = kb;
+        *reinterpret_cast<uint32_t*>(dv + j) = va;
+        *reinterpret_cast<uint32_t*>(dv + HALF + j) = vb;
       }
     }
   } else {
@@ -141,6 +236,17 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     uint32_t qf[KSTEPS][2];
     {
       const __nv_bfloat16* qrow = a.q_base + (size_t)row * a.q_stride + (size_t)(kvh * G + g) * HD;
+      if (rope) {
+        const __nv_bfloat16* qkv_row = a.q_base + (size_t)row * a.q_stride;
+        for (int h = warp; h < G; h += CW) {                  // a head per warp
+          uint32_t ua, ub;
+          norm_rotate(qkv_row + (size_t)(kvh * G + h) * HD, a.q_w != nullptr, ua, ub);
+          *reinterpret_cast<uint32_t*>(q_s + h * HD + j) = ua;
+          *reinterpret_cast<uint32_t*>(q_s + h * HD + HALF + j) = ub;
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(CW * 32) : "memory");      // the computing warps have left the query heads in shared memory
+        qrow = q_s + (g < G ? g : 0) * HD;
+      }
 #pragma unroll
       for (int k = 0; k < KSTEPS; ++k) {
         const int c0 = k * 16 + 2 * t4;
@@ -157,6 +263,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     for (int b = warp; b < nb; b += CW) {
       const int s = b % a.stages;
       mbar_wait(&full[s], (b / a.stages) & 1, abort, a.status);
+      if (patch && b == nb - 1) mbar_wait(patched, 0, abort, a.status);
       const uint32_t kt = smem_u32(stage0 + (size_t)s * STAGE_BYTES);
       consume_tile(kt, kt + TILE_BYTES, qf, o, m_run, l_run, j_first + (b0 + b) * BK, lo, p + 1, scale2, lane);
       __syncwarp();
@@ -235,8 +342,8 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
 }
 
 size_t cluster_smem(int stages, int max_tiles) {
-  return (size_t)stages * STAGE_BYTES + (size_t)(1 + CW) * GP * ROW * sizeof(float) + 2 * CMAX_STAGES * 8 +
-         (size_t)(max_tiles + 4) * sizeof(int) + 1024;
+  return (size_t)stages * STAGE_BYTES + (size_t)(1 + CW) * GP * ROW * sizeof(float) + (2 * CMAX_STAGES + 1) * 8 +
+         (size_t)(max_tiles + 8) * sizeof(int) + (size_t)GP * HD * sizeof(__nv_bfloat16) + 1024;
 }
 
 // Stages for blocks of up to `max_tiles` tiles: one per tile if they fit (every copy is then asked for at once and
@@ -285,11 +392,12 @@ MI_API int mi_attention_decode_cluster_fit(int cluster, int tiles_per_block) {
   return n;
 }
 
-// cluster: blocks that share a (request, kv head), 1 .. 16.  max_ctx_len: no request of the step is longer.
-MI_API int mi_attention_decode_cluster(void* out, const void* q_base, int q_stride, const void* kv_map,
-                                       const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
-                                       const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
-                                       int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream) {
+namespace {
+int launch_cluster(void* out, const void* q_base, int q_stride, const void* kv_map,
+                   const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
+                   const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
+                   int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream,
+                   int rope, const float* q_w, const float* k_w, const float* cos_sin, const int* slot_mapping, void* kv_layer, float eps) {
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode_cluster: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(nh / nkv <= GP, "attention_decode_cluster: at most %d query heads per kv head (got %d)", GP, nh / nkv);
   MI_REQUIRE(cluster >= 1 && cluster <= 16, "attention_decode_cluster: cluster=%d is not in 1..16", cluster);
@@ -311,6 +419,9 @@ MI_API int mi_attention_decode_cluster(void* out, const void* q_base, int q_stri
   a.status = status;
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
   a.scale = scale;
+  a.rope = rope; a.q_w = q_w; a.k_w = k_w; a.cos_sin = cos_sin; a.slot_mapping = slot_mapping;
+  a.kv_layer = (__nv_bfloat16*)kv_layer; a.eps = eps;
+  MI_REQUIRE(!rope || HD == 128, "attention_decode_cluster: norm and rotation inside the kernel are for head size 128 (got %d)", HD);
   // the most tiles a request can have (a window may start anywhere in its first tile), and a block's share
   const int span = window > 0 && window < max_ctx_len ? window : max_ctx_len;
   const int tiles = (span + BK - 1) / BK + 1;
@@ -358,6 +469,29 @@ MI_API int mi_attention_decode_cluster(void* out, const void* q_base, int q_stri
   if (err != cudaSuccess) return mi_fail("attention_decode_cluster: launch failed: %s", cudaGetErrorString(err));
   return 0;
 }
+}  // namespace
+
+// cluster: blocks that share a (request, kv head), 1 .. 16.  max_ctx_len: no request of the step is longer.
+MI_API int mi_attention_decode_cluster(void* out, const void* q_base, int q_stride, const void* kv_map,
+                                       const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
+                                       const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
+                                       int page_size, float scale, int window, int cluster, int max_ctx_len, cudaStream_t stream) {
+  return launch_cluster(out, q_base, q_stride, kv_map, block_table, bt_stride, decode_items, q_start, ctx_len, seq_slot, status, n_dec,
+                        nh, nkv, page_size, scale, window, cluster, max_ctx_len, stream, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f);
+}
+
+// The same for a step of decode tokens only, with the step before attention inside (head size 128, the whole head
+// rotated): q_base holds the raw QKV rows; q and k are normed (weights, or null) and rotated (table [position][128], or
+// null) as qk_norm_rope_store does, and the new token's k and v go into the cache at slot_mapping[row] (null: no store).
+MI_API int mi_attention_decode_cluster_rope(void* out, const void* qkv, int q_stride, const void* kv_map,
+                                            const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
+                                            const int* ctx_len, const int* seq_slot, int* status, int n_dec, int nh, int nkv,
+                                            int page_size, float scale, int window, int cluster, int max_ctx_len,
+                                            const float* q_w, const float* k_w, const float* cos_sin, const int* slot_mapping,
+                                            void* kv_layer, float eps, cudaStream_t stream) {
+  return launch_cluster(out, qkv, q_stride, kv_map, block_table, bt_stride, decode_items, q_start, ctx_len, seq_slot, status, n_dec,
+                        nh, nkv, page_size, scale, window, cluster, max_ctx_len, stream, 1, q_w, k_w, cos_sin, slot_mapping, kv_layer, eps);
+}
 
 #else  // head sizes that are not multiples of 64 have no TMA tiles
 
@@ -365,6 +499,11 @@ MI_API int mi_attention_decode_cluster_supported() { return 0; }
 MI_API int mi_attention_decode_cluster_fit(int, int) { return 0; }
 MI_API int mi_attention_decode_cluster(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,
                                        const int*, int*, int, int, int, int, float, int, int, int, cudaStream_t) {
+  return mi_fail("attention_decode_cluster: head size %d has no such kernel", MI_HEAD_DIM);
+}
+MI_API int mi_attention_decode_cluster_rope(void*, const void*, int, const void*, const int*, int, const int*, const int*, const int*,
+                                            const int*, int*, int, int, int, int, float, int, int, int, const float*, const float*,
+                                            const float*, const int*, void*, float, cudaStream_t) {
   return mi_fail("attention_decode_cluster: head size %d has no such kernel", MI_HEAD_DIM);
 }
 

@@ -11,6 +11,7 @@
 // table cos_sin[pos, 0:rotary_dim/2] = cos, [rotary_dim/2:rotary_dim] = sin.
 // Cache layout of one layer: [page, 2 (k, v), kv head, token in page, head_dim].
 #include "common.cuh"
+#include "qk_rope_math.cuh"
 
 namespace {
 
@@ -162,28 +163,23 @@ qk_norm_rope_store_fast_kernel(__nv_bfloat16* __restrict__ qkv, const float* __r
 #pragma unroll
         for (int i = 0; i < NP; ++i) {
           v[hf][i] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[u][hf][i]));
-          ss += v[hf][i].x * v[hf][i].x + v[hf][i].y * v[hf][i].y;
         }
+#pragma unroll
+      for (int i = 0; i < NP; ++i) ss = mi::rope_sum_squares(v[0][i], v[1][i], ss);
       float rstd = 1.f;
       if (normed) {
         ss = mi::warp_sum(ss);
-        rstd = rsqrtf(ss / (float)HD + eps);
+        rstd = mi::rope_rstd(ss, HD, eps);
       }
 #pragma unroll
       for (int i = 0; i < NP; ++i) {
         const int j = 64 * i + 2 * lane;              // index in the first half
         float2 a = v[0][i], b = v[1][i];
         if (normed) {
-          const float2 wa = is_q ? wq[0][i] : wk[0][i], wb = is_q ? wq[1][i] : wk[1][i];
-          a.x *= rstd * wa.x; a.y *= rstd * wa.y;
-          b.x *= rstd * wb.x; b.y *= rstd * wb.y;
+          a = mi::rope_scale(a, rstd, is_q ? wq[0][i] : wk[0][i]);
+          b = mi::rope_scale(b, rstd, is_q ? wq[1][i] : wk[1][i]);
         }
-        if (cs) {
-          const float2 c = cs_c[i], sn = cs_s[i];
-          const float2 ra = make_float2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
-          const float2 rb = make_float2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
-          a = ra; b = rb;
-        }
+        if (cs) mi::rope_rotate(a, b, cs_c[i], cs_s[i]);
         const __nv_bfloat162 oa = __floats2bfloat162_rn(a.x, a.y), ob = __floats2bfloat162_rn(b.x, b.y);
         const uint32_t ua = *reinterpret_cast<const uint32_t*>(&oa), ub = *reinterpret_cast<const uint32_t*>(&ob);
         *reinterpret_cast<uint32_t*>(x + j) = ua;

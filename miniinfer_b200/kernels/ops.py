@@ -485,6 +485,63 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     ctypes.c_float(scale), win, _stream()))
 
 
+def _rope_in_attention(qkv, cos_sin, kv_layer, batch, nh, nkv, hd, win, page_size) -> int:
+  """The cluster size with which a step takes the decode kernel that norms, rotates and stores itself, or 0: a step
+  of decode tokens only, bfloat16, head size 128 with the whole head rotated, and few enough (request, kv head)
+  pairs for the cluster-scheduled kernel."""
+  if not (qkv.is_cuda and qkv.dtype == torch.bfloat16 and hd == 128 and page_size % 64 == 0 and nh // nkv <= 8):
+    return 0
+  if batch.num_prefill_tiles or batch.num_decode != qkv.shape[0] or batch.num_decode == 0:
+    return 0
+  if cos_sin is not None and (cos_sin.shape[1] != hd or cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous()):
+    return 0
+  if os.environ.get("MINIINFER_B200_ROPE_IN_ATTENTION", "1") == "0" or os.environ.get("MINIINFER_B200_DECODE_TMA", "1") == "0":
+    return 0
+  lib = attention_lib(hd)
+  span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
+  return decode_cluster_size(lib, hd, batch.num_decode, nkv, span)
+
+
+def rope_store_attention(out: torch.Tensor, qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                         cos_sin: Optional[torch.Tensor], positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                         kv_layer: torch.Tensor, writes: bool, block_table: torch.Tensor, batch: AttentionBatch,
+                         num_heads: int, num_kv_heads: int, head_dim: int, eps: float, scale: float, window: Optional[int]) -> None:
+  """From the fused QKV rows of a step to its attention output: ``qk_norm_rope_store`` (which also puts the new
+  keys and values into the layer's pages, if ``writes``) followed by ``attention``.  A step of a few decode tokens
+  takes one kernel for both (attention_decode_cluster.cu), which does the first step's arithmetic operation for
+  operation: the results are the same bit for bit, except that ``qkv`` is then left as the product wrote it."""
+  win = int(window) if window else 0
+  page_size = kv_layer.shape[3] if kv_layer is not None and kv_layer.dim() == 5 else 0
+  cluster = _rope_in_attention(qkv, cos_sin, kv_layer, batch, num_heads, num_kv_heads, head_dim, win, page_size) if page_size else 0
+  if not cluster:
+    qk_norm_rope_store(qkv, q_weight, k_weight, cos_sin, positions, slot_mapping if writes else None,
+                       kv_layer if writes else None, num_heads, num_kv_heads, head_dim, eps)
+    attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, window)
+    return
+  T = qkv.shape[0]
+  if out.shape != (T, num_heads * head_dim) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype:
+    raise KernelError("rope_store_attention: shapes or dtypes do not match")
+  if kv_layer.shape[1:] != (2, num_kv_heads, page_size, head_dim) or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+    raise KernelError(f"rope_store_attention: cache layer {tuple(kv_layer.shape)} or qkv {tuple(qkv.shape)} do not match the head counts")
+  lib = attention_lib(head_dim)
+  if batch.scratch is not None:
+    status = batch.scratch.zeros("attention_decode_counters", batch.num_decode * num_kv_heads + 1, torch.int32)[:1]
+  else:
+    status = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+  none = _ptr(None)
+  _check(lib, lib.mi_attention_decode_cluster_rope(
+    _ptr(out), _ptr(qkv), qkv.shape[1], _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
+    _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
+    _ptr(batch.seq_slot, torch.int32), _ptr(status, torch.int32), batch.num_decode, num_heads, num_kv_heads, page_size,
+    ctypes.c_float(scale), win, cluster, batch.max_ctx_len,
+    _ptr(q_weight, torch.float32) if q_weight is not None else none, _ptr(k_weight, torch.float32) if k_weight is not None else none,
+    _ptr(cos_sin, torch.float32) if cos_sin is not None else none,
+    _ptr(slot_mapping, torch.int32) if (writes and slot_mapping is not None) else none,
+    _ptr(kv_layer) if writes else none, ctypes.c_float(eps), _stream()))
+  if batch.scratch is None and int(status[0]) != 0:
+    raise KernelError("attention_decode_cluster: a bounded wait on a copy barrier ran out")
+
+
 DECODE_CHUNKS = (512, 256, 128, 64)
 def decode_chunk(num_decode: int, num_kv_heads: int, max_ctx_len: int, head_dim: int) -> int:
   """Keys per block of the cp.async split-KV decode kernel: the longest chunk that still gives every

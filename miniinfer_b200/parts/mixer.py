@@ -150,11 +150,8 @@ class AttentionMixer(Mixer):
     table = self.position.rotary_table() if self.position is not None else None
     qn = self.q_norm if self.qk_norm_eps is not None else None
     kn = self.k_norm if self.qk_norm_eps is not None else None
-    ops.qk_norm_rope_store(qkv, qn, kn, table, ctx.positions,
-                           ctx.slot_mapping[cache.group] if cache.writes else None,
-                           cache.tensor if cache.writes else None, nh, nkv, hd,
-                           self.qk_norm_eps if self.qk_norm_eps is not None else 1.0)
     attn = ctx.ws.buffer("attn_out", (T, nh * hd), ctx.dtype)
-    ops.attention(attn, qkv, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), nh, nkv, hd,
-                  self.scale, self.window)
+    ops.rope_store_attention(attn, qkv, qn, kn, table, ctx.positions, ctx.slot_mapping[cache.group], cache.tensor,
+                             cache.writes, ctx.block_tables[cache.group], self._batch(ctx), nh, nkv, hd,
+                             self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.scale, self.window)
     return attn

@@ -226,6 +226,50 @@ def test_decode_attention_in_clusters(ops, monkeypatch, cluster, nh, nkv, hd, wi
   assert (out.float() - want.float()).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("nh,nkv,window,with_norm,with_table,writes", [(16, 8, None, True, True, True), (6, 2, 700, True, True, True),
+                                                                       (8, 8, None, False, True, True), (4, 2, None, True, False, True),
+                                                                       (16, 8, None, True, True, False)])
+def test_decode_attention_that_norms_rotates_and_stores_itself(ops, monkeypatch, cluster, nh, nkv, window, with_norm, with_table, writes):
+  """A step of decode tokens through the one kernel that norms and rotates q and k, stores the new token's k and v
+  and attends, against the two kernels it stands for: the same output rows and the same cache, bit for bit, at every
+  cluster size, with and without norm weights, rotation table, window and cache store."""
+  hd, P = 128, 64
+  monkeypatch.setenv("MINIINFER_B200_DECODE_CLUSTER", str(cluster))
+  items = [(3000, 1), (1, 1), (64, 1), (65, 1), (1500, 1), (700, 1), (2049, 1), (128, 1)]
+  qkv0, kv0, bt, batch = make_attention_case(items, nh, nkv, hd, P, torch.bfloat16, seed=cluster, num_slots=9)
+  qw = (1 + 0.1 * rnd(hd, seed=3)) if with_norm else None
+  kw = (1 + 0.1 * rnd(hd, seed=4)) if with_norm else None
+  table = None
+  if with_table:
+    ang = torch.arange(3100, device=DEV)[:, None].float() * (10000.0 ** (-torch.arange(hd // 2, device=DEV).float() / (hd // 2)))[None, :]
+    table = torch.cat((ang.cos(), ang.sin()), dim=1).contiguous()
+  slots = torch.tensor([int(bt[int(batch.seq_slot[b]), (c - 1) // P]) * P + (c - 1) % P for b, (c, _) in enumerate(items)],
+                       dtype=torch.int32, device=DEV)
+  eps, scale = 1e-6, hd ** -0.5
+  results = []
+  for fused in ("1", "0"):
+    monkeypatch.setenv("MINIINFER_B200_ROPE_IN_ATTENTION", fused)
+    qkv, kv = qkv0.clone(), kv0.clone()
+    out = torch.full((len(items), nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.rope_store_attention(out, qkv, qw, kw, table, batch.positions, slots, kv, writes, bt, batch, nh, nkv, hd, eps, scale, window)
+    assert torch.isfinite(out.float()).all()
+    results.append((out, kv, qkv))
+  (out1, kv1, qkv1), (out0, kv0_, qkv0_) = results
+  assert torch.equal(qkv1, qkv0), "the one kernel leaves the rows as the product wrote them"
+  assert not torch.equal(qkv0_, qkv0) or not (with_norm or with_table)
+  assert torch.equal(kv1, kv0_), "the cache"
+  assert torch.equal(out1, out0), "the output rows"
+  if not writes:
+    assert torch.equal(kv1, kv0)
+  # and both against the statements
+  qkv, kv = qkv0.clone(), kv0.clone()
+  ref.qk_norm_rope_store(qkv, qw, kw, table, batch.positions, slots if writes else None, kv if writes else None, nh, nkv, hd, eps)
+  want = torch.empty_like(out1)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, scale, window)
+  assert (out1.float() - want.float()).abs().max() < 3e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
   """Random data would hide a key that is skipped: make one key's score stand out."""
