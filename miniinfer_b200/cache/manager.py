@@ -164,11 +164,23 @@ class _Request:
   pages: List[List[int]] = field(default_factory=list)   # per paged group: page ids by index, 0 = given back
 
 
+def pages_in_flight(window: int, page_size: int, max_step_tokens: int) -> int:
+  """The most pages a request holds in a group that keeps the last ``window`` positions: the window, what up to two
+  steps of ``max_step_tokens`` tokens add before the first of them is committed and the pages behind the window go
+  back, and one page for where the window starts inside a page."""
+  return -(-(window + 2 * max_step_tokens) // page_size) + 1
+
+
 class KVCacheManager:
-  """``layer_specs[i]`` is the need of cache layer ``i`` (None: the layer keeps nothing)."""
+  """``layer_specs[i]`` is the need of cache layer ``i`` (None: the layer keeps nothing).
+
+  ``num_pages`` is the size of a group that keeps every key.  A group that keeps a window needs no more than its
+  requests can hold at a time: with ``max_step_tokens`` (the most tokens a request gets in one step) such a group
+  gets ``max_num_seqs * pages_in_flight(window, ...)`` pages, if that is less."""
 
   def __init__(self, layer_specs: Sequence[Optional[CacheSpec]], page_size: int, num_pages: int,
-               max_num_seqs: int, max_model_len: int, dtype: torch.dtype, device="cpu"):
+               max_num_seqs: int, max_model_len: int, dtype: torch.dtype, device="cpu",
+               max_step_tokens: Optional[int] = None):
     self.page_size = page_size
     self.max_num_seqs = max_num_seqs
     self.max_model_len = max_model_len
@@ -184,7 +196,8 @@ class KVCacheManager:
     place: Dict[int, tuple] = {}
     for spec, layers in by_spec.items():
       if isinstance(spec, PagedKVSpec):
-        g = PagedGroup(len(self.paged_groups), spec, len(layers), page_size, num_pages,
+        g = PagedGroup(len(self.paged_groups), spec, len(layers), page_size,
+                       self.group_pages(spec, page_size, num_pages, max_num_seqs, max_step_tokens),
                        max_num_seqs, max_model_len, dtype, device)
         self.paged_groups.append(g)
         for j, layer in enumerate(layers):
@@ -204,12 +217,21 @@ class KVCacheManager:
   # ------------------------------------------------------------------ sizing
 
   @staticmethod
-  def bytes_per_page(layer_specs: Sequence[Optional[CacheSpec]], page_size: int, dtype: torch.dtype) -> int:
-    """Bytes that one more page in every paged group costs."""
+  def group_pages(spec: PagedKVSpec, page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int]) -> int:
+    """Pages of the group of ``spec`` when a group that keeps every key has ``num_pages``."""
+    if spec.window is None or max_step_tokens is None:
+      return num_pages
+    return min(num_pages, max_num_seqs * pages_in_flight(spec.window, page_size, max_step_tokens))
+
+  @staticmethod
+  def bytes_per_page(layer_specs: Sequence[Optional[CacheSpec]], page_size: int, dtype: torch.dtype,
+                     windowed: Optional[bool] = None) -> int:
+    """Bytes that one more page costs in every paged group (``windowed`` None), in the groups that keep a window
+    (True) or in those that keep every key (False)."""
     size = torch.empty((), dtype=dtype).element_size()
     total = 0
     for spec in layer_specs:
-      if isinstance(spec, PagedKVSpec):
+      if isinstance(spec, PagedKVSpec) and (windowed is None or windowed == (spec.window is not None)):
         total += 2 * spec.num_kv_heads * spec.head_dim * page_size * size
     return total
 

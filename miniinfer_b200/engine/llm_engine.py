@@ -21,6 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import KVCacheManager
+from ..cache.specs import PagedKVSpec
 from ..config import EngineConfig, build_model_spec, load_model_config
 from ..sampling import Sampler, SamplingParams, derive_seed
 from ..utils.crash_dump import dump_step_failure
@@ -34,22 +35,33 @@ logger = get_logger(__name__)
 
 
 def size_cache_pages(layer_specs, page_size: int, dtype: torch.dtype, device: torch.device,
-                     utilization: float, max_num_seqs: int, max_model_len: int) -> int:
-  """Pages per group from the memory that is free now (the reference: a share of the free memory
-  divided by the bytes of one token, miniinfer/utils/memory_utils.py:85-144), capped at what
-  ``max_num_seqs`` requests of ``max_model_len`` tokens could ever hold."""
-  per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype)
+                     utilization: float, max_num_seqs: int, max_model_len: int, max_step_tokens: Optional[int] = None) -> int:
+  """Pages of a group that keeps every key, from the memory that is free now (the reference: a share of the free
+  memory divided by the bytes of one token, miniinfer/utils/memory_utils.py:85-144), capped at what ``max_num_seqs``
+  requests of ``max_model_len`` tokens could ever hold.  Groups that keep a window have a size of their own
+  (``KVCacheManager.group_pages``), which is taken off the memory first."""
   cap = max_num_seqs * (-(-max_model_len // page_size))
-  if per_page == 0:
+  if KVCacheManager.bytes_per_page(layer_specs, page_size, dtype) == 0:
     return 1
   if device.type != "cuda":
     return cap
   free, total = torch.cuda.mem_get_info(device)
-  usable = free - (1.0 - utilization) * total
-  pages = int(usable * 0.9) // per_page
+  usable = int((free - (1.0 - utilization) * total) * 0.9)
+  per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype, windowed=False)
+  if max_step_tokens is None:
+    per_page = KVCacheManager.bytes_per_page(layer_specs, page_size, dtype)
+  else:
+    size = torch.empty((), dtype=dtype).element_size()
+    for spec in layer_specs:
+      if isinstance(spec, PagedKVSpec) and spec.window is not None:
+        pages = KVCacheManager.group_pages(spec, page_size, cap, max_num_seqs, max_step_tokens) + 1
+        usable -= pages * 2 * spec.num_kv_heads * spec.head_dim * page_size * size
+  if per_page == 0:
+    return cap
+  pages = usable // per_page
   if pages < 2:
     raise RuntimeError(f"not enough free device memory for the cache: {free >> 20} MiB free, "
-                       f"one page costs {per_page >> 10} KiB")
+                       f"one page of the groups that keep every key costs {per_page >> 10} KiB")
   return min(pages, cap)
 
 
@@ -84,12 +96,13 @@ class LLMEngine:
     logger.info("weights ready in %.1f s", time.time() - t0)
     cfg.max_context_len = min(cfg.max_context_len, self.model_config.max_position_embeddings)
     layer_specs = self.spec.cache_layer_specs()
+    max_step_tokens = max(1, min(cfg.max_num_batched_tokens, cfg.chunked_prefill_size))   # the most a request gets in one step
     num_pages = cfg.num_pages
     if num_pages is None:
       num_pages = size_cache_pages(layer_specs, cfg.page_size, cfg.dtype, self.device, cfg.gpu_memory_utilization,
-                                   cfg.max_num_seqs, cfg.max_context_len)
+                                   cfg.max_num_seqs, cfg.max_context_len, max_step_tokens)
     self.cache = KVCacheManager(layer_specs, cfg.page_size, num_pages, cfg.max_num_seqs, cfg.max_context_len,
-                                cfg.dtype, self.device)
+                                cfg.dtype, self.device, max_step_tokens=max_step_tokens)
     self.runner = ModelRunner(self.spec, self.cache, cfg.dtype, self.device)
     self.scheduler = Scheduler(self.cache, cfg.max_num_seqs, cfg.max_num_batched_tokens, cfg.chunked_prefill_size,
                                cfg.max_context_len, self.model_config.eos_ids())

@@ -100,6 +100,39 @@ def test_window_gives_pages_back_as_it_passes():
   m.check_invariants()
 
 
+def test_a_windowed_group_is_as_large_as_its_requests_need():
+  """With the most tokens a request gets in a step known, a group that keeps a window has a pool of its own size;
+  requests that grow to the longest length in steps of that many tokens (two steps in flight before the first is
+  committed) never find it empty, and the group that keeps every key keeps the size it was given."""
+  from miniinfer_b200.cache.manager import pages_in_flight
+  full, win = PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=100)
+  m = KVCacheManager([full, win, full, win], page_size=16, num_pages=1000, max_num_seqs=4, max_model_len=4000,
+                     dtype=torch.float32, max_step_tokens=64)
+  sizes = {g.spec.window: g.num_pages for g in m.paged_groups}
+  assert sizes[None] == 1000 and sizes[100] == 4 * pages_in_flight(100, 16, 64) == 4 * 16
+  same = KVCacheManager([full, win], page_size=16, num_pages=1000, max_num_seqs=4, max_model_len=4000, dtype=torch.float32)
+  assert [g.num_pages for g in same.paged_groups] == [1000, 1000]          # without the bound: one size for all
+  rng = random.Random(3)
+  for r in range(4):
+    m.admit(r)
+  length = {r: 0 for r in range(4)}
+  pending = {r: [] for r in range(4)}
+  while any(length[r] + sum(pending[r]) < 4000 for r in range(4)):
+    for r in range(4):
+      left = 4000 - length[r] - sum(pending[r])
+      if left > 0:
+        n = min(left, rng.randint(1, 64))
+        m.append(r, n)                                    # raises OutOfPages if the pool were too small
+        pending[r].append(n)
+      if len(pending[r]) == 2 or (left <= 0 and pending[r]):    # the older of two steps in flight is done
+        n = pending[r].pop(0)
+        m.commit(r, n)
+        length[r] += n
+    m.check_invariants()
+  used = [g.num_pages - g.allocator.num_free for g in m.paged_groups]
+  assert used[0] == 4 * 250 and used[1] <= 4 * 16
+
+
 def test_state_rows_start_at_zero():
   m = make(extra=[FixedStateSpec((5,))])
   s = m.admit("a")
