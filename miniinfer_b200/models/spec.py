@@ -1,5 +1,9 @@
 """A model as data: its parts and the order in which its layers run.
 
+The frame around the layers is three parts by role - an ``Embedding``, a ``Norm``, a ``Head`` - and the step
+function knows no more of them than the role's one method: an embedding made of several tables, or a head that
+does more than a product, is a part like any other.
+
 ``run_list`` is the order of execution.  An entry names a block (a block may be named more than
 once: its weights then run again, with a cache of their own) and, optionally, an earlier entry
 whose cache it reads instead of keeping one (its mixer then writes nothing).
@@ -12,8 +16,7 @@ from typing import Dict, List, Optional
 
 from ..cache.specs import CacheSpec
 from ..config.model_config import ModelConfig
-from ..parts.base import Block, Norm, Part, PositionEncoding
-from ..parts.embedding import LMHead, TokenEmbedding
+from ..parts.base import Block, Embedding, Head, Norm, Part, PositionEncoding
 
 
 @dataclass(frozen=True)
@@ -25,10 +28,10 @@ class LayerRun:
 @dataclass
 class ModelSpec:
   config: ModelConfig
-  embedding: TokenEmbedding
+  embedding: Embedding             # token ids -> float32 residual rows
   blocks: List[Block]
-  final_norm: Norm
-  lm_head: LMHead
+  final_norm: Norm                 # residual rows (+ what the last block left pending) -> the wanted rows, normed
+  lm_head: Head                    # those rows -> float32 logits
   position_encodings: List[PositionEncoding] = field(default_factory=list)
   run_list: Optional[List[LayerRun]] = None
   # file tensors that may be present without being loaded, each equal to another file tensor

@@ -1,5 +1,5 @@
-from .base import (Block, FeedForward, HostStep, Mixer, Norm, ParamSpec, Part, Piece, PositionEncoding, StepWork,
-                   whole)
+from .base import (Block, Embedding, FeedForward, Head, HostStep, Mixer, Norm, ParamSpec, Part, Piece, PositionEncoding,
+                   StepWork, whole)
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .feedforward import SwiGLUFeedForward

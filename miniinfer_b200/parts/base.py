@@ -202,6 +202,22 @@ class FeedForward(Part):
     raise NotImplementedError
 
 
+class Embedding(Part):
+  """The start of a model's frame: token ids to the float32 residual stream ``[tokens, hidden]`` (a buffer of
+  ``ctx.ws``).  Any number of tables or none: the step function only calls ``forward``."""
+
+  def forward(self, ids: torch.Tensor, ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+
+class Head(Part):
+  """The end of a model's frame: the rows the final norm wrote (``[wanted rows, hidden]``) to float32 logits
+  ``[wanted rows, vocabulary]``."""
+
+  def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    raise NotImplementedError
+
+
 class Block(Part):
   def mixer_part(self) -> Optional[Mixer]:
     return None

@@ -14,10 +14,10 @@ from typing import Dict, Optional
 import torch
 
 from ..kernels import ops
-from .base import ParamSpec, Part, whole
+from .base import Embedding, Head, ParamSpec, whole
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
   def __init__(self, name: str, vocab_size: int, hidden_size: int):
     super().__init__(name)
     self.vocab_size = vocab_size
@@ -33,7 +33,7 @@ class TokenEmbedding(Part):
     return out
 
 
-class LMHead(Part):
+class LMHead(Head):
   def __init__(self, name: str, vocab_size: int, hidden_size: int, tied_to: Optional[TokenEmbedding] = None):
     super().__init__(name)
     self.vocab_size = vocab_size

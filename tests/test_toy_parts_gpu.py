@@ -3,7 +3,8 @@ change to the package: a feed-forward with routing (a router in float32 picks tw
 experts per token), a learned absolute position encoding that acts on the hidden state after the
 embedding, and a model whose layers differ - the package's attention (no rotation, no QK norm) with
 a dense feed-forward in one layer, the toy mixer with state and the routed feed-forward in the other.
-The run list names the first block twice.  Compared with a plain whole-sequence statement under
+The frame is the test's own too: an embedding that adds two tables (tokens, and token classes) and a head
+that caps its logits softly.  The run list names the first block twice.  Compared with a plain whole-sequence statement under
 every way of cutting the requests into steps."""
 from dataclasses import dataclass
 from typing import Dict
@@ -23,9 +24,41 @@ def define_parts():
   from miniinfer_b200.config.model_config import ModelConfig
   from miniinfer_b200.config.registry import _MODELS
   from miniinfer_b200.models import LayerRun, ModelSpec
-  from miniinfer_b200.parts import (FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, AttentionMixer, FeedForward, LMHead,
+  from miniinfer_b200.kernels import ops
+  from miniinfer_b200.parts import (FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, AttentionMixer, Embedding, FeedForward, Head,
                                     ParamSpec, PositionEncoding, PreNormBlock, RMSNorm, SwiGLUFeedForward,
-                                    TokenEmbedding, make, register_feed_forward, register_position_encoding, whole)
+                                    make, register_feed_forward, register_position_encoding, whole)
+
+  class TwoTableEmbedding(Embedding):
+    """hidden_t = tokens[id_t] + classes[id_t mod num_classes]: a frame that starts from more than one table."""
+
+    def __init__(self, name, vocab_size, hidden_size, num_classes):
+      super().__init__(name)
+      self.vocab_size, self.hidden_size, self.num_classes = vocab_size, hidden_size, num_classes
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+      V, H, C = self.vocab_size, self.hidden_size, self.num_classes
+      return {"tokens": ParamSpec((V, H), "table", [whole(f"{self.name}.tokens", (V, H))]),
+              "classes": ParamSpec((C, H), "table", [whole(f"{self.name}.classes", (C, H))])}
+
+    def forward(self, ids, ctx):
+      out = ctx.ws.buffer("resid", (ids.shape[0], self.hidden_size), torch.float32)
+      ops.embedding(out, self.tokens, ids)
+      out += self.classes[(ids % self.num_classes).long()].float()
+      return out
+
+  class SoftCapHead(Head):
+    """logits = cap * tanh((x W^T) / cap), W the embedding's token table."""
+
+    def __init__(self, name, vocab_size, hidden_size, cap, tied_to):
+      super().__init__(name)
+      self.vocab_size, self.hidden_size, self.cap, self.tied_to = vocab_size, hidden_size, cap, tied_to
+
+    def forward(self, x, ctx):
+      out = ctx.ws.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
+      ops.linear(out, x, self.tied_to.tokens)
+      out.copy_(self.cap * torch.tanh(out / self.cap))
+      return out
 
   if "toy_routed" not in FEED_FORWARDS:
     @register_feed_forward("toy_routed")
@@ -88,12 +121,14 @@ def define_parts():
     decay: float = 0.25
     rms_norm_eps: float = 1e-5
     num_positions: int = 160
+    num_classes: int = 7
+    logit_cap: float = 3.0
 
   if "ToyPartsLM" not in _MODELS:
     @register_model("ToyPartsLM", ToyPartsConfig)
     def build(cfg):
       H = cfg.hidden_size
-      emb = TokenEmbedding("emb", cfg.vocab_size, H)
+      emb = TwoTableEmbedding("emb", cfg.vocab_size, H, cfg.num_classes)
       pos = make(POSITION_ENCODINGS, "toy_learned", "pos", H, cfg.num_positions)
       attn = AttentionMixer("l0.attn", H, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.head_dim ** -0.5, None, None)
       b0 = PreNormBlock("l0", RMSNorm("l0.n1", H, cfg.rms_norm_eps), attn, RMSNorm("l0.n2", H, cfg.rms_norm_eps),
@@ -103,7 +138,7 @@ def define_parts():
                         make(FEED_FORWARDS, "toy_routed", "l1.moe", H, cfg.expert_size, cfg.num_experts, cfg.top_k))
       # the attention block runs twice, with a cache of its own each time
       return ModelSpec(config=cfg, embedding=emb, blocks=[b0, b1], final_norm=RMSNorm("norm", H, cfg.rms_norm_eps),
-                       lm_head=LMHead("head", cfg.vocab_size, H, tied_to=emb), position_encodings=[pos],
+                       lm_head=SoftCapHead("head", cfg.vocab_size, H, cfg.logit_cap, emb), position_encodings=[pos],
                        run_list=[LayerRun(0), LayerRun(1), LayerRun(0)])
   return ToyPartsConfig
 
@@ -113,7 +148,7 @@ def plain_parts_model(w, cfg, ids):
   import plain_qwen3 as plain
   T, H = len(ids), cfg["hidden_size"]
   nh, nkv, hd = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
-  res = w["emb.weight"][torch.tensor(ids)] + w["pos.table"][:T]
+  res = w["emb.tokens"][torch.tensor(ids)] + w["emb.classes"][torch.tensor(ids) % cfg["num_classes"]] + w["pos.table"][:T]
 
   def attention_block(res, pending):
     if pending is not None:
@@ -152,7 +187,7 @@ def plain_parts_model(w, cfg, ids):
   res, pending = decay_block(res, pending)
   res, pending = attention_block(res, pending)
   x = plain.rms_norm(pending + res, w["norm.weight"], cfg["rms_norm_eps"])
-  return x @ w["emb.weight"].t()
+  return cfg["logit_cap"] * torch.tanh((x @ w["emb.tokens"].t()) / cfg["logit_cap"])
 
 
 def test_toy_parts_run_through_the_engine(tmp_path):
@@ -163,7 +198,7 @@ def test_toy_parts_run_through_the_engine(tmp_path):
   from miniinfer_b200.weights import write_random_model
   cfg = dict(architectures=["ToyPartsLM"], model_type="toy_parts", vocab_size=101, max_position_embeddings=160, hidden_size=48,
              num_heads=3, num_kv_heads=1, head_dim=16, intermediate_size=40, expert_size=24, num_experts=4, top_k=2,
-             decay=0.25, rms_norm_eps=1e-5, num_positions=160)
+             decay=0.25, rms_norm_eps=1e-5, num_positions=160, num_classes=7, logit_cap=3.0)
   d = write_random_model(cfg, str(tmp_path / "toy_parts"), seed=4, dtype=torch.float32)
   weights = plain.read_weights(d)
   reqs = rc.make_requests(101, (70, 33, 12, 5), seed=2)
