@@ -145,7 +145,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
       w1 = *reinterpret_cast<const float2*>(w + HALF + j);
     }
     if (a.cos_sin) {
-      const float* cs = a.cos_sin + (size_t)p * HD;
+      const float* cs = a.cos_sin + (size_t)max(p, 0) * HD;    // (an item without a token, p = -1, has no tile either)
       c = *reinterpret_cast<const float2*>(cs + j);
       sn = *reinterpret_cast<const float2*>(cs + HALF + j);
       has_table = true;
