@@ -5,16 +5,17 @@
 // the weights from HBM and the question is only how evenly and how deeply the SMs keep asking for
 // them.  The product is turned around: 128 weight rows are the rows of the tensor-core tile (its A
 // operand, lanes of tensor memory), the activation rows its 16 columns.
-//   * The work is the list of (tile of 128 weight rows, slice of 128 elements of K), tile after tile.
+//   * The work is the list of (tile of 128 weight rows, slice of 256 elements of K), tile after tile.
 //     Each of the persistent blocks - one per SM - takes an equal, contiguous stretch of that list,
 //     whatever tiles it cuts: every SM streams the same number of bytes and all end together.  A block
 //     starts with the tiles its stretch cuts and goes on to the whole tiles between them.
-//   * warp 0, one thread: asks the TMA engine for the slices - two boxes of 64 weight rows x 64
-//     elements for each half of a slice, and the 16 x 64 box of the activations beside them - into a
-//     ring of three stages of 36 KB, 128-byte swizzled as the tensor cores read them.  The weight
-//     boxes of the first three slices are asked for at once, before the block has met and before the
-//     kernel waits for its predecessor in the stream: no kernel writes weights.
-//   * warp 1, one thread: eight tcgen05.mma (M = 128, N = 16, K = 16) per slice into one of two
+//   * warp 0 asks the TMA engine for the slices, a lane per copy - eight boxes of 64 weight rows x 64
+//     elements (512 bytes of each row at a time: slices of 128 elements streamed 5 % slower) and
+//     four 16 x 64 boxes of the activations beside them - into a ring of three stages of 72 KB,
+//     128-byte swizzled as the tensor cores read them.  The weight boxes of the first three slices are
+//     asked for at once, before the block has met and before the kernel waits for its predecessor in
+//     the stream: no kernel writes weights.
+//   * warp 1, one thread: sixteen tcgen05.mma (M = 128, N = 16, K = 16) per slice into one of two
 //     accumulators of 16 columns of tensor memory; tcgen05.commit hands the stage back and, at the end
 //     of a stretch of one tile, the accumulator over.
 //   * warps 2-5, a thread per weight row: read the accumulator (tcgen05.ld), and either store the 16
@@ -28,15 +29,17 @@
 // activation, as the product followed by the activation kernel rounds them.
 //
 // Measured on B200 with 8 rows, cold weights, launches chained in a graph (this kernel / the mma.sync kernel
-// of gemm_skinny.cuh): 5120 x 25600 (262 MB) 51.0 / 64.8 us, SwiGLU 2 x 25600 x 5120 (524 MB) 89.0 / 93.3 us,
-// SwiGLU 2 x 12288 x 4096 (201 MB) 40.8 / 41.9 us, 151936 x 1024 (311 MB) 55.1 / 56.6 us; but 4096 x 12288
-// (101 MB) 24.8 / 19.9 us, 6144 x 4096 (50 MB) 15.9 / 11.6 us, 4096 x 1024 (8 MB) 8.5 / 2.8 us.  Both stream at
-// about 5.7 TB/s once they run.  What this kernel adds is the even split - the other kernel's blocks make 2.2
-// rounds over the SMs for 10240 weight rows, or fill 72 % of them for 5120 - and what it costs is its start and
-// its end: 1.2 us until tensor memory is allocated and the block has met, 3 us from the first request to the first
-// slice, and for a matrix with fewer tiles than SMs every sum goes through the workspace, a round trip of
-// 3 to 5 us.  So the engine takes it from 160 MB of weights on (ops.STREAM_TC_MIN_BYTES): a decode step of the
-// Qwen3-32B shape goes from 1.717 to 1.618 ms (6 layers and the head, batch 8).
+// of gemm_skinny.cuh / the library's product at 17 rows): 5120 x 25600 (262 MB) 49.2 / 64.1 / 47.2 us, 10240 x 5120
+// (105 MB) 23.6 / 26.1 / 22.3, SwiGLU 2 x 25600 x 5120 (524 MB) 84.3 / 93.4 / 90.8 (+ the activation), SwiGLU
+// 2 x 12288 x 4096 (201 MB) 38.8 / 41.7 / 37.2 (+ the activation), 151936 x 1024 (311 MB) 55.1 / 56.2; but 4096 x 12288
+// (101 MB) 23.1 / 19.7 / 22.4, 6144 x 4096 (50 MB) 14.2 / 11.7 / 11.6, 4096 x 1024 (8 MB) 6.2 / 2.8.  Once it runs
+// it streams at 6.0 to 6.6 TB/s (the 1.2 GB head of the 8B shape: 188 us, the mma.sync kernel 216 us, the library
+// 207 us).  What this kernel adds is the even split - the other kernel's blocks make 2.2 rounds over the SMs for
+// 10240 weight rows, or fill 72 % of them for 5120 - and what it costs is its start and its end: 1.2 us until
+// tensor memory is allocated and the block has met, 3 us from the first request to the first slice, and for a
+// matrix with fewer tiles than SMs every sum goes through the workspace, a round trip of 3 to 5 us.  So the engine
+// takes it from 160 MiB of weights on, and from 80 MiB for more than 4096 rows (ops.STREAM_TC_MIN_BYTES): a decode
+// step of the Qwen3-32B shape goes from 15.4 to 13.7 ms at batch 8.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag that ends all other waits
 // of the block, sets the status word to 8, and the block runs to its end, tensor memory freed.
