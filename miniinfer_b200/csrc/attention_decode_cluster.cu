@@ -16,6 +16,9 @@
 //     result in its own shared memory, the cluster meets at its hardware barrier, and each block
 //     combines a slice of the output rows from all of them.  Nothing goes through global memory but
 //     the output; there are no counters, and no block waits in a loop for another;
+//   * for a step of decode tokens only (head size 128) the kernel also does what otherwise a kernel of
+//     its own does before it - the QK norm, the rotation, the new token's key and value into the cache
+//     (mi_attention_decode_cluster_rope): 2.4 us a layer less at the Qwen3-0.6B shape;
 //   * every wait on a copy's mbarrier is bounded: one that runs out raises a flag that ends the
 //     block's other waits, sets the status word, and the block runs to its end.
 //
