@@ -227,14 +227,15 @@ def test_decode_attention_in_clusters(ops, monkeypatch, cluster, nh, nkv, hd, wi
 
 
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
-@pytest.mark.parametrize("nh,nkv,window,with_norm,with_table,writes", [(16, 8, None, True, True, True), (6, 2, 700, True, True, True),
-                                                                       (8, 8, None, False, True, True), (4, 2, None, True, False, True),
-                                                                       (16, 8, None, True, True, False)])
-def test_decode_attention_that_norms_rotates_and_stores_itself(ops, monkeypatch, cluster, nh, nkv, window, with_norm, with_table, writes):
+@pytest.mark.parametrize("nh,nkv,window,with_norm,with_table,writes,P", [(16, 8, None, True, True, True, 64), (6, 2, 700, True, True, True, 64),
+                                                                         (8, 8, None, False, True, True, 128), (4, 2, None, True, False, True, 64),
+                                                                         (16, 8, None, True, True, False, 64), (16, 2, 100, True, True, True, 256)])
+def test_decode_attention_that_norms_rotates_and_stores_itself(ops, monkeypatch, cluster, nh, nkv, window, with_norm, with_table, writes, P):
   """A step of decode tokens through the one kernel that norms and rotates q and k, stores the new token's k and v
   and attends, against the two kernels it stands for: the same output rows and the same cache, bit for bit, at every
-  cluster size, with and without norm weights, rotation table, window and cache store."""
-  hd, P = 128, 64
+  cluster size, with and without norm weights, rotation table, window and cache store, pages of 64 to 256 tokens,
+  one to eight query heads per kv head."""
+  hd = 128
   monkeypatch.setenv("MINIINFER_B200_DECODE_CLUSTER", str(cluster))
   items = [(3000, 1), (1, 1), (64, 1), (65, 1), (1500, 1), (700, 1), (2049, 1), (128, 1)]
   qkv0, kv0, bt, batch = make_attention_case(items, nh, nkv, hd, P, torch.bfloat16, seed=cluster, num_slots=9)
