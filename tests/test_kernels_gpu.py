@@ -317,7 +317,8 @@ class _Scratch:
 
 
 @pytest.mark.parametrize("N,K,swiglu", [(6144, 4096, False), (4096, 4096, False), (3080, 4104, False), (3072, 4096, True),
-                                          (12288, 2048, True), (2056, 6152, True)])
+                                          (12288, 2048, True), (2056, 6152, True),
+                                          (12288, 4096, True), (10240, 5120, False), (5128, 8200, False)])   # sizes that the engine gives the tcgen05 streaming kernel
 def test_few_rows_times_many_megabytes_of_weights(ops, N, K, swiglu):
   """The few-row product at the sizes of larger models (24 MB of weights and more) against the
   statement; a row's value must not depend on the other rows."""
