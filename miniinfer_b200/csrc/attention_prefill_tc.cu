@@ -66,7 +66,8 @@
 // the barriers of the next tile looked at while this tile's products are issued (40.8 -> 41.7 us in the
 // build that could switch it: the look comes too early to find P written); an issuing thread per
 // stream (46.2 us: the two streams fall into step, both in the softmax and then both on the tensor
-// cores, instead of taking turns).)
+// cores, instead of taking turns).  Nor does the special-function unit bind: with the exponential replaced by a
+// multiply-add (wrong numbers, for the time only) the launch takes as long.)
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
 // ends all later waits at once and sets the status word, and the block runs to its end, where the
