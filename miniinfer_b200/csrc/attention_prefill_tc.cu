@@ -8,66 +8,54 @@
 // one per SM (a block takes all of an SM's tensor memory): the works are dealt out longest first, in
 // rounds that go back and forth over the blocks, and a block's barriers run on from one work to the
 // next, so that the next work's Q and first keys are copied and its first S is computed while the
-// softmax warps finish the work before (2048 tokens of 16 heads: 40.1 -> 38.5 us).  Within a work:
+// softmax warps finish the work before.  Within a work:
 //   * a producer warp asks the TMA engine for the Q rows once and for K and V tile by tile (boxes
 //     of 64 rows x 64 elements, one page and one half of the head size each, written in the
 //     128-byte swizzle), two stages each, counted on mbarriers; K and V are counted apart, since
 //     K is free again as soon as S is computed;
-//   * the key tiles are dealt to two streams, the even and the odd ones.  A stream has an S
-//     accumulator (128 columns of tensor memory), an output accumulator (head size columns), and
-//     a running maximum and sum per row of its own, as if it were a request with half the keys;
-//     the two are merged at the end.  Inside a stream everything follows in order - S, softmax,
-//     P V, S of its next tile - and the two streams take turns on the tensor cores, which so have
-//     the products of one stream to do while the softmax warps of the other work;
-//   * one thread of the MMA warp issues S = Q K^T (tcgen05.mma, M = 128, N = 128, K = 16 per
-//     instruction, operands described in shared memory, K-major) and, once the stream's softmax
-//     warps have written P, O += P V (P from tensor memory, where it overwrites the columns of S
-//     it came from; V from shared memory, MN-major: dims contiguous, as the cache stores it);
-//     tcgen05.commit tells the mbarriers when the products are done;
-//   * eight softmax warps per stream - two threads per query row (tensor-memory lane = row), 64
-//     columns each - read S with tcgen05.ld (once for the maximum, again for the exponentials),
-//     keep the maximum and the sum in float32, base 2 with the scale folded in, and write P in
-//     bf16 back into tensor memory.  The output row stays in tensor memory; it is rescaled there
-//     only when a row's maximum moves up by more than 2^8 (until then sums and P are taken
-//     against the older maximum, which costs no accuracy in float32 and bf16), and read once at
-//     the end.
-// Causal and window masks go by absolute position; tiles that the mask does not touch skip the
-// comparisons.  Rows past the end of the item's tokens are computed on whatever the Q copy brought
-// and never stored.
+//   * the key tiles are dealt to two streams, the even and the odd ones.  A stream has four softmax
+//     warps, an output accumulator (head size columns of tensor memory), 64 columns for P, and a running
+//     maximum and sum per row of its own, as if it were a request with half the keys; the two are merged
+//     at the end;
+//   * S = Q K^T of every tile goes into ONE buffer of 128 columns.  A softmax thread owns a query row (its
+//     lane of tensor memory): it reads the row's 128 scores into registers with one tcgen05.ld and hands
+//     the buffer back at once, so the S of the next tile - the other stream's - follows as soon as its K
+//     is there, whatever the P V products do.  One thread issues the S products (tcgen05.mma, M = 128,
+//     N = 128, K = 16, operands described in shared memory, K-major);
+//   * the softmax thread then works in registers: the mask (only in tiles that it touches: the scores a
+//     row may not see are set to -inf once), the maximum, the exponentials in float32, base 2 with the
+//     scale folded in, the sum, and P in bf16 into the stream's own columns.  The output row stays in
+//     tensor memory; it is rescaled there only when a row's maximum moves up by more than 2^8 (until then
+//     sums and P are taken against the older maximum, which costs no accuracy in float32 and bf16), and
+//     read once at the end;
+//   * a second thread issues O += P V (P from tensor memory, V from shared memory, MN-major: dims
+//     contiguous, as the cache stores it) when a stream's P is written; tcgen05.commit tells the
+//     mbarriers when products are done.  Nothing orders an S behind a P V any more, and the softmax warps
+//     of a stream go from one tile to the next without waiting for either;
+//   * at the end of a work each thread reads its half of the two streams' output rows with one wait, and
+//     the rows go to global memory through shared memory, so that a store of the warp covers whole
+//     128-byte lines.
+// Causal and window masks go by absolute position.  Rows past the end of the item's tokens are computed on
+// whatever the Q copy brought and never stored.
 //
-// (Tried and not kept, at 2048 tokens of 16 heads, 40.9 us per launch as it stands: the scores read
-// once and held in registers between the maximum and the exponentials, 44.5 us; the keys of a block
-// split over two blocks, 61 us; every other exponential as a polynomial on the FMA pipe instead
-// of the special-function unit, 45.7 us - the softmax warps wait on the latencies of tensor
-// memory and of each other, not on a pipe, and more instructions only lengthen their path.
-// With persistent blocks, 38.5 us as it stands: one softmax thread per row that reads the row's 128
-// scores once and holds them in registers (four warps per stream, 200 registers a thread by
-// setmaxnreg, no exchange between threads), 96 us - half as many warps hide the latencies of
-// tensor memory and of the exponentials half as well.  Two threads per row that hold their 64
-// scores in registers between the maximum and the exponentials need about 112 registers each; the
-// block is launched with 96 for each of its 640 threads, and setmaxnreg only moves registers that the
-// block already has between its warpgroups - four softmax warpgroups at 112 and the fifth at 56
-// are more than that, and a setmaxnreg.inc that cannot be met waits for ever.  Not built.
-// A timeline of one block (clock64 stamps of the issuing thread and of the softmax warps, 16 tiles of
-// one work) shows what binds: a stream's tile takes S (~600 cycles on the tensor cores), the softmax
-// warps' round (~2600: 1400 for the pass over the scores, where the stream's two warps per scheduler
-// share one special-function unit, 200 for the exchange of maxima, 500 to 800 for the store of P and
-// its wait, 350 for the barriers), P V (~500), and two looks at barriers in between, each of which
-// costs 350 to 600 cycles even when the barrier completed long before: while S products run, the
-// tensor cores read Q and K at the full width of shared memory, and everything else that goes to
-// shared memory queues behind them.  Two such chains, interleaved, give the ~2900 cycles a tile
-// takes; the tensor cores are busy for ~1100 of them.  The issuing thread spends a tile's time as 16
-// products (60 to 80 cycles each), five commits (55 each), a fence (100), the wait for P (600) and the
-// looks at V and the next K.  Tried against that, none faster (38.5 us as it stands): later tiles of a
-// stream in one pass over the scores (exponentials against the old maximum, redone only if the maximum
-// moves by more than 2^8: 38.6 us, and the kernel spills at its 96 registers); one arrival per warp
-// instead of per thread on the barriers the softmax warps complete (no change); the block table read
-// by the whole producer warp, 32 entries at a time (no change: the copies do not wait for those reads);
-// the barriers of the next tile looked at while this tile's products are issued (40.8 -> 41.7 us in the
-// build that could switch it: the look comes too early to find P written); an issuing thread per
-// stream (46.2 us: the two streams fall into step, both in the softmax and then both on the tensor
-// cores, instead of taking turns).  Nor does the special-function unit bind: with the exponential replaced by a
-// multiply-add (wrong numbers, for the time only) the launch takes as long.)
+// How it got here (2048 tokens of 16 heads of 128, microseconds per launch).  The first forms kept an S buffer per
+// stream, with P written over the S it came from: S of a stream's next tile then had to wait for the P V that read
+// that P, and a tile's chain S - softmax - P V ran 5000 to 5800 cycles, two such chains interleaved (40.9; with
+// persistent blocks 38.5; with the block set up before it waits for its predecessor 37.9).  A timeline of one
+// block (clock64 stamps of the issuing thread and the softmax warps) showed what bound it: not a pipe - with the
+// exponential replaced by a multiply-add the launch took as long, the tensor cores were busy ~1100 of ~2900 cycles
+// a tile - but the chain, and in it the one issuing thread, whose every look at a barrier in shared memory costs
+// 350 to 600 cycles while S products read Q and K at the full width of shared memory.  Tried on that form and not
+// faster: the scores held in registers by two threads a row (spills at the 96 registers 18 warps leave), one
+// arrival per warp on the barriers, the block table read 32 entries at a time by the whole producer warp, the
+// next tile's barriers looked at early, an issuing thread per stream (46.2: the streams fall into step), every
+// other exponential as a polynomial (45.7), the keys of a block split over two blocks (61).  One thread per row
+// with the row in registers (10 warps, 168 registers, no exchange between threads) took 40.6 as it was; what it
+// made possible is what counts: the S buffer shared and handed back at once, P in columns of its own (36.8), an
+// issuing thread for S and one for P V (36.1), the mask applied once to the scores instead of in both passes - a
+// masked tile took 6800 cycles against 2000, one warp per scheduler has nobody to hide its instructions behind -
+// (31.5), the epilogue's loads under one wait and its stores through shared memory (30.2).  A tile now takes ~2250
+// cycles, of which the tensor cores are busy ~1800 (P V with P from tensor memory runs at about half the rate of S).
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
 // ends all later waits at once and sets the status word, and the block runs to its end, where the
@@ -80,6 +68,8 @@
 // Compiled once per head size: -DMI_HEAD_DIM=<head size>.
 #include <cuda.h>
 #include <string.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -101,17 +91,19 @@ constexpr int Q_BYTES = NHALF * HALF_BYTES;
 constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
 constexpr int STAGE_BYTES = 2 * K_BYTES;
 constexpr int STREAMS = 2;                      // the key tiles are dealt to two streams (even, odd) with sums of their own
-constexpr int TPR = 2;                          // softmax threads per query row and stream, half of the columns each
-constexpr int COLS = BN / TPR;                  // columns of S per softmax thread
+constexpr int TPR = 1;                          // softmax threads per query row and stream: one, with the whole row of scores in registers
 constexpr int SOFTMAX_WARPS = 4 * TPR * STREAMS;
 constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1;
-constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr int PV_WARP = MMA_WARP + 1;             // the thread that issues the P V products (MMA_WARP's issues the S products)
+constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;
 constexpr int TMEM_COLS = 512;
-// Tensor memory: per stream an S accumulator (128 float32 columns; P overwrites part of it) and an
-// output accumulator (head size columns).
-constexpr int S_COL = 0, O_COL = 256;                  // stream s: S at S_COL + 128 s, O at O_COL + 128 s
+// Tensor memory: one S accumulator (128 float32 columns) that the streams take turns at, and per stream 64 columns
+// of P (bf16, two keys to a column) and an output accumulator (head size columns).
+constexpr int S_COL = 0, P_COL = 128, O_COL = 256;      // S: one buffer both streams take their scores from; stream s: P at P_COL + 64 s, O at O_COL + 128 s
 constexpr int WAIT_LIMIT = 1 << 22;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float);
+constexpr int OUT_ROW_BYTES = HD;                       // a softmax thread's half of an output row in bf16
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float) +
+                              (size_t)SOFTMAX_WARPS * 32 * OUT_ROW_BYTES;
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
@@ -200,18 +192,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
-// 16 consecutive columns of this thread's lane, read.
-__device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 // 32 consecutive columns of this thread's lane, written.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -238,11 +218,49 @@ __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// by the length of the array
-__device__ __forceinline__ void tmem_ld(float (&v)[32], uint32_t taddr) { tmem_ld32(v, taddr); }
-__device__ __forceinline__ void tmem_ld(float (&v)[16], uint32_t taddr) { tmem_ld16(v, taddr); }
-__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
-__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
+// 128 consecutive columns of this thread's lane - a whole row of S - with one wait.
+__device__ __forceinline__ void tmem_ld128(float (&v)[128], uint32_t taddr) {
+  uint32_t r[128];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x128.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127}, [%128];\n"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]), "=r"(r[64]), "=r"(r[65]), "=r"(r[66]), "=r"(r[67]), "=r"(r[68]), "=r"(r[69]), "=r"(r[70]), "=r"(r[71]), "=r"(r[72]), "=r"(r[73]), "=r"(r[74]), "=r"(r[75]), "=r"(r[76]), "=r"(r[77]), "=r"(r[78]), "=r"(r[79]), "=r"(r[80]), "=r"(r[81]), "=r"(r[82]), "=r"(r[83]), "=r"(r[84]), "=r"(r[85]), "=r"(r[86]), "=r"(r[87]), "=r"(r[88]), "=r"(r[89]), "=r"(r[90]), "=r"(r[91]), "=r"(r[92]), "=r"(r[93]), "=r"(r[94]), "=r"(r[95]), "=r"(r[96]), "=r"(r[97]), "=r"(r[98]), "=r"(r[99]), "=r"(r[100]), "=r"(r[101]), "=r"(r[102]), "=r"(r[103]), "=r"(r[104]), "=r"(r[105]), "=r"(r[106]), "=r"(r[107]), "=r"(r[108]), "=r"(r[109]), "=r"(r[110]), "=r"(r[111]), "=r"(r[112]), "=r"(r[113]), "=r"(r[114]), "=r"(r[115]), "=r"(r[116]), "=r"(r[117]), "=r"(r[118]), "=r"(r[119]), "=r"(r[120]), "=r"(r[121]), "=r"(r[122]), "=r"(r[123]), "=r"(r[124]), "=r"(r[125]), "=r"(r[126]), "=r"(r[127])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 128; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Two stretches of this thread's lane, N columns each, with one wait: the two streams' halves of an output row.
+template <int N>
+__device__ __forceinline__ void tmem_ld_pair(float (&v0)[N], float (&v1)[N], uint32_t a0, uint32_t a1) {
+  static_assert(N == 64 || N == 32, "half a head of 128 or of 64");
+  uint32_t r[2 * N];
+  if constexpr (N == 64) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%128];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127}, [%129];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]), "=r"(r[64]), "=r"(r[65]), "=r"(r[66]), "=r"(r[67]), "=r"(r[68]), "=r"(r[69]), "=r"(r[70]), "=r"(r[71]), "=r"(r[72]), "=r"(r[73]), "=r"(r[74]), "=r"(r[75]), "=r"(r[76]), "=r"(r[77]), "=r"(r[78]), "=r"(r[79]), "=r"(r[80]), "=r"(r[81]), "=r"(r[82]), "=r"(r[83]), "=r"(r[84]), "=r"(r[85]), "=r"(r[86]), "=r"(r[87]), "=r"(r[88]), "=r"(r[89]), "=r"(r[90]), "=r"(r[91]), "=r"(r[92]), "=r"(r[93]), "=r"(r[94]), "=r"(r[95]), "=r"(r[96]), "=r"(r[97]), "=r"(r[98]), "=r"(r[99]), "=r"(r[100]), "=r"(r[101]), "=r"(r[102]), "=r"(r[103]), "=r"(r[104]), "=r"(r[105]), "=r"(r[106]), "=r"(r[107]), "=r"(r[108]), "=r"(r[109]), "=r"(r[110]), "=r"(r[111]), "=r"(r[112]), "=r"(r[113]), "=r"(r[114]), "=r"(r[115]), "=r"(r[116]), "=r"(r[117]), "=r"(r[118]), "=r"(r[119]), "=r"(r[120]), "=r"(r[121]), "=r"(r[122]), "=r"(r[123]), "=r"(r[124]), "=r"(r[125]), "=r"(r[126]), "=r"(r[127])
+        : "r"(a0), "r"(a1)
+        : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(a0), "r"(a1)
+        : "memory");
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    v0[i] = __uint_as_float(r[i]);
+    v1[i] = __uint_as_float(r[N + i]);
+  }
+}
+
 
 // Shared-memory operand descriptor, 128-byte swizzle: start address, leading and stride byte offsets
 // in 16-byte units, descriptor version 1 (bits 46..47), layout type 2 = 128-byte swizzle (bits 61..63).
@@ -322,17 +340,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   uint64_t* o_full = p_full + STREAMS;                    // [stream]: its P V is added to the output row
   uint64_t* q_empty = o_full + STREAMS;                   // the work's last S is computed: the Q rows may be replaced
   uint64_t* o_free = q_empty + 1;                         // the work's output rows are read: the next work's P V may overwrite them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 1);
+  uint64_t* s_free = o_free + 1;                          // the scores in the S buffer are in their stream's registers: the next S may overwrite them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(bars + 32);       // [stream][2][TPR][BM]: the maxima the threads of a row tell each other
-  float* fin_l = xch + 2 * STREAMS * TPR * BM;            // [2][stream][TPR][BM]: at the end of a work, each thread's sum
-  float* fin_m = fin_l + 2 * STREAMS * TPR * BM;          // [2][stream][BM]: and each stream's maximum (two works take turns)
+  float* fin_l = reinterpret_cast<float*>(bars + 32);     // [2][stream][BM]: at the end of a work, each thread's sum
+  float* fin_m = fin_l + 2 * STREAMS * BM;                // [2][stream][BM]: and each stream's maximum (two works take turns)
+  unsigned char* out_s = reinterpret_cast<unsigned char*>(fin_l + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM);   // [softmax warp][32 rows][half a row]: output rows on their way to global memory
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
-    mbar_init(o_free, SOFTMAX_WARPS * 32);
+    mbar_init(o_free, SOFTMAX_WARPS);
+    mbar_init(s_free, 4);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -341,7 +361,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
     for (int b = 0; b < STREAMS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 4 * TPR * 32);
+      mbar_init(&p_full[b], 4);
       mbar_init(&o_full[b], 1);
     }
     *abort = 0;
@@ -414,24 +434,47 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       }
     }
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ the thread that issues S = Q K^T
+    // S goes into one buffer of tensor memory that both streams take their scores from: a stream's softmax warps
+    // read their row of a tile into registers at once and hand the buffer back, so S of the next tile - of the
+    // other stream - can follow as soon as that has happened and its K is copied, whatever the P V products do.
     if (lane == 0) {
       constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
-      constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
-      const uint32_t q_addr = smem_u32(q_s);
-      // Tile j of a work belongs to stream j & 1.  The products of a stream follow each other - S, (softmax,)
-      // P V, S of its next tile, ... - and the two streams take turns, so the tensor cores have the
-      // products of one stream to do while the softmax warps of the other work.  The tensor cores
-      // run the products in the order they are issued: P V of a tile (which reads P from the
-      // columns of S) is issued before S of the stream's next tile overwrites them.
-      // What this one thread issues is on the path of both streams, so it is kept short: the
-      // descriptors are made once and stepped by addition (the address field counts 16 bytes), a
-      // barrier that copies complete is looked at before the thread blocks on the softmax warps'
-      // barrier (the look's latency passes meanwhile), and only that barrier - behind which other
-      // threads wrote P with tcgen05.st - is followed by a fence.
-      const uint64_t q_desc = smem_desc(q_addr, 16, 1024);
+      const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
       auto k_step = [](int ks) { return (uint64_t)((ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2); };
-      int gi = 0, it = 0;                                  // key tiles and works so far
+      int gi = 0, it = 0, s_count = 0;                     // key tiles, works and S products so far
+      for (int i = 0;; ++i) {
+        const int w = nth_work(i, me, blocks, total_work);
+        if (w < 0 || *abort) break;
+        const Work k = work_of(a, w);
+        if (k.skip) continue;
+        const int n = k.n;
+        mbar_wait(q_full, it & 1, abort, a.status);
+        for (int j = 0; j < n && !*abort; ++j, ++s_count) {
+          const int g = gi + j, st_ = g % STAGES;
+          const uint32_t k_ready = mbar_peek(&k_full[st_], (g / STAGES) & 1);
+          if (s_count > 0) mbar_wait(s_free, (s_count - 1) & 1, abort, a.status);   // the scores before are in registers
+          if (!k_ready) mbar_wait(&k_full[st_], (g / STAGES) & 1, abort, a.status);
+          if (*abort) break;
+          tc_fence_after();
+          const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * STAGE_BYTES), 16, 1024);
+          const uint32_t d = tmem_base + S_COL;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks)
+            tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
+          tc_commit(&s_full[j & 1]);
+          tc_commit(&k_empty[st_]);
+          if (j == n - 1) tc_commit(q_empty);              // the work's last S: the Q rows are free once it is done
+        }
+        gi += n;
+        ++it;
+      }
+    }
+  } else if (warp == PV_WARP) {
+    // ------------------------------------------------------------------ the thread that issues O += P V
+    if (lane == 0) {
+      constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
+      int gi = 0, it = 0;
       int sb[STREAMS] = {0, 0};                            // tiles of each stream so far
       for (int i = 0;; ++i) {
         const int w = nth_work(i, me, blocks, total_work);
@@ -439,43 +482,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         const Work k = work_of(a, w);
         if (k.skip) continue;
         const int n = k.n;
-        auto issue_s = [&](int li, uint32_t ready) {
-          const int g = gi + li;
-          const int s = g % STAGES, b = li & 1;
-          if (!ready) mbar_wait(&k_full[s], (g / STAGES) & 1, abort, a.status);
-          const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES), 16, 1024);
-          const uint32_t d = tmem_base + S_COL + 128 * b;
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
-          tc_commit(&s_full[b]);
-          tc_commit(&k_empty[s]);
-          if (li == n - 1) tc_commit(q_empty);             // the work's last S: the Q rows are free once it is done
-        };
-        mbar_wait(q_full, it & 1, abort, a.status);
-        if (!*abort) issue_s(0, 0u);
-        if (!*abort && n > 1) issue_s(1, 0u);
         // the output rows in tensor memory are the work before's until its softmax warps have read them
         if (it > 0) mbar_wait(o_free, (it - 1) & 1, abort, a.status);
         for (int j = 0; j < n && !*abort; ++j) {
-          const int g = gi + j;
-          const int s = g % STAGES, b = j & 1;
-          const uint32_t v_ready = mbar_peek(&v_full[s], (g / STAGES) & 1);
-          const uint32_t k_ready = j + 2 < n ? mbar_peek(&k_full[(g + 2) % STAGES], ((g + 2) / STAGES) & 1) : 1u;
+          const int g = gi + j, st_ = g % STAGES, b = j & 1;
+          const uint32_t v_ready = mbar_peek(&v_full[st_], (g / STAGES) & 1);
           mbar_wait(&p_full[b], (sb[b] + j / 2) & 1, abort, a.status);
-          if (!v_ready) mbar_wait(&v_full[s], (g / STAGES) & 1, abort, a.status);
+          if (!v_ready) mbar_wait(&v_full[st_], (g / STAGES) & 1, abort, a.status);
           if (*abort) break;
           tc_fence_after();
-          const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)s * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
-          const uint32_t p_tmem = tmem_base + S_COL + 128 * b;   // thread `ch` of a row leaves its 64 keys in its first 32 columns
+          const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
+          const uint32_t p_tmem = tmem_base + P_COL + 64 * b;   // lane = row, two keys to a column
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks)                   // 16 keys further: 2048 bytes of V
-            tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(64 * (ks >> 2) + 8 * (ks & 3)),
+            tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(8 * ks),
                       v_desc + (uint64_t)(ks * (2048 >> 4)), IDESC_PV,
                       (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over the work's tiles in tensor memory
           tc_commit(&o_full[b]);
-          tc_commit(&v_empty[s]);
-          if (j + 2 < n) issue_s(j + 2, k_ready);
+          tc_commit(&v_empty[st_]);
         }
         gi += n;
         sb[0] += (n + 1) / 2;
@@ -486,17 +510,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   } else {
     // ------------------------------------------------------------------ softmax
     // Warp w: tensor-memory lanes 32 (w & 3) .. + 31 (a warp reaches the lanes of its number mod
-    // 4), half ch = (w >> 2) & 1 of the columns, stream st = w >> 3.  A stream keeps a maximum, a sum
-    // and an output row of its own over its tiles (the even or the odd ones); the two are merged at
-    // the end.  The two threads of a row and stream tell each other their half's maximum through
-    // shared memory, with a barrier of the 64 threads that share the rows.
-    const int q = warp & 3, ch = (warp >> 2) & 1, st = warp >> 3;
+    // 4), stream st = w >> 2; a thread owns a row.  A stream keeps a maximum, a sum and an output row
+    // of its own over its tiles (the even or the odd ones); the two are merged at the end.
+    const int q = warp & 3, st = warp >> 2;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
     const float sc = a.scale_log2;
-    auto row_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + st * 4 + q) : "memory"); };
-    // o_full of the stream completes once per tile of the stream; every thread takes the phases in
-    // order, each at most one tile late, and remembers how many it has seen
     int o_seen = 0;
     auto wait_o = [&](int upto) {
       while (o_seen <= upto) {
@@ -505,8 +524,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       }
       tc_fence_after();
     };
-    const uint32_t s_addr = t_lane + S_COL + 128 * st + ch * COLS;
-    const uint32_t o_addr = t_lane + O_COL + 128 * st + ch * (HD / 2);   // for rescaling: this thread's half of the stream's output row
+    const uint32_t s_addr = t_lane + S_COL;
+    const uint32_t p_addr = t_lane + P_COL + 64 * st;
+    const uint32_t o_addr = t_lane + O_COL + 128 * st;
     int base = 0, it = 0;                                  // tiles of this stream and works so far
 
     for (int i = 0;; ++i) {
@@ -521,139 +541,141 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       const bool row_valid = tok < rows_tok;
       const int pos = row_valid ? start + o + tok : p_last;
       const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-      float m_run = -INFINITY, l_run = 0.f;                // m_run: the maximum the stream's sums are taken against
+      float m_run = -INFINITY, l_run = 0.f;
       const int n_mine = (n - st + 1) / 2;                 // tiles of this stream
 
       for (int k = 0; k < n_mine; ++k) {
         const int j = 2 * k + st;
-        const int kk = base + k;                           // the tile's number among all tiles of this stream and block
-        const int key0 = (t_begin + j) * BN + ch * COLS;   // first key of this thread's columns
-        const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);   // some (row, key) of the tile is hidden
-        // (after a wait has run out the loop goes on without waiting, so that the warps of a row
-        // still meet at every row barrier; what it computes then is never stored)
+        const int kk = base + k;
+        const int key0 = (t_begin + j) * BN;
+        const bool masked = !((t_begin + j) * BN + BN - 1 <= p_first && (t_begin + j) * BN >= lo_last);
         mbar_wait(&s_full[st], kk & 1, abort, a.status);
         tc_fence_after();
-        // first pass over this thread's 64 scores: their maximum
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64 links
-#pragma unroll
-        for (int c = 0; c < COLS / 32; ++c) {
-          float v[32];
-          tmem_ld32(v, s_addr + 32 * c);
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = key0 + 32 * c + e;
-            if (!masked || (key >= lo_r && key <= pos)) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
-          }
-        }
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        float* my_xch = xch + ((st * 2 + (kk & 1)) * TPR) * BM;
-        my_xch[ch * BM + r] = mx;
-        row_sync();
-        mx = fmaxf(mx, my_xch[(ch ^ 1) * BM + r]);
-        // The sums stay relative to the old maximum while the new one is at most 2^8 above it (the
-        // exponentials then stay below 2^8, which float32 sums and bf16 P hold easily); only a larger
-        // move - the first tile, mostly - rescales the sum and the output row in tensor memory.  The
-        // decision is taken for the warp, so that the tensor-memory accesses stay warp-wide; both
-        // threads of a row see the same maxima and decide alike.
-        const float m_new = fmaxf(m_run, mx * sc);         // the scale is positive
-        const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
-        if (__any_sync(0xffffffffu, move)) {
-          const float m_next = move ? m_new : m_run;
-          const float m_to = m_next == -INFINITY ? 0.f : m_next;
-          const float alpha = move ? exp2f(m_run - m_to) : 1.f;   // 0 for a row that had no key yet
-          if (k > 0) {
-            wait_o(kk - 1);                                // the stream's products so far are in its output row
-#pragma unroll
-            for (int c = 0; c < HD / 2 / 32; ++c) {
-              float op[32];
-              tmem_ld32(op, o_addr + c * 32);
-              uint32_t wv[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) wv[e] = __float_as_uint(op[e] * alpha);
-              tmem_st32(o_addr + c * 32, wv);
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-          }
-          l_run *= alpha;
-          m_run = m_next;
-        }
-        const float m_use = m_run == -INFINITY ? 0.f : m_run;
-        // exponentials, their sum, and P in bf16 into tensor memory, where the second product reads
-        // its A operand (lane = row, two keys to a column): this thread's 64 keys go to the first 32
-        // of its own 64 columns of S, which it has read
-        // (32 scores at a time: the first 32 are read before P overwrites the first 16 columns, and
-        // the P of the second 32 goes to the columns 16..31, read by then)
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < COLS / 32; ++c) {
-          float v[32];
-          tmem_ld32(v, s_addr + 32 * c);
-          uint32_t packed[16];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = key0 + 32 * c + e;
-            float x = fmaf(v[e], sc, -m_use);
-            if (masked) x = (key >= lo_r && key <= pos) ? x : -INFINITY;
-            float pe;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
-            v[e] = pe;
-            part[e & 3] += pe;
-          }
-#pragma unroll
-          for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(v[2 * e], v[2 * e + 1]);
-          tmem_st16(s_addr + 16 * c, packed);
-        }
-        l_run += (part[0] + part[1]) + (part[2] + part[3]);
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        // Every phase of o_full is taken no later than one tile after it completes (a waiter two
-        // phases behind would read the parity of the wrong phase).  The product waited for here was
-        // issued a whole tile of the stream ago.
-        if (kk > 0) wait_o(kk - 1);
+        float v[BN];
+        tmem_ld128(v, s_addr);
+        // the scores are in registers: the S buffer may take the next tile's (of either stream)
         tc_fence_before();
-        mbar_arrive(&p_full[st]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+        if (masked) {
+          // A tile that the mask touches: the scores a row may not see are set to -inf once, here, and everything
+          // after treats the tile like any other (a maximum ignores them, their exponentials are 0).  The visible
+          // columns of a row are one stretch, first .. last.
+          int first = lo_r - key0, last = pos - key0;
+          if (last < first) first = BN + 1;                // none: no column passes the test below
+          const unsigned span = (unsigned)(last - first);
+#pragma unroll
+          for (int e = 0; e < BN; ++e) v[e] = (unsigned)(e - first) <= span ? v[e] : -INFINITY;
+        }
+        {
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          const float m_new = fmaxf(m_run, mx * sc);       // the scale is positive
+          const bool move = m_new > m_run + 8.f || m_run == -INFINITY;
+          if (__any_sync(0xffffffffu, move)) {
+            const float m_next = move ? m_new : m_run;
+            const float m_to = m_next == -INFINITY ? 0.f : m_next;
+            const float alpha = move ? exp2f(m_run - m_to) : 1.f;
+            if (k > 0) {
+              wait_o(kk - 1);
+#pragma unroll 1
+              for (int c = 0; c < HD / 32; ++c) {
+                float op[32];
+                tmem_ld32(op, o_addr + c * 32);
+                uint32_t wv[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) wv[e] = __float_as_uint(op[e] * alpha);
+                tmem_st32(o_addr + c * 32, wv);
+              }
+              asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            l_run *= alpha;
+            m_run = m_next;
+          }
+          const float m_use = m_run == -INFINITY ? 0.f : m_run;
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float x = fmaf(v[32 * c + e], sc, -m_use);     // -inf where the row may not see the key
+              float pe;
+              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pe) : "f"(x));
+              v[32 * c + e] = pe;
+              part[e & 3] += pe;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(v[32 * c + 2 * e], v[32 * c + 2 * e + 1]);
+            if (c == 0 && kk > 0) wait_o(kk - 1);          // the product that read the stream's P before has run
+            tmem_st16(p_addr + 16 * c, packed);            // P: two keys to a column
+          }
+          l_run += (part[0] + part[1]) + (part[2] + part[3]);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[st]);
       }
       if (n_mine > 0) wait_o(base + n_mine - 1);
-      // ---- the two streams' sums are merged: every thread leaves its sum (and the stream's maximum)
-      // in shared memory, all softmax warps meet, and each thread finishes a quarter of the output row
-      float* fl = fin_l + (it & 1) * STREAMS * TPR * BM;
+      // ---- the two streams' sums are merged: every thread leaves its sum and maximum in shared memory, all
+      // softmax warps meet, and each thread finishes half of its row's output
+      float* fl = fin_l + (it & 1) * STREAMS * BM;
       float* fm = fin_m + (it & 1) * STREAMS * BM;
-      fl[(st * TPR + ch) * BM + r] = l_run;
-      if (ch == 0) fm[st * BM + r] = m_run;
+      fl[st * BM + r] = l_run;
+      fm[st * BM + r] = m_run;
       tc_fence_before();
       asm volatile("bar.sync 9, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");
       tc_fence_after();
       const float m0 = fm[r], m1 = fm[BM + r];
       const float m_all = fmaxf(m0, m1);
-      const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);     // a stream without tiles, or without a visible key, counts nothing
+      const float w0 = m0 == -INFINITY ? 0.f : exp2f(m0 - m_all);
       const float w1 = m1 == -INFINITY ? 0.f : exp2f(m1 - m_all);
-      const float l_all = (fl[r] + fl[BM + r]) * w0 + (fl[2 * BM + r] + fl[3 * BM + r]) * w1;
-      constexpr int OD = HD / 4;                           // output columns of this thread: 32 or 16
-      const int part_no = st * 2 + ch;
+      const float l_all = fl[r] * w0 + fl[BM + r] * w1;
+      constexpr int OD = HD / 2;                           // output columns of this thread
+      const bool has1 = n > 1;
+      const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
+      (void)head; (void)row_valid;
       float o0[OD], o1[OD];
-      const bool has1 = n > 1;                             // the second stream has an output row only if it had a tile
-      tmem_ld(o0, t_lane + O_COL + part_no * OD);
       if (has1) {
-        tmem_ld(o1, t_lane + O_COL + 128 + part_no * OD);
+        tmem_ld_pair<OD>(o0, o1, t_lane + O_COL + st * OD, t_lane + O_COL + 128 + st * OD);
       } else {
-#pragma unroll
-        for (int e = 0; e < OD; ++e) o1[e] = 0.f;
+        tmem_ld_pair<OD>(o0, o1, t_lane + O_COL + st * OD, t_lane + O_COL + st * OD);
       }
       // the output rows are in registers: the next work's products may overwrite them in tensor memory
       tc_fence_before();
-      mbar_arrive(o_free);
-      if (row_valid && !*abort) {
-        const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
-        __nv_bfloat16* dst = a.out + (size_t)(wk.row0 + tok) * a.nh * HD + (size_t)head * HD + part_no * OD;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
+      // A thread's half row goes through shared memory (16-byte chunks, swizzled by the row), so that a store of
+      // the warp covers whole 128-byte lines of four rows instead of 16 bytes of each of 32 rows.
+      constexpr int CH = OUT_ROW_BYTES / 16;               // chunks of a half row: 8 (head size 128) or 4
+      unsigned char* mine = out_s + (size_t)warp * 32 * OUT_ROW_BYTES;
 #pragma unroll
-        for (int d = 0; d < OD; d += 8) {
-          uint4 wv;
-          wv.x = pack_bf16(o0[d] * f0 + o1[d] * f1, o0[d + 1] * f0 + o1[d + 1] * f1);
-          wv.y = pack_bf16(o0[d + 2] * f0 + o1[d + 2] * f1, o0[d + 3] * f0 + o1[d + 3] * f1);
-          wv.z = pack_bf16(o0[d + 4] * f0 + o1[d + 4] * f1, o0[d + 5] * f0 + o1[d + 5] * f1);
-          wv.w = pack_bf16(o0[d + 6] * f0 + o1[d + 6] * f1, o0[d + 7] * f0 + o1[d + 7] * f1);
-          *reinterpret_cast<uint4*>(dst + d) = wv;
+      for (int d = 0; d < OD; d += 8) {
+        uint4 wv;
+        wv.x = pack_bf16(o0[d] * f0 + o1[d] * f1, o0[d + 1] * f0 + o1[d + 1] * f1);
+        wv.y = pack_bf16(o0[d + 2] * f0 + o1[d + 2] * f1, o0[d + 3] * f0 + o1[d + 3] * f1);
+        wv.z = pack_bf16(o0[d + 4] * f0 + o1[d + 4] * f1, o0[d + 5] * f0 + o1[d + 5] * f1);
+        wv.w = pack_bf16(o0[d + 6] * f0 + o1[d + 6] * f1, o0[d + 7] * f0 + o1[d + 7] * f1);
+        *reinterpret_cast<uint4*>(mine + lane * OUT_ROW_BYTES + (((d / 8) ^ (lane & (CH - 1))) << 4)) = wv;
+      }
+      __syncwarp();
+      if (!*abort) {
+#pragma unroll
+        for (int i2 = 0; i2 < CH; ++i2) {
+          const int rw = i2 * (32 / CH) + lane / CH, chunk = lane % CH;     // row of the warp, chunk of its half row
+          const int rg = q * 32 + rw;                                       // row of the block
+          const int tok2 = a.hpt == 2 ? (rg & 63) : rg;
+          const int head2 = wk.head0 + (a.hpt == 2 ? (rg >> 6) : 0);
+          if (tok2 < rows_tok) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(mine + rw * OUT_ROW_BYTES + ((chunk ^ (rw & (CH - 1))) << 4));
+            *reinterpret_cast<uint4*>(a.out + (size_t)(wk.row0 + tok2) * a.nh * HD + (size_t)head2 * HD + st * OD + chunk * 8) = wv;
+          }
         }
       }
+      __syncwarp();                                        // the warp's rows are out before the next work's are put there
       base += n_mine;
       ++it;
     }
