@@ -427,11 +427,13 @@ def kernel_case(name: str, reps: int = 3) -> str:
       tok_item += [b] * n
       row += n
     tiles = [(b, o) for b, (c, n) in enumerate(items) if n > 1 for o in range(0, n, ops.PREFILL_TILE)]
+    wide = [(b, o) for b, (c, n) in enumerate(items) if n > 1 for o in range(0, n, ops.PREFILL_WIDE_TILE)]
     dec = [b for b, (c, n) in enumerate(items) if n == 1]
     batch = AttentionBatch(token_item=i32(tok_item), positions=i32(pos), seq_slot=i32(list(range(len(items)))), q_start=i32(q_start),
                            q_len=i32([n for _, n in items]), ctx_len=i32([c for c, _ in items]), num_tokens=T, num_items=len(items),
                            prefill_tiles=i32(tiles).view(-1, 2) if tiles else torch.zeros((0, 2), dtype=torch.int32, device=dev),
-                           num_prefill_tiles=len(tiles), decode_items=i32(dec) if dec else torch.zeros(0, dtype=torch.int32, device=dev),
+                           num_prefill_tiles=len(tiles), prefill_wide_tiles=i32(wide).view(-1, 2) if wide else None,
+                           num_prefill_wide_tiles=len(wide), decode_items=i32(dec) if dec else torch.zeros(0, dtype=torch.int32, device=dev),
                            num_decode=len(dec), max_ctx_len=max(c for c, _ in items), scratch=ws)
     qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype)
     out = torch.empty(T, nh * hd, dtype=dtype, device=dev)

@@ -4,7 +4,13 @@
 //
 // A piece of work is 128 query rows that share one kv head - 128 tokens of one query head, or, when
 // the number of query heads per kv head is even, 64 tokens of two neighbouring heads (so K and V are
-// read once for both) - and the keys the mask allows, walked in tiles of 128.  Blocks are persistent,
+// read once for both) - and the keys the mask allows, walked in tiles of 128.  Two blocks may also share
+// a work of 128 tokens of two neighbouring heads, a head each (a cluster of two, tcgen05 cta_group::2:
+// one instruction stream for 256 rows; a block then holds its own Q rows, 64 of a tile's 128 keys and 64
+// of the 128 dims of its values, so each SM asks L2 for half the bytes and the ring has four stages
+// instead of two; the copies of both blocks count on the first block's barriers, its commits arrive on
+// both blocks' barriers, both blocks' softmax warps tell the first block when S is read and P written).
+// Blocks are persistent,
 // one per SM (a block takes all of an SM's tensor memory): the works are dealt out longest first, in
 // rounds that go back and forth over the blocks, and a block's barriers run on from one work to the
 // next, so that the next work's Q and first keys are copied and its first S is computed while the
@@ -55,7 +61,21 @@
 // issuing thread for S and one for P V (36.1), the mask applied once to the scores instead of in both passes - a
 // masked tile took 6800 cycles against 2000, one warp per scheduler has nobody to hide its instructions behind -
 // (31.5), the epilogue's loads under one wait and its stores through shared memory (30.2).  A tile now takes ~2250
-// cycles, of which the tensor cores are busy ~1800 (P V with P from tensor memory runs at about half the rate of S).
+// cycles, of which the tensor cores are busy ~1500: eight products of S and eight of P V at ~95 cycles each, which is
+// the rate the library's products reach too (1.5 PFLOP/s while they run).  The rest is the chain again - a stream's
+// softmax takes ~2500 cycles from S computed to P written, with two streams the tensor cores wait 500 to 1000 cycles
+// before every P V - and it is not the softmax's arithmetic: without the exponential, the maximum, the sum or the
+// conversion to bf16 (each left out in turn) a launch takes as long.  Per work there are ~6500 cycles (3.4 us) beside
+// the tiles: 3500 until the first scores are there (the work's description three dependent loads deep, the first
+// Q and K copies ~1300 cycles each, the first S cold) and 2500 for the merge and the output rows; 8192 tokens of 16
+// heads run at 907 TFLOP/s, 2048 at 564.  Measured against this form and not faster: the works' descriptions worked
+// out once into shared memory and the page numbers of sixteen tiles kept in the producer warp's registers (31.8
+// against 31.1 in a graph of launches), named barriers instead of mbarriers for "S is read" and "P is written"
+// (30.5), half of every K and V copy left out (28.8: the copies' latency, ~3000 cycles under load with two stages,
+// is part of the chain, their bandwidth is not the bound), and pairs of blocks (31.4 at 2048 tokens, 291 against 303
+// at 8192, 56.3 against 57.7 at 32 heads): pairs run where a step brings many tokens.  With an odd number of
+// query heads per kv head a block takes 128 tokens of one head from a list of 128-token tiles (41 against 66 us
+// on three prompts of 24 heads when half the works of a 64-token list were skipped one by one).
 //
 // Every wait on an mbarrier is bounded: a wait that runs out raises a flag in shared memory that
 // ends all later waits at once and sets the status word, and the block runs to its end, where the
@@ -84,12 +104,25 @@ namespace {
 constexpr int HD = MI_HEAD_DIM;
 constexpr int BM = 128;                       // query rows of a block
 constexpr int BN = 128;                       // keys of a tile
-constexpr int STAGES = 2;
+constexpr int MAX_STAGES = 4;
 constexpr int NHALF = HD / 64;                // 64-element (128-byte) halves of a row
 constexpr int HALF_BYTES = 128 * 128;         // 128 rows x 128 bytes
 constexpr int Q_BYTES = NHALF * HALF_BYTES;
 constexpr int K_BYTES = NHALF * HALF_BYTES;   // and V
 constexpr int STAGE_BYTES = 2 * K_BYTES;
+constexpr int KV_RING_BYTES = 2 * STAGE_BYTES;  // shared memory of the K / V ring: two stages of a block that works alone, four of a block of a pair
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;   // clears the bit of a shared::cluster address that tells the two blocks of a pair apart
+// CTAS: blocks that share a tile's instruction stream (1, or 2 as a cluster - tcgen05 cta_group::2).  A block of a
+// pair holds its own 128 query rows, the first or second 64 keys of a K tile and the first or second 64 dims of
+// a V tile: half the bytes per tile, so the same shared memory holds twice the stages.
+template <int CTAS> struct Ring {
+  static constexpr int KEYS = BN / CTAS;                   // keys of a K tile that a block holds
+  static constexpr int K_HALF = KEYS * 128;                // one 64-element half of those keys' rows
+  static constexpr int K_HELD = NHALF * K_HALF;
+  static constexpr int V_HELD = K_BYTES / CTAS;
+  static constexpr int STAGE = K_HELD + V_HELD;
+  static constexpr int STAGES = KV_RING_BYTES / STAGE;
+};
 constexpr int STREAMS = 2;                      // the key tiles are dealt to two streams (even, odd) with sums of their own
 constexpr int TPR = 1;                          // softmax threads per query row and stream: one, with the whole row of scores in registers
 constexpr int SOFTMAX_WARPS = 4 * TPR * STREAMS;
@@ -102,14 +135,14 @@ constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0, P_COL = 128, O_COL = 256;      // S: one buffer both streams take their scores from; stream s: P at P_COL + 64 s, O at O_COL + 128 s
 constexpr int WAIT_LIMIT = 1 << 22;
 constexpr int OUT_ROW_BYTES = HD;                       // a softmax thread's half of an output row in bf16
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float) +
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + KV_RING_BYTES + 256 + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM * sizeof(float) +
                               (size_t)SOFTMAX_WARPS * 32 * OUT_ROW_BYTES;
 
 struct Args {
   __nv_bfloat16* out;            // [T, nh * HD]
   const int* block_table;
   int bt_stride;
-  const int* tiles;              // [n_tiles, 2]: item, first row of the tile within the item's new tokens (multiples of 64)
+  const int* tiles;              // [n_tiles, 2]: item, first row of the tile within the item's new tokens (multiples of 64, or of 128 when hpt = 1 and nothing is skipped)
   const int* q_start;
   const int* q_len;
   const int* ctx_len;
@@ -117,6 +150,8 @@ struct Args {
   int* status;
   int n_tiles, nh, nkv, page_size, window;
   int hpt;                       // query heads of a block: 1 (128 tokens) or 2 (64 tokens each)
+  int hw;                        // query heads of a work: hpt, or 2 x hpt when a pair of blocks shares the work
+  int skip_odd;                  // hpt = 1 on a list of 64-token tiles: the tiles that start at an odd multiple of 64 are covered by the tile before
   float scale_log2;              // scale * log2(e)
 };
 
@@ -158,32 +193,95 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
-// ---- tensor memory and tcgen05
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_in_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_in_smem)), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+// The same from a block of a pair: the bytes are counted on the barrier of the pair's first block.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar) & PAIR_LEADER_MASK) : "memory");
 }
+template <int CTAS>
+__device__ __forceinline__ void tma_load(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  if (CTAS == 1) tma_load_2d(dst, map, x, y, bar);
+  else tma_load_2d_pair(dst, map, x, y, bar);
+}
+// One more arrival on a barrier of the block that issues the products (in a pair: the first block, from either).
+template <int CTAS>
+__device__ __forceinline__ void mbar_arrive_issuer(uint64_t* bar) {
+  if (CTAS == 1) mbar_arrive(bar);
+  else asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PAIR_LEADER_MASK) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ---- tensor memory and tcgen05 (in a pair: the same warp of both blocks allocates, each for its own SM)
+template <int CTAS>
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_in_smem, uint32_t cols) {
+  if (CTAS == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_in_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_in_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+}
+template <int CTAS>
 __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+  if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// The barrier gets an arrival when all products issued so far by this thread are done; in a pair the barrier at
+// the same place in both blocks does.
+template <int CTAS>
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+  if (CTAS == 1) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+  } else {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+  }
 }
-// D[tmem] (+)= A[smem] * B[smem], bf16 in, float32 out; one thread issues it for the block.
+// D[tmem] (+)= A[smem] * B[smem], bf16 in, float32 out; one thread issues it for the block, or for the pair
+// (A: 128 rows in each block, B: half of its rows in each block, D: 128 rows in each block's tensor memory).
+template <int CTAS>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  if (CTAS == 1) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    const uint32_t z = 0;      // no output lane is masked
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+  }
 }
 // The same with A in tensor memory: lane = row, two bf16 of consecutive k to a column.
+template <int CTAS>
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  if (CTAS == 1) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    const uint32_t z = 0;
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+  }
 }
 // 16 consecutive columns of this thread's lane, written.
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -287,15 +385,15 @@ struct Work {
 
 // Work number w of the step, longest first: all head groups of the last 64-token tile, then of the tile
 // before, ...  (Later tiles of a request see more keys.)
-__device__ __forceinline__ Work work_of(const Args& a, int w) {
+__device__ __forceinline__ Work work_of(const Args& a, int w, int rank) {
   Work k;
-  const int X = a.nh / a.hpt;
+  const int X = a.nh / a.hw;
   const int tile = a.n_tiles - 1 - w / X;
   k.item = a.tiles[2 * tile];
   k.o = a.tiles[2 * tile + 1];
-  k.skip = a.hpt == 1 && (k.o & 64);                      // the work of the tile before covers these 64 tokens too
+  k.skip = a.skip_odd && (k.o & 64);                      // the work of the tile before covers these 64 tokens too
   const int G = a.nh / a.nkv;
-  k.head0 = (w % X) * a.hpt;
+  k.head0 = (w % X) * a.hw + rank * a.hpt;                // in a pair the second block takes the work's second head
   k.kvh = k.head0 / G;
   const int qlen = a.q_len[k.item], ctx = a.ctx_len[k.item];
   k.start = ctx - qlen;                                   // position of the item's first new token
@@ -320,22 +418,27 @@ __device__ __forceinline__ int nth_work(int i, int b, int blocks, int total) {
   return w < total ? w : -1;
 }
 
+template <int CTAS>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
-  const int total_work = (a.nh / a.hpt) * a.n_tiles;
-  const int blocks = (int)gridDim.x, me = (int)blockIdx.x;
+  using R = Ring<CTAS>;
+  constexpr int STAGES = R::STAGES;
+  const int total_work = (a.nh / a.hw) * a.n_tiles;
+  const int blocks = (int)gridDim.x / CTAS, me = (int)blockIdx.x / CTAS;      // pairs (or blocks) and this one's number
+  const int rank = CTAS == 1 ? 0 : (int)cluster_rank();                      // place in the pair; its first block issues the products
+  const bool leader = rank == 0;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + Q_BYTES;                    // [stage][K, V]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + STAGES * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + KV_RING_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;                            // K and V of a tile are counted apart: K is free again
-  uint64_t* k_empty = k_full + STAGES;                    // once S is computed, long before P V is
-  uint64_t* v_full = k_empty + STAGES;
-  uint64_t* v_empty = v_full + STAGES;
-  uint64_t* s_full = v_empty + STAGES;                    // [stream]: S of the stream's tile is computed
+  uint64_t* k_empty = k_full + MAX_STAGES;                // once S is computed, long before P V is
+  uint64_t* v_full = k_empty + MAX_STAGES;
+  uint64_t* v_empty = v_full + MAX_STAGES;
+  uint64_t* s_full = v_empty + MAX_STAGES;                // [stream]: S of the stream's tile is computed
   uint64_t* p_full = s_full + STREAMS;                    // [stream]: its P is written
   uint64_t* o_full = p_full + STREAMS;                    // [stream]: its P V is added to the output row
   uint64_t* q_empty = o_full + STREAMS;                   // the work's last S is computed: the Q rows may be replaced
@@ -348,11 +451,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   unsigned char* out_s = reinterpret_cast<unsigned char*>(fin_l + (2 * STREAMS * TPR + 2 * STREAMS * (TPR + 1)) * BM);   // [softmax warp][32 rows][half a row]: output rows on their way to global memory
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // In a pair the barriers that the issuing threads wait on (Q, K, V copied; S read; P written; output rows read) are
+  // the first block's and count both blocks' copies and arrivals; the barriers that copies and softmax warps wait on
+  // are each block's own, and a commit of the first block arrives on both.
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
-    mbar_init(o_free, SOFTMAX_WARPS);
-    mbar_init(s_free, 4);
+    mbar_init(o_free, SOFTMAX_WARPS * CTAS);
+    mbar_init(s_free, 4 * CTAS);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -361,15 +467,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
     for (int b = 0; b < STREAMS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 4);
+      mbar_init(&p_full[b], 4 * CTAS);
       mbar_init(&o_full[b], 1);
     }
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc<CTAS>(tmem_slot, TMEM_COLS);
+  if (warp == PRODUCER_WARP && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&q_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kv_map)) : "memory");
+  }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync();     // the other block's barriers are set up before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // Up to here the block has touched nothing that a kernel writes: set up beside its predecessor in the stream, it
@@ -378,7 +489,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   {
     const int w0 = nth_work(0, me, blocks, total_work);
     if (w0 >= 0) {
-      const Work k0 = work_of(a, w0);
+      const Work k0 = work_of(a, w0, rank);
       asm volatile("" ::"r"(k0.n), "r"(k0.row0), "l"(k0.bt));
     }
   }
@@ -395,17 +506,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       for (int i = 0;; ++i) {
         const int w = nth_work(i, me, blocks, total_work);
         if (w < 0 || *abort) break;
-        const Work k = work_of(a, w);
+        const Work k = work_of(a, w, rank);
         if (k.skip) continue;
         mbar_wait(q_empty, (it & 1) ^ 1, abort, a.status);   // the S products of the work before have read the Q rows
-        mbar_expect_tx(q_full, (uint32_t)Q_BYTES);
+        if (leader) mbar_expect_tx(q_full, (uint32_t)(CTAS * Q_BYTES));
 #pragma unroll
         for (int rb = 0; rb < 2; ++rb) {
           const int head = k.head0 + (a.hpt == 2 ? rb : 0);
           const int y = k.row0 + (a.hpt == 2 ? 0 : 64 * rb);
 #pragma unroll
           for (int h = 0; h < NHALF; ++h)
-            tma_load_2d(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
+            tma_load<CTAS>(q_s + h * HALF_BYTES + rb * 64 * 128, &q_map, head * HD + h * 64, y, q_full);
         }
         // K of tile i goes first, then V of tile i - 1: S of the next tile never waits for a V copy
         auto load = [&](int li, bool values) {
@@ -413,16 +524,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           const int s = g % STAGES;
           uint64_t* full = values ? &v_full[s] : &k_full[s];
           mbar_wait(values ? &v_empty[s] : &k_empty[s], ((g / STAGES) & 1) ^ 1, abort, a.status);
-          unsigned char* dst = kv_s + (size_t)s * STAGE_BYTES + (values ? K_BYTES : 0);
-          mbar_expect_tx(full, (uint32_t)K_BYTES);
+          unsigned char* dst = kv_s + (size_t)s * R::STAGE + (values ? R::K_HELD : 0);
+          if (leader) mbar_expect_tx(full, (uint32_t)K_BYTES);     // of both blocks of a pair together
           const int key0 = (k.t_begin + li) * BN;
 #pragma unroll
           for (int pg = 0; pg < 2; ++pg) {
+            if (CTAS == 2 && !values && pg != rank) continue;      // K: a block of a pair holds its 64 keys, all dims
             const int key = key0 + 64 * pg;
             const int page = k.bt[min(key / a.page_size, a.bt_stride - 1)];   // past the context: the dummy page, masked below
             const int y = ((page * 2 + (values ? 1 : 0)) * a.nkv + k.kvh) * a.page_size + key % a.page_size;
 #pragma unroll
-            for (int h = 0; h < NHALF; ++h) tma_load_2d(dst + h * HALF_BYTES + pg * 64 * 128, &kv_map, h * 64, y, full);
+            for (int h = 0; h < NHALF; ++h) {
+              if (CTAS == 2 && values && h != rank) continue;      // V: all 128 keys, its 64 dims
+              unsigned char* to = CTAS == 1 ? dst + h * HALF_BYTES + pg * 64 * 128
+                                            : (values ? dst + pg * 64 * 128 : dst + h * R::K_HALF);
+              tma_load<CTAS>(to, &kv_map, h * 64, y, full);
+            }
           }
         };
         for (int step = 0; step <= k.n && !*abort; ++step) {
@@ -438,15 +555,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     // S goes into one buffer of tensor memory that both streams take their scores from: a stream's softmax warps
     // read their row of a tile into registers at once and hand the buffer back, so S of the next tile - of the
     // other stream - can follow as soon as that has happened and its K is copied, whatever the P V products do.
-    if (lane == 0) {
-      constexpr uint32_t IDESC_S = instr_desc(BM, BN, false);
+    if (lane == 0 && leader) {
+      constexpr uint32_t IDESC_S = instr_desc(BM * CTAS, BN, false);
       const uint64_t q_desc = smem_desc(smem_u32(q_s), 16, 1024);
-      auto k_step = [](int ks) { return (uint64_t)((ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2); };
+      auto q_step = [](int ks) { return (uint64_t)((ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2); };
+      auto k_step = [](int ks) { return (uint64_t)((ks >> 2) * (R::K_HALF >> 4) + (ks & 3) * 2); };
       int gi = 0, it = 0, s_count = 0;                     // key tiles, works and S products so far
       for (int i = 0;; ++i) {
         const int w = nth_work(i, me, blocks, total_work);
         if (w < 0 || *abort) break;
-        const Work k = work_of(a, w);
+        const Work k = work_of(a, w, rank);
         if (k.skip) continue;
         const int n = k.n;
         mbar_wait(q_full, it & 1, abort, a.status);
@@ -457,14 +575,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           if (!k_ready) mbar_wait(&k_full[st_], (g / STAGES) & 1, abort, a.status);
           if (*abort) break;
           tc_fence_after();
-          const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * STAGE_BYTES), 16, 1024);
+          const uint64_t k_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * R::STAGE), 16, 1024);
           const uint32_t d = tmem_base + S_COL;
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks)
-            tc_mma(d, q_desc + k_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
-          tc_commit(&s_full[j & 1]);
-          tc_commit(&k_empty[st_]);
-          if (j == n - 1) tc_commit(q_empty);              // the work's last S: the Q rows are free once it is done
+            tc_mma<CTAS>(d, q_desc + q_step(ks), k_desc + k_step(ks), IDESC_S, ks > 0 ? 1u : 0u);
+          tc_commit<CTAS>(&s_full[j & 1]);
+          tc_commit<CTAS>(&k_empty[st_]);
+          if (j == n - 1) tc_commit<CTAS>(q_empty);        // the work's last S: the Q rows are free once it is done
         }
         gi += n;
         ++it;
@@ -472,14 +590,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
   } else if (warp == PV_WARP) {
     // ------------------------------------------------------------------ the thread that issues O += P V
-    if (lane == 0) {
-      constexpr uint32_t IDESC_PV = instr_desc(BM, HD, true);
+    if (lane == 0 && leader) {
+      constexpr uint32_t IDESC_PV = instr_desc(BM * CTAS, HD, true);
       int gi = 0, it = 0;
       int sb[STREAMS] = {0, 0};                            // tiles of each stream so far
       for (int i = 0;; ++i) {
         const int w = nth_work(i, me, blocks, total_work);
         if (w < 0 || *abort) break;
-        const Work k = work_of(a, w);
+        const Work k = work_of(a, w, rank);
         if (k.skip) continue;
         const int n = k.n;
         // the output rows in tensor memory are the work before's until its softmax warps have read them
@@ -491,15 +609,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           if (!v_ready) mbar_wait(&v_full[st_], (g / STAGES) & 1, abort, a.status);
           if (*abort) break;
           tc_fence_after();
-          const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * STAGE_BYTES + K_BYTES), HALF_BYTES, 1024);
+          const uint64_t v_desc = smem_desc(smem_u32(kv_s + (size_t)st_ * R::STAGE + R::K_HELD), HALF_BYTES, 1024);
           const uint32_t p_tmem = tmem_base + P_COL + 64 * b;   // lane = row, two keys to a column
 #pragma unroll
           for (int ks = 0; ks < BN / 16; ++ks)                   // 16 keys further: 2048 bytes of V
-            tc_mma_ts(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(8 * ks),
+            tc_mma_ts<CTAS>(tmem_base + O_COL + 128 * b, p_tmem + (uint32_t)(8 * ks),
                       v_desc + (uint64_t)(ks * (2048 >> 4)), IDESC_PV,
                       (j >= 2 || ks > 0) ? 1u : 0u);         // the stream's output row is summed over the work's tiles in tensor memory
-          tc_commit(&o_full[b]);
-          tc_commit(&v_empty[st_]);
+          tc_commit<CTAS>(&o_full[b]);
+          tc_commit<CTAS>(&v_empty[st_]);
         }
         gi += n;
         sb[0] += (n + 1) / 2;
@@ -532,7 +650,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     for (int i = 0;; ++i) {
       const int w = nth_work(i, me, blocks, total_work);
       if (w < 0) break;
-      const Work wk = work_of(a, w);
+      const Work wk = work_of(a, w, rank);
       if (wk.skip) continue;
       const int n = wk.n, start = wk.start, o = wk.o, rows_tok = wk.rows_tok;
       const int p_first = wk.p_first, p_last = wk.p_last, lo_last = wk.lo_last, t_begin = wk.t_begin;
@@ -556,7 +674,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         // the scores are in registers: the S buffer may take the next tile's (of either stream)
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_free);
+        if (lane == 0) mbar_arrive_issuer<CTAS>(s_free);
         if (masked) {
           // A tile that the mask touches: the scores a row may not see are set to -inf once, here, and everything
           // after treats the tile like any other (a maximum ignores them, their exponentials are 0).  The visible
@@ -617,7 +735,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[st]);
+        if (lane == 0) mbar_arrive_issuer<CTAS>(&p_full[st]);
       }
       if (n_mine > 0) wait_o(base + n_mine - 1);
       // ---- the two streams' sums are merged: every thread leaves its sum and maximum in shared memory, all
@@ -647,7 +765,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       // the output rows are in registers: the next work's products may overwrite them in tensor memory
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(o_free);
+      if (lane == 0) mbar_arrive_issuer<CTAS>(o_free);
       // A thread's half row goes through shared memory (16-byte chunks, swizzled by the row), so that a store of
       // the warp covers whole 128-byte lines of four rows instead of 16 bytes of each of 32 rows.
       constexpr int CH = OUT_ROW_BYTES / 16;               // chunks of a half row: 8 (head size 128) or 4
@@ -683,10 +801,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   // ---- teardown: every tensor-memory access is done, then the columns go back
   tc_fence_before();
   __syncthreads();
+  // neither block of a pair leaves, or frees its tensor memory, while the other may still signal it or work on
+  // a tile they share
+  if (CTAS == 2) cluster_sync();
   if (warp == MMA_WARP) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc<CTAS>(tmem_base, TMEM_COLS);
   }
 }
 
@@ -724,12 +845,74 @@ MI_API int mi_qkv_tensor_map(void* out_map, const void* qkv, long long rows, lon
   return 0;
 }
 
+namespace {
+
+// Launches the kernel for blocks that work alone (CTAS = 1) or in pairs (2).  `placed` tells whether pairs can be
+// resident on this device at all; if not, nothing was launched and the caller takes the other form.
+template <int CTAS>
+int launch_prefill_tc(const CUtensorMap& qm, const CUtensorMap& km, const Args& a, int num_sms, cudaStream_t stream, bool* placed) {
+  auto kernel = attention_prefill_tc_kernel<CTAS>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (err != cudaSuccess) return mi_fail("attention_prefill_tc: cannot get %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(err));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  int groups = num_sms / CTAS;       // persistent blocks, one per SM (a block takes all of an SM's tensor memory)
+  if (CTAS == 2) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+    static int max_pairs = -1;       // how many pairs can be resident; asked once
+    if (max_pairs < 0) {
+      cfg.gridDim = dim3(num_sms / 2 * 2);
+      cfg.attrs = attr;
+      cfg.numAttrs = n_attr;
+      int n = 0;
+      cudaError_t err = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+      max_pairs = (err == cudaSuccess) ? n : 0;
+      cudaGetLastError();
+    }
+    if (max_pairs < 1) {
+      *placed = false;
+      return 0;
+    }
+    groups = min(groups, max_pairs);
+  }
+  if (mi::pdl_enabled()) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  const int total_work = (a.nh / a.hw) * a.n_tiles;
+  cfg.gridDim = dim3(CTAS * max(1, min(groups, total_work)));      // no more blocks (pairs) than there is work
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, qm, km, a);
+  if (err != cudaSuccess) return mi_fail("attention_prefill_tc: launch failed: %s", cudaGetErrorString(err));
+  *placed = true;
+  return 0;
+}
+
+}  // namespace
+
 // q_map: mi_qkv_tensor_map of the step's QKV rows; kv_map: mi_kv_tensor_map of the layer's cache.
-// status: one word, set to 2 if a bounded wait ran out.
+// status: one word, set to 2 if a bounded wait ran out.  tiles128: the tiles of 128 tokens of the same items (item,
+// first row), or null.  pairs: whether two blocks may share a work - 128 tokens of two neighbouring heads, a head
+// each - which takes heads of 128, an even number of query heads per kv head and the list of 128-token tiles;
+// otherwise, and where pairs cannot be placed, blocks work alone.
 MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_map, const int* block_table, int bt_stride,
                                    const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
                                    const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
-                                   int num_sms, cudaStream_t stream) {
+                                   int num_sms, cudaStream_t stream, const int* tiles128, int n_tiles128, int pairs) {
   MI_REQUIRE(num_sms > 0, "attention_prefill_tc: num_sms");
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill_tc: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % 64 == 0, "attention_prefill_tc: page_size=%d must be a multiple of 64", page_size);
@@ -747,20 +930,35 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   a.seq_slot = seq_slot;
   a.status = status;
   a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
-  a.hpt = ((nh / nkv) % 2 == 0) ? 2 : 1;
   a.scale_log2 = scale * 1.4426950408889634f;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (err != cudaSuccess) return mi_fail("attention_prefill_tc: cannot get %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(err));
-    configured = true;
-  }
   CUtensorMap qm, km;
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));
-  // persistent blocks, one per SM (a block takes all of an SM's tensor memory), no more than there is work
-  const int total_work = (nh / a.hpt) * n_tiles;
-  mi::launch(attention_prefill_tc_kernel, dim3(total_work < num_sms ? total_work : num_sms), dim3(THREADS), SMEM_BYTES, stream, qm, km, a);
+  const bool even_group = (nh / nkv) % 2 == 0;
+  bool placed = false;
+  if (pairs && HD == 128 && even_group && num_sms >= 2 && tiles128 != nullptr && n_tiles128 > 0) {
+    // a pair of blocks: 128 tokens of two neighbouring heads, a head each
+    Args p = a;
+    p.tiles = tiles128;
+    p.n_tiles = n_tiles128;
+    p.hpt = 1;
+    p.hw = 2;
+    p.skip_odd = 0;
+    const int r = launch_prefill_tc<2>(qm, km, p, num_sms, stream, &placed);
+    if (r != 0) return r;
+  }
+  if (!placed) {
+    a.hpt = even_group ? 2 : 1;
+    a.hw = a.hpt;
+    a.skip_odd = a.hpt == 1 ? 1 : 0;
+    if (a.hpt == 1 && tiles128 != nullptr && n_tiles128 > 0) {
+      a.tiles = tiles128;
+      a.n_tiles = n_tiles128;
+      a.skip_odd = 0;
+    }
+    const int r = launch_prefill_tc<1>(qm, km, a, num_sms, stream, &placed);
+    if (r != 0) return r;
+  }
   MI_LAUNCH_OK("attention_prefill_tc");
   return 0;
 }
@@ -770,7 +968,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
 MI_API int mi_attention_prefill_tc_supported() { return 0; }
 MI_API int mi_qkv_tensor_map(void*, const void*, long long, long long) { return mi_fail("qkv_tensor_map: head size %d has no tcgen05 kernel", MI_HEAD_DIM); }
 MI_API int mi_attention_prefill_tc(void*, const void*, const void*, const int*, int, const int*, int, const int*, const int*, const int*,
-                                   const int*, int*, int, int, int, float, int, int, cudaStream_t) {
+                                   const int*, int*, int, int, int, float, int, int, cudaStream_t, const int*, int, int) {
   return mi_fail("attention_prefill_tc: head size %d has no tcgen05 kernel", MI_HEAD_DIM);
 }
 

@@ -22,6 +22,8 @@ from . import build
 
 F32, BF16 = 0, 1
 PREFILL_TILE = 64     # query rows of one tile of the prefill attention kernels
+PREFILL_WIDE_TILE = 128   # tokens of a work of the tcgen05 prefill kernel when a block (or each block of a pair) takes one head
+PREFILL_PAIRS_MIN_WIDE_TILES = 48   # steps with at least this many such tiles (6144 new tokens) let two blocks share a work
 SKINNY_MAX_M = 64     # the most rows the skinny kernel takes
 SKINNY_BEST_M = 16    # up to here it is the faster one; above, cuBLAS is (measured on B200, M = 32 and 64)
 # Rows from which the tcgen05 gate-up product with SwiGLU in its epilogue beats the library product followed by the
@@ -450,12 +452,14 @@ class AttentionBatch:
   ``token_item[t]``: the batch item of token t; ``positions[t]``: its position in its request;
   ``seq_slot[b]``: the block-table row of item b; ``q_start[b]``, ``q_len[b]``, ``ctx_len[b]``:
   the item's first row, its number of new tokens and its length including them.
-  Host-side lists the launchers need: ``prefill_items`` / ``decode_items`` (device int32 lists of
-  item indices with more than one / exactly one new token), their lengths and the largest context."""
+  Lists the launchers need: ``prefill_tiles`` ((item, first row) of every ``PREFILL_TILE`` rows of the items
+  with several new tokens), ``prefill_wide_tiles`` (the same in steps of ``PREFILL_WIDE_TILE``; optional: without it
+  the tcgen05 prefill kernel never pairs blocks), ``decode_items`` (the items with exactly one new token), their
+  lengths and the largest context."""
 
   __slots__ = ("token_item", "positions", "seq_slot", "q_start", "q_len", "ctx_len", "num_tokens", "num_items",
-               "prefill_tiles", "num_prefill_tiles", "decode_items", "num_decode", "max_ctx_len", "decode_chunk",
-               "scratch")
+               "prefill_tiles", "num_prefill_tiles", "prefill_wide_tiles", "num_prefill_wide_tiles", "decode_items", "num_decode",
+               "max_ctx_len", "decode_chunk", "scratch")
 
   def __init__(self, **kw):
     for k in self.__slots__:
@@ -603,11 +607,17 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         status = batch.scratch.zeros("attention_prefill_status", 1, torch.int32)
       else:
         status = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+      wide, n_wide = batch.prefill_wide_tiles, int(batch.num_prefill_wide_tiles or 0)
+      # two blocks on one work (tcgen05 cta_group::2: half the K / V bytes per SM, twice the stages): measured on B200
+      # at 16 heads of 128, 291 against 303 us for 8192 new tokens, 31.4 against 31.2 us for 2048 - so only large steps
+      force = os.environ.get("MINIINFER_B200_PREFILL_PAIRS")
+      pairs = int(force == "1") if force in ("0", "1") else int(n_wide >= PREFILL_PAIRS_MIN_WIDE_TILES)
       _check(lib, lib.mi_attention_prefill_tc(
         _ptr(out), _qkv_tensor_map(lib, qkv), _kv_tensor_map(lib, kv_layer), _ptr(block_table, torch.int32), block_table.shape[1],
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
-        _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream()))
+        _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream(),
+        _ptr(wide, torch.int32) if wide is not None else _ptr(None), n_wide, pairs))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
     else:

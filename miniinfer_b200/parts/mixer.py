@@ -40,17 +40,26 @@ class PrefillTiles(StepWork):
   several tokens: one block of the prefill attention kernel per tile and head."""
 
   name = "attention_prefill_tiles"
+  tile = ops.PREFILL_TILE
 
   def build(self, step: HostStep) -> np.ndarray:
-    pairs = [(b, o) for b in np.flatnonzero(step.q_len > 1) for o in range(0, int(step.q_len[b]), ops.PREFILL_TILE)]
+    pairs = [(b, o) for b in np.flatnonzero(step.q_len > 1) for o in range(0, int(step.q_len[b]), self.tile)]
     return np.array(pairs, dtype=np.int32).reshape(-1)
 
   def key(self, step: HostStep) -> tuple:
     n = step.q_len[step.q_len > 1]
-    return (int((-(-n // ops.PREFILL_TILE)).sum()),)
+    return (int((-(-n // self.tile)).sum()),)
 
 
-_WORK = [DecodeItems(), PrefillTiles()]
+class PrefillWideTiles(PrefillTiles):
+  """The same in steps of ``ops.PREFILL_WIDE_TILE`` rows: the works of the tcgen05 prefill kernel when a block, or each
+  block of a pair, takes 128 tokens of one head."""
+
+  name = "attention_prefill_wide_tiles"
+  tile = ops.PREFILL_WIDE_TILE
+
+
+_WORK = [DecodeItems(), PrefillTiles(), PrefillWideTiles()]
 
 
 class AttentionMixer(Mixer):
@@ -110,11 +119,12 @@ class AttentionMixer(Mixer):
     """The step as the attention kernels take it; made once per step and shared by all layers."""
     batch = ctx.shared.get("attention_batch")
     if batch is None:
-      dec, tiles = ctx.work[DecodeItems.name], ctx.work[PrefillTiles.name]
+      dec, tiles, wide = ctx.work[DecodeItems.name], ctx.work[PrefillTiles.name], ctx.work[PrefillWideTiles.name]
       batch = AttentionBatch(
         token_item=ctx.token_item, positions=ctx.positions, seq_slot=ctx.seq_slot, q_start=ctx.q_start, q_len=ctx.q_len,
         ctx_len=ctx.ctx_len, num_tokens=ctx.num_tokens, num_items=ctx.num_items,
-        prefill_tiles=tiles.view(-1, 2), num_prefill_tiles=tiles.shape[0] // 2, decode_items=dec, num_decode=dec.shape[0],
+        prefill_tiles=tiles.view(-1, 2), num_prefill_tiles=tiles.shape[0] // 2,
+        prefill_wide_tiles=wide.view(-1, 2), num_prefill_wide_tiles=wide.shape[0] // 2, decode_items=dec, num_decode=dec.shape[0],
         max_ctx_len=max(1, ctx.work_key[DecodeItems.name][1]), scratch=ctx.ws)
       ctx.shared["attention_batch"] = batch
     return batch

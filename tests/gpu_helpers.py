@@ -51,12 +51,14 @@ def make_attention_case(items: Sequence[Tuple[int, int]], nh: int, nkv: int, hd:
     return torch.tensor(x, dtype=dt, device=DEV)
 
   tiles = [(b, o) for b, (c, n) in enumerate(items) if n > 1 for o in range(0, n, 64)]
+  wide = [(b, o) for b, (c, n) in enumerate(items) if n > 1 for o in range(0, n, 128)]
   dec = [b for b, (c, n) in enumerate(items) if n == 1]
   batch = AttentionBatch(
     token_item=dev(token_item), positions=dev(positions), seq_slot=dev(slots), q_start=dev(q_start), q_len=dev(q_len),
     ctx_len=dev(ctx_len), num_tokens=T, num_items=len(items),
     prefill_tiles=dev(tiles).view(-1, 2) if tiles else torch.zeros((0, 2), dtype=torch.int32, device=DEV),
-    num_prefill_tiles=len(tiles), decode_items=dev(dec) if dec else torch.zeros(0, dtype=torch.int32, device=DEV),
+    num_prefill_tiles=len(tiles), prefill_wide_tiles=dev(wide).view(-1, 2) if wide else None, num_prefill_wide_tiles=len(wide),
+    decode_items=dev(dec) if dec else torch.zeros(0, dtype=torch.int32, device=DEV),
     num_decode=len(dec), max_ctx_len=max_ctx, scratch=None)
   return qkv.to(DEV), kv.to(DEV), torch.from_numpy(bt).to(DEV), batch
 

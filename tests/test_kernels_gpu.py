@@ -271,6 +271,54 @@ def test_decode_attention_that_norms_rotates_and_stores_itself(ops, monkeypatch,
   assert (out1.float() - want.float()).abs().max() < 3e-2
 
 
+@pytest.mark.parametrize("nh,nkv,P,window", [(16, 8, 64, None), (8, 2, 128, None), (16, 2, 64, 900), (6, 2, 64, None), (4, 4, 64, None)])
+def test_prefill_attention_on_tcgen05_alone_and_in_pairs(ops, monkeypatch, nh, nkv, P, window):
+  """The tcgen05 prefill kernel in its three forms - two blocks sharing 128 tokens of two heads (an even number of
+  query heads per kv head), a block alone on the list of 128-token tiles, and a block alone without that list - on
+  prompts and portions of many lengths, several launches in a row (the barriers' phases run on within a launch
+  only): every form against the statement, and the forms that cut the keys the same way bit for bit."""
+  hd = 128
+  items = [(3000, 1700), (129, 129), (700, 2), (64, 64), (1, 1), (1300, 1153), (500, 1)]
+  qkv, kv, bt, batch = make_attention_case(items, nh, nkv, hd, P, torch.bfloat16, seed=nh, num_slots=9)
+  T = qkv.shape[0]
+  want = torch.empty((T, nh * hd), dtype=torch.bfloat16, device=DEV)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+  wide, n_wide = batch.prefill_wide_tiles, batch.num_prefill_wide_tiles
+  outs = {}
+  for form in ("pairs", "alone", "alone without the wide tiles"):
+    monkeypatch.setenv("MINIINFER_B200_PREFILL_PAIRS", "1" if form == "pairs" else "0")
+    batch.prefill_wide_tiles, batch.num_prefill_wide_tiles = (None, 0) if form.endswith("tiles") else (wide, n_wide)
+    out = torch.empty_like(want)
+    for _ in range(3):
+      out.fill_(float("nan"))
+      ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, window)
+    assert torch.isfinite(out.float()).all(), form
+    assert (out.float() - want.float()).abs().max() < 2e-2, form
+    outs[form] = out
+  if window is None:      # without a window every form walks the same key tiles from the first key on
+    assert torch.equal(outs["pairs"], outs["alone"])
+    assert torch.equal(outs["alone"], outs["alone without the wide tiles"])
+
+
+def test_prefill_attention_pairs_blocks_on_a_large_step(ops, monkeypatch):
+  """A step with more new tokens than ``ops.PREFILL_PAIRS_MIN_WIDE_TILES`` tiles of 128: nothing is forced, the
+  blocks work in pairs; the same rows as from blocks that work alone, and as the statement's."""
+  nh, nkv, hd, P = 4, 2, 128, 64
+  items = [(6500, 6300), (300, 1)]
+  qkv, kv, bt, batch = make_attention_case(items, nh, nkv, hd, P, torch.bfloat16, seed=11, num_slots=3)
+  assert batch.num_prefill_wide_tiles >= ops.PREFILL_PAIRS_MIN_WIDE_TILES
+  monkeypatch.delenv("MINIINFER_B200_PREFILL_PAIRS", raising=False)
+  out = torch.full((qkv.shape[0], nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+  ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, None)
+  monkeypatch.setenv("MINIINFER_B200_PREFILL_PAIRS", "0")
+  alone = torch.empty_like(out)
+  ops.attention(alone, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, None)
+  want = torch.empty_like(out)
+  ref.attention(want, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, None)
+  assert torch.equal(out, alone)
+  assert (out.float() - want.float()).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dtype):
   """Random data would hide a key that is skipped: make one key's score stand out."""
