@@ -464,6 +464,10 @@ def kernel_case(name: str, reps: int = 3) -> str:
     fn, what = (lambda: ops.linear(out, x, w)), "bf16 few-row product on tcgen05, M = 8, N = 5120, K = 25600 (262 MB of weights: the down product of the Qwen3-32B shape)"
   elif name == "attention_generic":
     fn, what = attention_case(torch.float32, 64, [(2048, 1)] * 8 + [(2048, 512)])
+  elif name == "attention_prefill_tc":
+    fn, what = attention_case(torch.bfloat16, 64, [(2048, 2048)])           # the tcgen05 kernel, blocks alone
+  elif name == "attention_prefill_tc_pairs":
+    fn, what = attention_case(torch.bfloat16, 64, [(8192, 8192)])           # enough tiles of 128 tokens for blocks in pairs
   elif name == "attention_prefill_mma":
     fn, what = attention_case(torch.bfloat16, 16, [(2048, 2048)])           # pages of 16 tokens: not the tcgen05 kernel's
   elif name == "attention_decode_cpasync":
@@ -481,7 +485,8 @@ def kernel_case(name: str, reps: int = 3) -> str:
   return f"{name}: {what}: {1000 * start.elapsed_time(end) / reps:.1f} us per call (warm, {reps} calls back to back)"
 
 
-KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_mma", "attention_decode_cpasync")
+KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_tc",
+                "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
