@@ -111,3 +111,33 @@ def test_decode_graphs_across_a_context_class(model_dirs, dtype):
     exact = plain.check_greedy_tokens(w, c, p, o["token_ids"], margin=2e-4 if dtype == "float32" else 2 * BOUND["bfloat16"])
     assert exact >= (58 if dtype == "float32" else 50)
   eng.runner.check_status()
+
+
+def test_a_step_of_many_thousand_tokens_pairs_the_attention_blocks(model_dirs, monkeypatch):
+  """Four prompts of about 1600 tokens in ONE step: more than 48 tiles of 128 new tokens, so the tcgen05 prefill
+  attention lets two blocks share a work.  The last rows' logits are the plain implementation's within the bfloat16
+  bound, and the same bits as with blocks that work alone."""
+  from miniinfer_b200.engine.replay import TraceRunner
+  from miniinfer_b200.kernels import ops
+  d = model_dirs("R")
+  w, c, _, _ = weights_and_reference(d)
+  lens = (1600, 1550, 1700, 1650)
+  assert sum(-(-n // ops.PREFILL_WIDE_TILE) for n in lens) >= ops.PREFILL_PAIRS_MIN_WIDE_TILES
+  reqs = rc.make_requests(V, lens, seed=21)
+  record = {"step": 0, "entries": [{"id": rid, "tokens": ids, "want": [len(ids) - 1]} for rid, ids in reqs.items()], "end": list(reqs)}
+  got = {}
+  for pairs in (None, "0"):
+    if pairs is None:
+      monkeypatch.delenv("MINIINFER_B200_PREFILL_PAIRS", raising=False)
+    else:
+      monkeypatch.setenv("MINIINFER_B200_PREFILL_PAIRS", pairs)
+    runner = TraceRunner(d, "bfloat16", sum(rc.round_up(n, PAGE) for n in lens), device=DEV, page_size=PAGE)
+    got[pairs] = runner.run_step(record)
+    runner.runner.check_status()
+    del runner
+    if DEV != "cpu":
+      torch.cuda.empty_cache()
+  assert np.array_equal(got[None], got["0"])
+  for i, (rid, ids) in enumerate(reqs.items()):
+    want = plain.forward(w, c, ids, rows=[len(ids) - 1])[0].numpy()
+    assert np.abs(got[None][i] - want).max() < BOUND["bfloat16"], rid
