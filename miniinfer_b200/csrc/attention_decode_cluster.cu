@@ -171,18 +171,18 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
   // this block holds the tile with position p, and the new token's entry is this kernel's to write
   const bool patch = rope && nb > 0 && b1 == tiles && a.slot_mapping != nullptr && a.kv_layer != nullptr;
   auto ask = [&](int b) {                                    // lane 0 of the copying warp
-      const int s = b % a.stages;
-      mbar_wait(&empty[s], ((b / a.stages) & 1) ^ 1, abort, a.status);
-      const int jb = j_first + (b0 + b) * BK;
-      const int y_k = ((pages[b] * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
-      const int y_v = y_k + a.nkv * a.page_size;
-      unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
-      mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
+    const int s = b % a.stages;
+    mbar_wait(&empty[s], ((b / a.stages) & 1) ^ 1, abort, a.status);
+    const int jb = j_first + (b0 + b) * BK;
+    const int y_k = ((pages[b] * 2) * a.nkv + kvh) * a.page_size + jb % a.page_size;
+    const int y_v = y_k + a.nkv * a.page_size;
+    unsigned char* dst = stage0 + (size_t)s * STAGE_BYTES;
+    mbar_expect_tx(&full[s], (uint32_t)STAGE_BYTES);
 #pragma unroll
-      for (int x = 0; x < NBOX; ++x) {
-        tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
-        tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
-      }
+    for (int x = 0; x < NBOX; ++x) {
+      tma_load_2d(dst + x * BOX_BYTES, &kv_map, x * 64, y_k, &full[s]);
+      tma_load_2d(dst + TILE_BYTES + x * BOX_BYTES, &kv_map, x * 64, y_v, &full[s]);
+    }
   };
   // When this kernel stores the new token itself, no kernel of the step has written this layer's cache before it:
   // what the cache holds is older than the kernel before the preceding one, which has completed (a kernel lets its
