@@ -67,7 +67,7 @@ struct ClusterArgs {
   int q_stride;
   const int* block_table;
   int bt_stride;
-  const int* decode_items;
+  const int* decode_items;         // the items that bring one token (null: all of the step's items do)
   const int* q_start;
   const int* ctx_len;
   const int* seq_slot;
@@ -114,7 +114,7 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // Read before the wait for the preceding kernel: only what the host uploaded.
-  const int item = a.decode_items[e];
+  const int item = a.decode_items ? a.decode_items[e] : e;     // null: every item of the step brings one token, in order
   const int p = a.ctx_len[item] - 1;
   const int row = a.q_start[item];
   const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
