@@ -43,12 +43,18 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
   return x;
 }
 
-__device__ __forceinline__ float uniform_for(uint64_t key, int index) {
+// The 23 random bits of (key, index).
+__device__ __forceinline__ uint32_t uniform_bits(uint64_t key, int index) {
+  return (uint32_t)(mix64(key ^ ((uint64_t)index * 0xD1342543DE82EF95ull)) >> 41);
+}
+__device__ __forceinline__ float uniform_of_bits(uint32_t n) {
   // 23 bits: (n + 0.5) * 2^-23 is exact in float32 and lies in [2^-24, 1 - 2^-24], strictly inside
   // (0, 1).  With 24 bits the largest n + 0.5 would round up and give u = 1, whose noise is +inf.
-  const uint64_t bits = mix64(key ^ ((uint64_t)index * 0xD1342543DE82EF95ull));
-  return ((float)(bits >> 41) + 0.5f) * (1.0f / 8388608.0f);
+  return ((float)n + 0.5f) * (1.0f / 8388608.0f);
 }
+// Seven draws in eight have u < 7/8, whose noise -log(-log(u)) is below 2.0135: a bound that needs no logarithm.
+constexpr uint32_t SMALL_NOISE_BITS = 7u << 20;         // n below this: u < 7/8
+constexpr float SMALL_NOISE = 2.02f;
 
 __device__ __forceinline__ uint32_t ordered(float f) {
   const uint32_t u = __float_as_uint(f);
@@ -329,6 +335,7 @@ static int launch_thresholds(uint32_t* thr, const float* logits, const float* te
 }
 
 constexpr int PICK_THREADS = 256;
+constexpr int PICK_BATCH = 8;           // logits a thread loads before it looks at any of them
 
 // Launch 2: best perturbed score of each slice; the last block of a row picks the row's best.
 __global__ void __launch_bounds__(PICK_THREADS)
@@ -344,19 +351,45 @@ sample_pick_kernel(int* __restrict__ out, const float* __restrict__ logits, cons
   const float temp = temperature[row];
   const int begin = slice * slice_len, end = min(V, begin + slice_len);
   Best b{-INFINITY, 0x7fffffff};
+  // A thread walks its logits in the order of their indices, PICK_BATCH of them loaded at a time: with few rows a
+  // slice is long, and a load per turn of the loop would make the walk a chain of memory latencies.
   if (!(temp > 0.f)) {
-    for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) b = better(b, Best{x[i], i});
+    for (int i0 = begin + threadIdx.x; i0 < end; i0 += PICK_THREADS * PICK_BATCH) {
+      float v[PICK_BATCH];
+#pragma unroll
+      for (int u = 0; u < PICK_BATCH; ++u) {
+        const int i = i0 + u * PICK_THREADS;
+        v[u] = i < end ? x[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < PICK_BATCH; ++u) {
+        const int i = i0 + u * PICK_THREADS;
+        if (i < end) b = better(b, Best{v[u], i});
+      }
+    }
   } else {
     const uint32_t thr = thr_in[row];
     const uint64_t key = mix64((uint64_t)seed[row] ^ mix64((uint64_t)counter[row] + 0x9E3779B97F4A7C15ull));
-    for (int i = begin + threadIdx.x; i < end; i += PICK_THREADS) {
-      const float z = x[i] / temp;
-      if (ordered(z) < thr || !(z > -INFINITY)) continue;
-      // u <= 1 - 2^-24, so the noise -log(-log(u)) stays below 16.7 < 17.4: a score that far under this
-      // thread's best cannot win, and its draw need not be worked out
-      if (z + 17.4f < b.v) continue;
-      const float u = uniform_for(key, i);
-      b = better(b, Best{z - logf(-logf(u)), i});
+    for (int i0 = begin + threadIdx.x; i0 < end; i0 += PICK_THREADS * PICK_BATCH) {
+      float v[PICK_BATCH];
+#pragma unroll
+      for (int u = 0; u < PICK_BATCH; ++u) {
+        const int i = i0 + u * PICK_THREADS;
+        v[u] = i < end ? x[i] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < PICK_BATCH; ++u) {
+        const int i = i0 + u * PICK_THREADS;
+        if (i >= end) continue;
+        const float z = v[u] / temp;
+        if (ordered(z) < thr || !(z > -INFINITY)) continue;
+        // u <= 1 - 2^-24, so the noise -log(-log(u)) stays below 16.7 < 17.4: a score that far under this
+        // thread's best cannot win, and its draw need not be worked out
+        if (z + 17.4f < b.v) continue;
+        const uint32_t n = uniform_bits(key, i);
+        if (n < SMALL_NOISE_BITS && z + SMALL_NOISE < b.v) continue;      // the same reasoning with the draw's own bound
+        b = better(b, Best{z - logf(-logf(uniform_of_bits(n))), i});
+      }
     }
   }
   // block arg-max
