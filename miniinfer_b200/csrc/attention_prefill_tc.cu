@@ -17,7 +17,7 @@
 // softmax warps finish the work before.  Within a work:
 //   * a producer warp asks the TMA engine for the Q rows once and for K and V tile by tile (boxes
 //     of 64 rows x 64 elements, one page and one half of the head size each, written in the
-//     128-byte swizzle), two stages each, counted on mbarriers; K and V are counted apart, since
+//     128-byte swizzle), two stages each (four in a pair), counted on mbarriers; K and V are counted apart, since
 //     K is free again as soon as S is computed;
 //   * the key tiles are dealt to two streams, the even and the odd ones.  A stream has four softmax
 //     warps, an output accumulator (head size columns of tensor memory), 64 columns for P, and a running
@@ -71,8 +71,10 @@
 // heads run at 907 TFLOP/s, 2048 at 564.  Measured against this form and not faster: the works' descriptions worked
 // out once into shared memory and the page numbers of sixteen tiles kept in the producer warp's registers (31.8
 // against 31.1 in a graph of launches), named barriers instead of mbarriers for "S is read" and "P is written"
-// (30.5), half of every K and V copy left out (28.8: the copies' latency, ~3000 cycles under load with two stages,
-// is part of the chain, their bandwidth is not the bound), and pairs of blocks (31.4 at 2048 tokens, 291 against 303
+// (30.5), half of every K and V copy left out (28.8: the copies' latency, ~3000 cycles under load, is part of the
+// chain - with two stages the K of tile j + 2 can only be asked for when S of tile j is done, so two tiles cannot
+// take less than that latency and an S product, and shared memory has no room for a third stage of K and of V
+// beside Q - their bandwidth is not the bound), and pairs of blocks (31.4 at 2048 tokens, 291 against 303
 // at 8192, 56.3 against 57.7 at 32 heads): pairs run where a step brings many tokens.  With an odd number of
 // query heads per kv head a block takes 128 tokens of one head from a list of 128-token tiles (41 against 66 us
 // on three prompts of 24 heads when half the works of a 64-token list were skipped one by one).
