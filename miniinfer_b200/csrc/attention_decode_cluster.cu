@@ -60,6 +60,10 @@ constexpr int CTHREADS = (CW + 1) * 32;      // + the warp that asks for the cop
 constexpr int CMAX_STAGES = 8;
 constexpr int ROW = HD + 2;                  // a head's partial result: HD weighted values, max, sum
 constexpr int GP = 8;                        // heads per kv head the tile computation is laid out for
+constexpr int MAX_CLUSTER = 16;
+// What the blocks of a cluster send each other at the end: a block's share of every block's output sums (G x HD
+// values over the cluster, rounded up per block) and every block's maximum and sum per head.
+constexpr int RECV_FLOATS = GP * HD + MAX_CLUSTER * (2 * GP + 1);
 
 struct ClusterArgs {
   __nv_bfloat16* out;              // [T, nh * HD]
@@ -89,10 +93,10 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // the swizzle pattern is a function of the address: the tiles start on a 1024-byte boundary
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  // [stages][K tile, V tile] | part [GP][ROW] | red [CW][GP][ROW] | barriers | pages [max_tiles] | flag
+  // [stages][K tile, V tile] | recv [RECV_FLOATS] | red [CW][GP][ROW] | barriers | pages [max_tiles] | flag
   unsigned char* stage0 = smem;
-  float* part = reinterpret_cast<float*>(smem + (size_t)a.stages * STAGE_BYTES);
-  float* red = part + GP * ROW;
+  float* recv = reinterpret_cast<float*>(smem + (size_t)a.stages * STAGE_BYTES);   // [block of the cluster][its sums of my slice | max, sum per head]
+  float* red = recv + RECV_FLOATS;
   uint64_t* full = reinterpret_cast<uint64_t*>(red + CW * GP * ROW);
   uint64_t* empty = full + CMAX_STAGES;
   uint64_t* patched = empty + CMAX_STAGES;                       // rope: the new token's key and value are in the last tile
@@ -103,6 +107,9 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int C = (int)gridDim.x, r = (int)blockIdx.x, kvh = (int)blockIdx.y, e = (int)blockIdx.z;
   const int G = a.nh / a.nkv;
+  // The blocks of a cluster write into one another's shared memory at the end, which needs them all to have
+  // started: every thread says so here and waits for the others only then.
+  if (C > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -301,8 +308,16 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     }
   }
   __syncthreads();
-  // the warps of the block, in warp order (which is the order of their first tiles)
-  for (int idx = threadIdx.x; idx < G * HD; idx += CTHREADS) {
+  // The warps of the block, in warp order (which is the order of their first tiles).  In a cluster every block then
+  // owns a slice of the output values: each block puts its sums of a slice into the owner's shared memory, and its
+  // maximum and sum per head into everybody's; one barrier over the cluster later each block finds all it needs
+  // at home, combines in rank order and leaves - nobody reads a neighbour's memory after the barrier.
+  cg::cluster_group cluster = cg::this_cluster();
+  const int total = G * HD;
+  const int slice = (total + C - 1) / C;
+  const int rs = slice + 2 * GP;                           // floats a block receives from one block
+  if (C > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");     // every block of the cluster has started
+  for (int idx = threadIdx.x; idx < total; idx += CTHREADS) {
     const int h = idx / HD, d = idx % HD;
     float M = -INFINITY;
 #pragma unroll
@@ -320,40 +335,42 @@ decode_cluster_kernel(const __grid_constant__ CUtensorMap kv_map, ClusterArgs a)
     if (C == 1) {
       a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = __float2bfloat16_rn(A / L);
     } else {
-      part[h * ROW + d] = A;
+      const int owner = idx / slice;
+      cluster.map_shared_rank(recv, owner)[(size_t)r * rs + (idx - owner * slice)] = A;
       if (d == 0) {
-        part[h * ROW + HD] = M;
-        part[h * ROW + HD + 1] = L;
+        for (int rr = 0; rr < C; ++rr) {
+          float* to = cluster.map_shared_rank(recv, rr) + (size_t)r * rs + slice;
+          to[2 * h] = M;
+          to[2 * h + 1] = L;
+        }
       }
     }
   }
   if (C == 1) return;
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
-  // the blocks of the cluster, in rank order; each block combines a slice of the output
-  cg::cluster_group cluster = cg::this_cluster();
-  cluster.sync();
-  const int total = G * HD;
-  const int slice = (total + C - 1) / C;
-  for (int idx = r * slice + threadIdx.x; idx < min(total, (r + 1) * slice); idx += CTHREADS) {
+  // the blocks of the cluster, in rank order
+  for (int t = threadIdx.x; t < slice && r * slice + t < total; t += CTHREADS) {
+    const int idx = r * slice + t;
     const int h = idx / HD, d = idx % HD;
     float M = -INFINITY;
-    for (int rr = 0; rr < C; ++rr) M = fmaxf(M, cluster.map_shared_rank(part, rr)[h * ROW + HD]);
+    for (int rr = 0; rr < C; ++rr) M = fmaxf(M, recv[(size_t)rr * rs + slice + 2 * h]);
     float L = 0.f, A = 0.f;
     for (int rr = 0; rr < C; ++rr) {
-      const float* src = cluster.map_shared_rank(part, rr) + h * ROW;
-      const float mr = src[HD];
+      const float* src = recv + (size_t)rr * rs;
+      const float mr = src[slice + 2 * h];
       if (mr == -INFINITY) continue;
       const float f = exp2f(mr - M);
-      L = fmaf(src[HD + 1], f, L);
-      A = fmaf(src[d], f, A);
+      L = fmaf(src[slice + 2 * h + 1], f, L);
+      A = fmaf(src[t], f, A);
     }
     a.out[(size_t)row * a.nh * HD + (size_t)(kvh * G + h) * HD + d] = __float2bfloat16_rn(A / L);
   }
-  cluster.sync();        // nobody leaves while its shared memory may still be read
 }
 
 size_t cluster_smem(int stages, int max_tiles) {
-  return (size_t)stages * STAGE_BYTES + (size_t)(1 + CW) * GP * ROW * sizeof(float) + (2 * CMAX_STAGES + 1) * 8 +
+  return (size_t)stages * STAGE_BYTES + (size_t)RECV_FLOATS * sizeof(float) + (size_t)CW * GP * ROW * sizeof(float) + (2 * CMAX_STAGES + 1) * 8 +
          (size_t)(max_tiles + 8) * sizeof(int) + (size_t)GP * HD * sizeof(__nv_bfloat16) + 1024;
 }
 
