@@ -569,8 +569,8 @@ def decode_cluster_size(lib, head_dim: int, num_decode: int, num_kv_heads: int, 
   block at least one 64-key tile (6 is tried as well: two requests are a little faster with it) and whose clusters - one per (request, kv head) - can all be on the GPU at once:
   a second round of clusters would double the kernel's time.  (Measured on B200, 8 kv heads of 128, 2048-token
   contexts: 1 / 2 / 4 / 8 / 16 requests are fastest with clusters of 8 / 4 / 4 / 2 / 1, which is what this rule
-  picks; decode steps take 0.74 / 0.79 / 0.83 / 0.99 / 1.34 ms against 0.92 / 0.92 / 0.99 / 1.12 / 1.55 ms with
-  the persistent kernel.)  Blocks with more than 64 tiles each, or more (request, kv head) pairs than fit at once,
+  picks; decode steps took 0.74 / 0.79 / 0.83 / 0.99 / 1.34 ms against 0.92 / 0.92 / 0.99 / 1.12 / 1.55 ms with
+  the persistent kernel, and the sizes were measured again after the cluster's merge had lost a barrier.)  Blocks with more than 64 tiles each, or more (request, kv head) pairs than fit at once,
   stream better from the persistent kernel, which deals the tiles out evenly over the SMs."""
   tiles = -(-span // 64) + 1
 
