@@ -75,7 +75,10 @@
 // chain - with two stages the K of tile j + 2 can only be asked for when S of tile j is done, so two tiles cannot
 // take less than that latency and an S product, and shared memory has no room for a third stage of K and of V
 // beside Q - their bandwidth is not the bound), and pairs of blocks (31.4 at 2048 tokens, 291 against 303
-// at 8192, 56.3 against 57.7 at 32 heads): pairs run where a step brings many tokens.  With an odd number of
+// at 8192, 56.3 against 57.7 at 32 heads): pairs run where a step brings many tokens.  P handed to the P V products
+// in two halves of 64 keys, so that the first four products run while the other half is still exponentiated, was
+// slower (31.9 against 31.1 at 2048 tokens, 317 against 303 at 8192): a second wait for the stores, a second arrival
+// and a second wait of the issuing thread cost more than the earlier start gains.  With an odd number of
 // query heads per kv head a block takes 128 tokens of one head from a list of 128-token tiles (41 against 66 us
 // on three prompts of 24 heads when half the works of a 64-token list were skipped one by one).
 //
