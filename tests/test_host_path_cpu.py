@@ -249,3 +249,27 @@ def test_stage_ranges_and_the_profile_option(cpu_kernels, model_dirs, tmp_path):
   for name in ("stage::schedule", "stage::describe+launch", "stage::wait+update"):
     assert name in text
   assert not stages_enabled()
+
+
+def test_the_attention_work_lists_of_a_step():
+  """What the attention mixer declares for a step: the items that bring one token, and the tiles of 64 and of 128
+  new tokens of the items that bring more (the 128-token tiles are the works of the tcgen05 prefill kernel where a
+  block takes one head).  The keys - what the launches depend on - are the lists' lengths and the class of the
+  longest decode context."""
+  from miniinfer_b200.parts.base import HostStep
+  from miniinfer_b200.parts.mixer import DecodeItems, PrefillTiles, PrefillWideTiles
+  q_len = np.array([1, 130, 64, 2, 1], dtype=np.int32)
+  start = np.array([99, 0, 500, 7, 1500], dtype=np.int32)
+  step = HostStep(q_len, start, 4096)
+  assert DecodeItems().build(step).tolist() == [0, 4]
+  assert DecodeItems().key(step) == (2, 2048)            # the longest decode context, 1501 tokens, in classes of 1024
+  tiles = PrefillTiles().build(step).reshape(-1, 2).tolist()
+  assert tiles == [[1, 0], [1, 64], [1, 128], [2, 0], [3, 0]]
+  assert PrefillTiles().key(step) == (5,)
+  wide = PrefillWideTiles().build(step).reshape(-1, 2).tolist()
+  assert wide == [[1, 0], [1, 128], [2, 0], [3, 0]]
+  assert PrefillWideTiles().key(step) == (4,)
+  assert PrefillTiles.name != PrefillWideTiles.name
+  # a step of decode tokens only has neither kind of tile
+  only = HostStep(np.ones(3, dtype=np.int32), np.array([5, 6, 7], dtype=np.int32), 4096)
+  assert PrefillTiles().build(only).size == 0 and PrefillWideTiles().key(only) == (0,)
